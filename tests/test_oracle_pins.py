@@ -126,7 +126,11 @@ def test_prep_backward():
     for slot, name in zip(oprep.BIAS_SLOTS, ("dt_bias", "gamma_bias", "omega_bias",
                                              "mix_r_bias", "mix_theta_bias",
                                              "mix_k_prev_bias", "mix_k_curr_bias")):
-        assert rel_err(dbias[:, slot], g["d_" + name]) < 2e-4, name
+        # a bias gradient is a signed sum over all tokens of fp32-noisy terms:
+        # bound the mismatch by the sum of magnitudes, not by the (cancelling) sum
+        mag = np.abs(dp[..., slot]).sum(axis=(0, 1))
+        floor = 5e-6 * b * T  # fp32 noise floor of the reference per token (O(1) upstream)
+        assert np.all(np.abs(dbias[:, slot] - g["d_" + name]) <= 1e-4 * mag + floor), name
     dbc, dscale = oprep.pack_bc_bwd(g["bc"], scale, cfg, g["gB"], g["gC"])
     assert rel_err(dbc, g["d_bc"]) < 2e-5
     assert rel_err(dscale[:, :2], g["d_b_scale"]) < 2e-5
@@ -159,3 +163,46 @@ def test_conv(tag):
     dxs, dws, dbs, _ = oprep.cconv1d_bwd(g["x"], g["w"], g["bias"], st, g["dy"], silu=True)
     assert rel_err(dxs, g["dx_silu"]) < 1e-12 and rel_err(dws, g["dw_silu"]) < 1e-12
     assert rel_err(dbs, g["dbias_silu"]) < 1e-12
+
+
+def test_prep_coefficient_vjp_matches_float64_autograd():
+    """The hand-written VJP equals torch.autograd of the same map in float64
+    (removes the fp32 noise of the reference fixture from the comparison)."""
+    import math
+
+    import torch
+
+    torch.manual_seed(0)
+    H = 3
+    cfg = oprep.PrepConfig(n_heads=H, d_state=4, d_head=4)
+    params = (1.5 * torch.randn(2, 7, H, 13, dtype=torch.float64)).requires_grad_(True)
+    bias = torch.randn(H, 13, dtype=torch.float64) * 0.3
+    sg = torch.sigmoid
+    p = params.permute(0, 2, 1, 3) + bias[None, :, None, :]
+    dt = cfg.dt_min + (cfg.dt_max - cfg.dt_min) * sg(p[..., 0])
+    gamma = torch.nn.functional.softplus(p[..., 1])
+    rs = cfg.r_min + (cfg.r_max - cfg.r_min) * torch.exp(-gamma * dt)
+    ths = p[..., 2] * dt
+    rd = cfg.r_min + (cfg.r_max - cfg.r_min) * sg(p[..., 3])
+    thd = cfg.theta_bound * torch.tanh(p[..., 4])
+    r = torch.lerp(rd, rs, sg(p[..., 5]))
+    th = torch.remainder(torch.lerp(thd, ths, sg(p[..., 6])) + math.pi, 2 * math.pi) - math.pi
+    rho = torch.polar(r, th)
+    z = torch.complex(torch.log(r), th)
+    k1 = (rho - 1) / z
+    k2 = (rho * (z - 1) + 1) / (z * z)
+    kps = dt * k2
+    kcs = dt * k1 - kps
+    kpl = cfg.k_max * torch.complex(torch.tanh(p[..., 9]), torch.tanh(p[..., 10]))
+    kcl = cfg.k_max * torch.complex(torch.tanh(p[..., 11]), torch.tanh(p[..., 12]))
+    kp = kpl + sg(p[..., 7]) * (kps - kpl)
+    kc = kcl + sg(p[..., 8]) * (kcs - kcl)
+    M = torch.view_as_real(rho)
+    K = torch.stack([torch.view_as_real(kp), torch.view_as_real(kc)], -2)
+    gM, gK = torch.randn_like(M), torch.randn_like(K)
+    (gp,) = torch.autograd.grad([M, K], [params], [gM, gK])
+    dp, _ = oprep.coefficients_bwd(params.detach().numpy(), bias.numpy(), cfg,
+                                   gM.numpy(), gK.numpy())
+    M2, K2 = oprep.coefficients_fwd(params.detach().numpy(), bias.numpy(), cfg)
+    assert rel_err(M2, M.detach().numpy()) < 1e-13 and rel_err(K2, K.detach().numpy()) < 1e-13
+    assert rel_err(dp, gp.numpy()) < 1e-12
