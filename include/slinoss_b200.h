@@ -1,0 +1,198 @@
+/*
+ * slinoss_b200 -- C ABI of the B200 (sm_100a) v2x2ssd scan backend.
+ *
+ * Every entry point
+ *   - takes raw DEVICE pointers, plain sizes and a CUDA stream (as void*),
+ *   - returns an int status: 0 = ok, negative = argument error (SLX_E_*),
+ *     positive = the cudaError_t raised by a launch,
+ *   - never allocates and never synchronises; scratch memory is passed in by the
+ *     caller (sizes from the *_workspace_bytes functions),
+ *   - launches on the given stream only.
+ * slx_last_error_string() returns a thread-local description of the last
+ * non-zero status.
+ *
+ * Layouts are the reference's canonical ones (slinoss/ops/v2x2ssd/reference.py:
+ * 1-41), with (batch, heads) flattened to BH:
+ *   U,Y      (BH, T, P)        activation dtype (see slx_dtype)
+ *   B,C      (BH, T, 2N)       activation dtype, interleaved [re0,im0,re1,...]
+ *   M        (BH, T, 2)        fp32 packed complex
+ *   K        (BH, T, 2, 2)     fp32, tap 0 = prev, tap 1 = curr, each (re,im)
+ *   states   (BH, P, 2N)       fp32 interleaved complex
+ *   chunk tensors (BH, NC, P, 2N) / (BH, NC, 2), NC = ceil(T / chunk), fp32
+ * Tokens past T in the last chunk behave as M=1, K=U=B=C=0
+ * (reference.py:541-667).  Nullable pointers are marked [opt].
+ */
+#ifndef SLINOSS_B200_H_
+#define SLINOSS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SLX_ABI_VERSION 1
+
+typedef enum { SLX_F32 = 0, SLX_BF16 = 1, SLX_F16 = 2 } slx_dtype;
+
+enum {
+  SLX_OK = 0,
+  SLX_E_NULL = -1,        /* required pointer is NULL */
+  SLX_E_SHAPE = -2,       /* non-positive or inconsistent size */
+  SLX_E_UNSUPPORTED = -3, /* size/dtype outside what the kernels cover */
+  SLX_E_WORKSPACE = -4,   /* workspace too small or misaligned */
+  SLX_E_DTYPE = -5
+};
+
+typedef struct {
+  int32_t batch_heads; /* BH = batch * heads                               */
+  int32_t T;           /* tokens                                           */
+  int32_t P;           /* head dim (1..64)                                 */
+  int32_t N;           /* complex state pairs; D = 2N                      */
+  int32_t chunk;       /* chunk length L: multiple of 16, 16..128          */
+  int32_t dtype;       /* slx_dtype of U, B, C, Y and their gradients      */
+} slx_scan_shape;
+
+int slx_abi_version(void);
+const char *slx_last_error_string(void);
+
+/* ---- forward stages --------------------------------------------------- */
+
+/* Replaces reference.py:937 chunk_increment (CuTe: kernels/fwd/__init__.py:740
+ * chunk_increment_cute).  inc (BH,NC,P,2N) fp32, m_chunk (BH,NC,2) fp32. */
+int slx_chunk_increment_fwd(const slx_scan_shape *s, const void *U,
+                            const float *M, const float *K, const void *B,
+                            const float *B_prev /*[opt] (BH,2N)*/,
+                            const float *U_prev /*[opt] (BH,P)*/, float *inc,
+                            float *m_chunk, void *stream);
+
+/* Replaces reference.py:1015 state_passing (CuTe: kernels/fwd/__init__.py:897).
+ * chunk_starts may alias inc (the pass is then in place). */
+int slx_state_passing_fwd(int32_t batch_heads, int32_t n_chunks, int32_t P,
+                          int32_t N, const float *inc, const float *m_chunk,
+                          const float *initial_states /*[opt]*/,
+                          float *chunk_starts, float *final_state, void *stream);
+
+/* Replaces reference.py:1059 chunk_scan (CuTe: kernels/fwd/__init__.py:1125). */
+int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M,
+                       const float *K, const void *B, const void *C,
+                       const float *chunk_starts, const float *B_prev /*[opt]*/,
+                       const float *U_prev /*[opt]*/, void *Y, void *stream);
+
+/* Replaces reference.py:1195 v2x2ssd / cute/kernels/fwd/__init__.py:1691
+ * v2x2ssd_fwd_cute: the three stages back to back on one stream.
+ * chunk_starts doubles as the increment buffer. */
+int slx_v2x2ssd_fwd(const slx_scan_shape *s, const void *U, const float *M,
+                    const float *K, const void *B, const void *C,
+                    const float *initial_states /*[opt]*/,
+                    const float *B_prev /*[opt]*/, const float *U_prev /*[opt]*/,
+                    void *Y, float *final_state, float *chunk_starts,
+                    float *m_chunk, void *stream);
+
+/* ---- backward ----------------------------------------------------------- */
+
+/* Scratch for slx_v2x2ssd_bwd (and the three backward stages). */
+size_t slx_v2x2ssd_bwd_workspace_bytes(const slx_scan_shape *s);
+
+/* dZ0[c] = sum_t conj(prefix_t) dY_t (x) c_t : gradient of the loss with respect
+ * to each chunk's start state through that chunk's outputs only.  Replaces
+ * cute/kernels/bwd/chunk_scan/dz0.py:521.  dZ0 (BH,NC,P,2N) fp32. */
+int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *C,
+                           const void *dY, float *dZ0, void *stream);
+
+/* Reverse recurrence over chunks (cute/kernels/bwd/state_passing/state.py:119
+ * and m.py:83 fused): on return d_inc[c] = dL/d(end state of chunk c) (it may
+ * alias dZ0), d_initial = dL/d(initial state), and zdot (BH,NC,2) holds
+ * sum_{p,n} conj(end_state_c) * d_inc[c], the chunk-level term of dM.
+ * final_state is the forward's fp32 final state. */
+int slx_state_passing_bwd(int32_t batch_heads, int32_t n_chunks, int32_t P,
+                          int32_t N, const float *dZ0, const float *m_chunk,
+                          const float *chunk_starts, const float *final_state,
+                          const float *d_final /*[opt]*/, float *d_inc,
+                          float *d_initial /*[opt]*/, float *zdot,
+                          float *zdot_partials /* workspace */, void *stream);
+
+/* Full backward of the scan: what torch.autograd computes through
+ * reference.py:1195; replaces cute/kernels/bwd/__init__.py:1310
+ * v2x2ssd_bwd_stateful_cute.  Gradients dU,dB,dC in the activation dtype;
+ * dM,dK,d_initial,dB_prev,dU_prev fp32. */
+int slx_v2x2ssd_bwd(const slx_scan_shape *s, const void *U, const float *M,
+                    const float *K, const void *B, const void *C,
+                    const float *B_prev /*[opt]*/, const float *U_prev /*[opt]*/,
+                    const float *chunk_starts, const float *m_chunk,
+                    const float *final_state, const void *dY,
+                    const float *d_final /*[opt]*/, void *dU, float *dM,
+                    float *dK, void *dB, void *dC, float *d_initial /*[opt]*/,
+                    float *dB_prev /*[opt]*/, float *dU_prev /*[opt]*/,
+                    void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- scan preparation ---------------------------------------------------- */
+
+typedef struct {
+  int32_t batch, T, heads, P, N;
+  int32_t dtype;        /* slx_dtype of value / params / bc and of U, B, C  */
+  int32_t normalize_bc; /* RMS-norm (eps 1e-5) + per-head scale when != 0   */
+  float dt_min, dt_max, r_min, r_max, theta_bound, k_max, eps;
+  /* row strides in elements of the (batch*T, width) inputs: they may be column
+   * slices of one wider projection output */
+  int64_t value_stride, params_stride, bc_stride;
+} slx_prep_shape;
+
+/* Replaces slinoss/layers/scanprep.py:351 _prepare_inputs_reference (CuTe:
+ * ops/scanprep/cute/kernels/fwd.py:83).  value (b,T,H*P), params (b,T,H*13),
+ * bc (b,T,H*4*N) -> U (b,H,T,P), B,C (b,H,T,2N) activation dtype; M (b,H,T,2),
+ * K (b,H,T,2,2) fp32.  bias (H,13) fp32 (zeros in the unbiased slots),
+ * scale (H,4,N) fp32 [opt when normalize_bc == 0]. */
+int slx_scanprep_fwd(const slx_prep_shape *s, const void *value,
+                     const void *params, const void *bc, const float *bias,
+                     const float *scale, void *U, float *M, float *K, void *B,
+                     void *C, void *stream);
+
+size_t slx_scanprep_bwd_workspace_bytes(const slx_prep_shape *s);
+
+/* VJP of slx_scanprep_fwd (CuTe: ops/scanprep/cute/kernels/bwd.py:113,271).
+ * d_value/d_params/d_bc are contiguous (b,T,width) in the activation dtype;
+ * d_bias (H,13) and d_scale (H,4,N) fp32 are overwritten (deterministic
+ * two-level reduction through the workspace, no atomics). */
+int slx_scanprep_bwd(const slx_prep_shape *s, const void *params, const void *bc,
+                     const float *bias, const float *scale, const void *dU,
+                     const float *dM, const float *dK, const void *dB,
+                     const void *dC, void *d_value, void *d_params, void *d_bc,
+                     float *d_bias, float *d_scale, void *workspace,
+                     size_t workspace_bytes, void *stream);
+
+/* ---- depthwise causal conv1d --------------------------------------------- */
+
+typedef struct {
+  int32_t batch, T, channels, width; /* width 2..4 */
+  int32_t dtype;                     /* slx_dtype of x, y, weight, bias, state */
+  int32_t silu;                      /* fuse y = silu(conv) when != 0          */
+  int64_t x_stride;                  /* row stride of x (batch*T, channels)    */
+  int64_t x_batch_stride;            /* elements between batches of x          */
+} slx_conv_shape;
+
+/* Replaces csrc/causal_conv1d/causal_conv1d.cpp:150 causal_conv1d_fwd as the
+ * mixer uses it (slinoss/layers/mixer.py:456 _apply_cconv_cuda): x (b,T,C)
+ * channel-last, weight (C,W), bias (C) [opt], state (b,C,W-1) [opt] ->
+ * y (b,T,C) contiguous, next_state (b,C,W-1) [opt]. */
+int slx_cconv1d_fwd(const slx_conv_shape *s, const void *x, const void *weight,
+                    const void *bias, const void *state, void *y,
+                    void *next_state, void *stream);
+
+size_t slx_cconv1d_bwd_workspace_bytes(const slx_conv_shape *s);
+
+/* Replaces causal_conv1d.cpp:261 causal_conv1d_bwd.  dy (b,T,C) contiguous,
+ * d_next_state (b,C,W-1) [opt]; dx (b,T,C) contiguous activation dtype;
+ * dweight (C,W), dbias (C) fp32, overwritten, deterministic; dstate (b,C,W-1)
+ * fp32 [opt]. */
+int slx_cconv1d_bwd(const slx_conv_shape *s, const void *x, const void *weight,
+                    const void *bias, const void *state, const void *dy,
+                    const void *d_next_state, void *dx, float *dweight,
+                    float *dbias, float *dstate, void *workspace,
+                    size_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SLINOSS_B200_H_ */

@@ -1,0 +1,107 @@
+"""ctypes binding of ``libslinoss_b200.so`` (the C ABI in ``include/slinoss_b200.h``).
+
+The library is the only compute path of this package: if it is missing or a
+symbol is absent, the import of any op fails loudly -- there is no CPU or
+framework fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int32, c_int64, c_size_t, c_void_p
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "_C" / "libslinoss_b200.so"
+
+SLX_F32, SLX_BF16, SLX_F16 = 0, 1, 2
+_DTYPE_CODE = {torch.float32: SLX_F32, torch.bfloat16: SLX_BF16, torch.float16: SLX_F16}
+
+
+class ScanShape(Structure):
+    _fields_ = [("batch_heads", c_int32), ("T", c_int32), ("P", c_int32), ("N", c_int32),
+                ("chunk", c_int32), ("dtype", c_int32)]
+
+
+class PrepShape(Structure):
+    _fields_ = [("batch", c_int32), ("T", c_int32), ("heads", c_int32), ("P", c_int32),
+                ("N", c_int32), ("dtype", c_int32), ("normalize_bc", c_int32),
+                ("dt_min", c_float), ("dt_max", c_float), ("r_min", c_float), ("r_max", c_float),
+                ("theta_bound", c_float), ("k_max", c_float), ("eps", c_float),
+                ("value_stride", c_int64), ("params_stride", c_int64), ("bc_stride", c_int64)]
+
+
+class ConvShape(Structure):
+    _fields_ = [("batch", c_int32), ("T", c_int32), ("channels", c_int32), ("width", c_int32),
+                ("dtype", c_int32), ("silu", c_int32), ("x_stride", c_int64),
+                ("x_batch_stride", c_int64)]
+
+
+# name -> (restype, argtypes); mirrors include/slinoss_b200.h one to one
+_P = c_void_p
+SIGNATURES = {
+    "slx_abi_version": (c_int32, []),
+    "slx_last_error_string": (c_char_p, []),
+    "slx_chunk_increment_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 9),
+    "slx_state_passing_fwd": (c_int32, [c_int32] * 4 + [_P] * 6),
+    "slx_chunk_scan_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 10),
+    "slx_v2x2ssd_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 13),
+    "slx_v2x2ssd_bwd_workspace_bytes": (c_size_t, [POINTER(ScanShape)]),
+    "slx_chunk_scan_bwd_dz0": (c_int32, [POINTER(ScanShape)] + [_P] * 5),
+    "slx_state_passing_bwd": (c_int32, [c_int32] * 4 + [_P] * 10),
+    "slx_v2x2ssd_bwd": (c_int32, [POINTER(ScanShape)] + [_P] * 21 + [c_size_t, _P]),
+    "slx_scanprep_fwd": (c_int32, [POINTER(PrepShape)] + [_P] * 11),
+    "slx_scanprep_bwd_workspace_bytes": (c_size_t, [POINTER(PrepShape)]),
+    "slx_scanprep_bwd": (c_int32, [POINTER(PrepShape)] + [_P] * 15 + [c_size_t, _P]),
+    "slx_cconv1d_fwd": (c_int32, [POINTER(ConvShape)] + [_P] * 7),
+    "slx_cconv1d_bwd_workspace_bytes": (c_size_t, [POINTER(ConvShape)]),
+    "slx_cconv1d_bwd": (c_int32, [POINTER(ConvShape)] + [_P] * 11 + [c_size_t, _P]),
+}
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load the shared library (once) and bind every declared symbol."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build the sm_100a kernels first "
+                "(python -m slinoss_b200.build). There is no fallback path.")
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError if the export is absent
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dt]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {dt}; expected float32, bfloat16 or float16") from None
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def check(status: int, what: str) -> None:
+    """Turn a non-zero C status into the exception the reference would raise."""
+    if status == 0:
+        return
+    msg = lib().slx_last_error_string().decode("utf-8", "replace")
+    if status < 0:
+        if status == -5:
+            raise TypeError(f"{what}: {msg}")
+        raise ValueError(f"{what}: {msg}")
+    raise RuntimeError(f"{what}: CUDA error {status}: {msg}")

@@ -1,0 +1,88 @@
+"""Drop-in backends for the reference's ``SLinOSSMixer`` backend switch.
+
+Each class implements the matching Protocol of slinoss/layers/backend.py
+(``ScanBackend`` :238, ``ScanPrepBackend`` :114, ``CConv1dBackend`` :174) and is
+handed to the mixer through its constructor:
+
+    SLinOSSMixer(..., backend=B200ScanBackend(), scanprep_backend=B200ScanPrepBackend(),
+                 cconv_backend=B200CConv1dBackend())
+
+The classes accept the reference's own ``ScanInputs`` / ``ScanPrepInputs`` /
+``ScanState`` objects (only attributes are read) and return this package's
+mirror types, which expose the same attributes.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple, Union
+
+import torch
+
+from .ops.cconv1d import cconv1d_b200
+from .ops.scanprep import scanprep_b200
+from .ops.v2x2ssd import v2x2ssd_b200
+from .types import ScanInputs, ScanState
+
+
+def _default_compute_dtype(dtype: torch.dtype) -> Optional[torch.dtype]:
+    # slinoss/layers/backend.py:271-274
+    return torch.float32 if dtype in (torch.float16, torch.bfloat16) else None
+
+
+class B200ScanBackend:
+    """``ScanBackend`` running the sm_100a chunked scan (cf. ``CuteScanBackend``,
+    backend.py:318-377)."""
+
+    def __init__(self, *, compute_dtype: Optional[torch.dtype] = None, state_cls=ScanState) -> None:
+        self.compute_dtype = compute_dtype
+        self.state_cls = state_cls
+
+    def __call__(self, inputs, *, chunk_size: int, state=None,
+                 return_state: Optional[bool] = None) -> Union[torch.Tensor, Tuple[torch.Tensor, ScanState]]:
+        if return_state is None:
+            return_state = state is not None
+        st = self.state_cls() if state is None else state
+        odt = inputs.U.dtype
+        cdt = self.compute_dtype if self.compute_dtype is not None else _default_compute_dtype(odt)
+        out = v2x2ssd_b200(inputs.U, inputs.M, inputs.K, inputs.B, inputs.C, chunk_size=chunk_size,
+                           initial_states=st.state, B_prev=st.b_prev, U_prev=st.u_prev,
+                           compute_dtype=cdt, output_dtype=odt, return_state=bool(return_state))
+        if not return_state:
+            return out
+        y, final_state, b_last, u_last = out
+        return y, self.state_cls(state=final_state, b_prev=b_last, u_prev=u_last)
+
+
+class B200ScanPrepBackend:
+    """``ScanPrepBackend``: ``owner`` is the ``SLinOSSScanPrep`` module whose
+    hyper-parameters and parameters are read (cf. scanprep.py:359-384)."""
+
+    def __init__(self, inputs_cls=ScanInputs) -> None:
+        self.inputs_cls = inputs_cls
+
+    def __call__(self, owner, inputs):
+        out = scanprep_b200(
+            inputs.value, inputs.params, inputs.bc, n_heads=owner.n_heads, d_state=owner.d_state,
+            d_head=owner.d_head, normalize_bc=owner.normalize_bc, dt_min=owner.dt_min,
+            dt_max=owner.dt_max, r_min=owner.r_min, r_max=owner.r_max, theta_bound=owner.theta_bound,
+            k_max=owner.k_max, eps=owner.eps, dt_bias=owner.dt_bias, gamma_bias=owner.gamma_bias,
+            omega_bias=owner.omega_bias, mix_r_bias=owner.mix_r_bias,
+            mix_theta_bias=owner.mix_theta_bias, mix_k_prev_bias=owner.mix_k_prev_bias,
+            mix_k_curr_bias=owner.mix_k_curr_bias, b_scale=owner.b_scale, c_scale=owner.c_scale)
+        if self.inputs_cls is ScanInputs:
+            return out
+        return self.inputs_cls(U=out.U, M=out.M, K=out.K, B=out.B, C=out.C)
+
+
+class B200CConv1dBackend:
+    """``CConv1dBackend``: ``owner`` is the mixer (``dw_weight (C,W)``, ``dw_bias (C)``,
+    ``d_conv``); returns ``(y (b,T,C), next_state (b,C,W-1))`` like
+    mixer.py:420-454.  Width-1 convolutions are not a kernel case."""
+
+    def __call__(self, owner, x: torch.Tensor, conv_state: Optional[torch.Tensor]):
+        if int(owner.d_conv) < 2:
+            raise ValueError("B200CConv1dBackend needs d_conv in {2,3,4}.")
+        return cconv1d_b200(x, owner.dw_weight, owner.dw_bias, conv_state)
+
+
+__all__ = ["B200ScanBackend", "B200ScanPrepBackend", "B200CConv1dBackend"]

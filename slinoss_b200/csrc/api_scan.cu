@@ -1,0 +1,305 @@
+// C-ABI entry points of the scan (argument checks + launches; no allocation,
+// no synchronisation).
+#include <cstdarg>
+#include <cstdio>
+
+#include "scan_simt.cuh"
+#include "state_passing.cuh"
+
+namespace slx {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int fail(int code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_launch(const char *what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return (int)e;
+  }
+  return SLX_OK;
+}
+
+static int check_shape(const slx_scan_shape *s, ScanDims *d) {
+  SLX_REQUIRE(s != nullptr, SLX_E_NULL, "shape is NULL");
+  SLX_REQUIRE(s->batch_heads > 0 && s->T > 0 && s->P > 0 && s->N > 0 && s->chunk > 0, SLX_E_SHAPE,
+              "batch_heads, T, P, N and chunk must be positive (got %d %d %d %d %d)", s->batch_heads, s->T, s->P,
+              s->N, s->chunk);
+  SLX_REQUIRE(s->P <= kPMax, SLX_E_UNSUPPORTED, "P=%d exceeds the supported maximum %d", s->P, kPMax);
+  SLX_REQUIRE(s->chunk == 16 || s->chunk == 32 || s->chunk == 64 || s->chunk == 128, SLX_E_UNSUPPORTED,
+              "chunk=%d: supported chunk lengths are 16, 32, 64, 128", s->chunk);
+  SLX_REQUIRE(s->dtype == SLX_F32 || s->dtype == SLX_BF16 || s->dtype == SLX_F16, SLX_E_DTYPE, "bad dtype %d",
+              s->dtype);
+  SLX_REQUIRE(s->batch_heads <= 65535, SLX_E_UNSUPPORTED, "batch_heads=%d exceeds 65535", s->batch_heads);
+  d->BH = s->batch_heads;
+  d->T = s->T;
+  d->P = s->P;
+  d->N = s->N;
+  d->D = 2 * s->N;
+  d->L = s->chunk;
+  d->NC = (s->T + s->chunk - 1) / s->chunk;
+  return SLX_OK;
+}
+
+template <typename K>
+static int set_smem(K kernel, size_t bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(%zu bytes): %s", bytes, cudaGetErrorString(e));
+    return (int)e;
+  }
+  return SLX_OK;
+}
+
+#define SLX_DISPATCH_L(Lval, ...)            \
+  switch (Lval) {                            \
+    case 16: { constexpr int L_ = 16; __VA_ARGS__; } break;   \
+    case 32: { constexpr int L_ = 32; __VA_ARGS__; } break;   \
+    case 64: { constexpr int L_ = 64; __VA_ARGS__; } break;   \
+    default: { constexpr int L_ = 128; __VA_ARGS__; } break;  \
+  }
+
+#define SLX_DISPATCH_T(dt, ...)                                   \
+  switch (dt) {                                                   \
+    case SLX_F32: { using T_ = float; __VA_ARGS__; } break;       \
+    case SLX_BF16: { using T_ = __nv_bfloat16; __VA_ARGS__; } break; \
+    default: { using T_ = __half; __VA_ARGS__; } break;           \
+  }
+
+// ---- stage launchers ----------------------------------------------------------
+template <typename T, int L, int MODE>
+static int launch_outer(const ScanDims &d, const void *A, const void *X, const float *M, const float *K,
+                        const float *Bprev, const float *Uprev, float *out, float *m_chunk, cudaStream_t st) {
+  OuterArgs<T> a{(const T *)A, (const T *)X, M, K, Bprev, Uprev, out, m_chunk, d};
+  auto kern = chunk_outer_kernel<T, L, MODE>;
+  size_t smem = outer_smem_bytes<L>();
+  int rc = set_smem(kern, smem);
+  if (rc) return rc;
+  kern<<<dim3(d.NC, d.BH), kThreads, smem, st>>>(a);
+  return check_launch(MODE == 0 ? "chunk_increment_fwd" : "chunk_scan_bwd_dz0");
+}
+
+template <typename T, int L>
+static int launch_scan_fwd(const ScanDims &d, const void *U, const float *M, const float *K, const void *B,
+                           const void *C, const float *starts, const float *Bprev, const float *Uprev, void *Y,
+                           cudaStream_t st) {
+  ScanFwdArgs<T> a{(const T *)U, (const T *)B, (const T *)C, M, K, starts, Bprev, Uprev, (T *)Y, nullptr, d};
+  auto kern = chunk_scan_fwd_kernel<T, L>;
+  size_t smem = scan_fwd_smem_bytes<L>();
+  int rc = set_smem(kern, smem);
+  if (rc) return rc;
+  kern<<<dim3(d.NC, d.BH), kThreads, smem, st>>>(a);
+  return check_launch("chunk_scan_fwd");
+}
+
+template <typename T, int L>
+static int launch_scan_bwd(const ScanDims &d, const ScanBwdArgs<T> &a, cudaStream_t st) {
+  auto kern = chunk_scan_bwd_kernel<T, L>;
+  size_t smem = scan_bwd_smem_bytes<L>();
+  int rc = set_smem(kern, smem);
+  if (rc) return rc;
+  kern<<<dim3(d.NC, d.BH), kThreads, smem, st>>>(a);
+  return check_launch("chunk_scan_bwd");
+}
+
+static int launch_state_fwd(int BH, int NC, int P, int N, const float *inc, const float *m_chunk, const float *init,
+                            float *starts, float *final_state, cudaStream_t st) {
+  const int elems = P * 2 * N;
+  if (elems % 4 == 0) {
+    int nv = elems / 4;
+    state_passing_fwd_kernel<4><<<dim3((nv + 255) / 256, BH), 256, 0, st>>>(inc, m_chunk, init, starts, final_state,
+                                                                          NC, nv);
+  } else {
+    int nv = elems / 2;
+    state_passing_fwd_kernel<2><<<dim3((nv + 255) / 256, BH), 256, 0, st>>>(inc, m_chunk, init, starts, final_state,
+                                                                          NC, nv);
+  }
+  return check_launch("state_passing_fwd");
+}
+
+static int state_bwd_blocks(int P, int N) {
+  const int elems = P * 2 * N;
+  int nv = (elems % 4 == 0) ? elems / 4 : elems / 2;
+  return (nv + 255) / 256;
+}
+
+static int launch_state_bwd(int BH, int NC, int P, int N, const float *dZ0, const float *m_chunk, const float *starts,
+                            const float *final_state, const float *d_final, float *d_inc, float *d_initial,
+                            float *zdot, float *partials, cudaStream_t st) {
+  const int elems = P * 2 * N;
+  const int nblk = state_bwd_blocks(P, N);
+  if (elems % 4 == 0) {
+    state_passing_bwd_kernel<4><<<dim3(nblk, BH), 256, 0, st>>>(dZ0, m_chunk, starts, final_state, d_final, d_inc,
+                                                               d_initial, partials, NC, elems / 4);
+  } else {
+    state_passing_bwd_kernel<2><<<dim3(nblk, BH), 256, 0, st>>>(dZ0, m_chunk, starts, final_state, d_final, d_inc,
+                                                               d_initial, partials, NC, elems / 2);
+  }
+  int rc = check_launch("state_passing_bwd");
+  if (rc) return rc;
+  int rows = BH * NC;
+  zdot_reduce_kernel<<<(rows + 255) / 256, 256, 0, st>>>(partials, zdot, rows, nblk);
+  return check_launch("zdot_reduce");
+}
+
+// workspace layout of the backward (all fp32, 256-byte aligned sections)
+struct BwdWs {
+  size_t d_inc, zdot, partials, carryB, carryU, total;
+};
+static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+static BwdWs bwd_ws(const ScanDims &d) {
+  BwdWs w;
+  size_t off = 0;
+  w.d_inc = off;
+  off += align256(sizeof(float) * (size_t)d.BH * d.NC * d.P * d.D);
+  w.zdot = off;
+  off += align256(sizeof(float) * (size_t)d.BH * d.NC * 2);
+  w.partials = off;
+  off += align256(sizeof(float) * (size_t)d.BH * d.NC * 2 * state_bwd_blocks(d.P, d.N));
+  w.carryB = off;
+  off += align256(sizeof(float) * (size_t)d.BH * d.NC * d.D);
+  w.carryU = off;
+  off += align256(sizeof(float) * (size_t)d.BH * d.NC * d.P);
+  w.total = off;
+  return w;
+}
+
+}  // namespace slx
+
+using namespace slx;
+
+extern "C" {
+
+int slx_abi_version(void) { return SLX_ABI_VERSION; }
+const char *slx_last_error_string(void) { return g_err; }
+
+int slx_chunk_increment_fwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
+                            const float *B_prev, const float *U_prev, float *inc, float *m_chunk, void *stream) {
+  ScanDims d;
+  int rc = check_shape(s, &d);
+  if (rc) return rc;
+  SLX_REQUIRE(U && M && K && B && inc && m_chunk, SLX_E_NULL, "chunk_increment_fwd: NULL tensor");
+  SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
+  SLX_DISPATCH_T(s->dtype, SLX_DISPATCH_L(d.L, rc = (launch_outer<T_, L_, 0>(d, U, B, M, K, B_prev, U_prev, inc,
+                                                                              m_chunk, as_stream(stream)))));
+  return rc;
+}
+
+int slx_state_passing_fwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const float *inc, const float *m_chunk,
+                          const float *initial_states, float *chunk_starts, float *final_state, void *stream) {
+  SLX_REQUIRE(BH > 0 && NC > 0 && P > 0 && N > 0, SLX_E_SHAPE, "state_passing_fwd: sizes must be positive");
+  SLX_REQUIRE(BH <= 65535, SLX_E_UNSUPPORTED, "batch_heads=%d exceeds 65535", BH);
+  SLX_REQUIRE(inc && m_chunk && chunk_starts && final_state, SLX_E_NULL, "state_passing_fwd: NULL tensor");
+  return launch_state_fwd(BH, NC, P, N, inc, m_chunk, initial_states, chunk_starts, final_state, as_stream(stream));
+}
+
+int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
+                       const void *C, const float *chunk_starts, const float *B_prev, const float *U_prev, void *Y,
+                       void *stream) {
+  ScanDims d;
+  int rc = check_shape(s, &d);
+  if (rc) return rc;
+  SLX_REQUIRE(U && M && K && B && C && chunk_starts && Y, SLX_E_NULL, "chunk_scan_fwd: NULL tensor");
+  SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
+  SLX_DISPATCH_T(s->dtype, SLX_DISPATCH_L(d.L, rc = (launch_scan_fwd<T_, L_>(d, U, M, K, B, C, chunk_starts, B_prev,
+                                                                             U_prev, Y, as_stream(stream)))));
+  return rc;
+}
+
+int slx_v2x2ssd_fwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
+                    const void *C, const float *initial_states, const float *B_prev, const float *U_prev, void *Y,
+                    float *final_state, float *chunk_starts, float *m_chunk, void *stream) {
+  int rc = slx_chunk_increment_fwd(s, U, M, K, B, B_prev, U_prev, chunk_starts, m_chunk, stream);
+  if (rc) return rc;
+  SLX_REQUIRE(final_state != nullptr, SLX_E_NULL, "v2x2ssd_fwd: final_state is NULL");
+  const int NC = (s->T + s->chunk - 1) / s->chunk;
+  rc = slx_state_passing_fwd(s->batch_heads, NC, s->P, s->N, chunk_starts, m_chunk, initial_states, chunk_starts,
+                             final_state, stream);
+  if (rc) return rc;
+  return slx_chunk_scan_fwd(s, U, M, K, B, C, chunk_starts, B_prev, U_prev, Y, stream);
+}
+
+size_t slx_v2x2ssd_bwd_workspace_bytes(const slx_scan_shape *s) {
+  ScanDims d;
+  if (check_shape(s, &d)) return 0;
+  return bwd_ws(d).total;
+}
+
+int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *C, const void *dY, float *dZ0,
+                           void *stream) {
+  ScanDims d;
+  int rc = check_shape(s, &d);
+  if (rc) return rc;
+  SLX_REQUIRE(M && C && dY && dZ0, SLX_E_NULL, "chunk_scan_bwd_dz0: NULL tensor");
+  SLX_DISPATCH_T(s->dtype, SLX_DISPATCH_L(d.L, rc = (launch_outer<T_, L_, 1>(d, dY, C, M, nullptr, nullptr, nullptr,
+                                                                              dZ0, nullptr, as_stream(stream)))));
+  return rc;
+}
+
+int slx_state_passing_bwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const float *dZ0, const float *m_chunk,
+                          const float *chunk_starts, const float *final_state, const float *d_final, float *d_inc,
+                          float *d_initial, float *zdot, float *zdot_partials, void *stream) {
+  SLX_REQUIRE(BH > 0 && NC > 0 && P > 0 && N > 0, SLX_E_SHAPE, "state_passing_bwd: sizes must be positive");
+  SLX_REQUIRE(BH <= 65535, SLX_E_UNSUPPORTED, "batch_heads=%d exceeds 65535", BH);
+  SLX_REQUIRE(dZ0 && m_chunk && chunk_starts && final_state && d_inc && zdot && zdot_partials, SLX_E_NULL,
+              "state_passing_bwd: NULL tensor");
+  return launch_state_bwd(BH, NC, P, N, dZ0, m_chunk, chunk_starts, final_state, d_final, d_inc, d_initial, zdot,
+                          zdot_partials, as_stream(stream));
+}
+
+int slx_v2x2ssd_bwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
+                    const void *C, const float *B_prev, const float *U_prev, const float *chunk_starts,
+                    const float *m_chunk, const float *final_state, const void *dY, const float *d_final, void *dU,
+                    float *dM, float *dK, void *dB, void *dC, float *d_initial, float *dB_prev, float *dU_prev,
+                    void *workspace, size_t workspace_bytes, void *stream) {
+  ScanDims d;
+  int rc = check_shape(s, &d);
+  if (rc) return rc;
+  SLX_REQUIRE(U && M && K && B && C && chunk_starts && m_chunk && final_state && dY && dU && dM && dK && dB && dC,
+              SLX_E_NULL, "v2x2ssd_bwd: NULL tensor");
+  SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
+  const BwdWs w = bwd_ws(d);
+  SLX_REQUIRE(workspace != nullptr && workspace_bytes >= w.total, SLX_E_WORKSPACE,
+              "v2x2ssd_bwd: workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
+  SLX_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, SLX_E_WORKSPACE,
+              "v2x2ssd_bwd: workspace must be 256-byte aligned");
+  char *base = static_cast<char *>(workspace);
+  float *d_inc = reinterpret_cast<float *>(base + w.d_inc);
+  float *zdot = reinterpret_cast<float *>(base + w.zdot);
+  float *partials = reinterpret_cast<float *>(base + w.partials);
+  float *carryB = reinterpret_cast<float *>(base + w.carryB);
+  float *carryU = reinterpret_cast<float *>(base + w.carryU);
+  cudaStream_t st = as_stream(stream);
+
+  rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, d_inc, stream);
+  if (rc) return rc;
+  rc = launch_state_bwd(d.BH, d.NC, d.P, d.N, d_inc, m_chunk, chunk_starts, final_state, d_final, d_inc, d_initial,
+                        zdot, partials, st);
+  if (rc) return rc;
+  SLX_DISPATCH_T(s->dtype, {
+    ScanBwdArgs<T_> a{(const T_ *)U, (const T_ *)B, (const T_ *)C, (const T_ *)dY, M, K, chunk_starts, d_inc, zdot,
+                      B_prev, U_prev, (T_ *)dU, (T_ *)dB, (T_ *)dC, dM, dK, carryB, carryU, d};
+    SLX_DISPATCH_L(d.L, rc = (launch_scan_bwd<T_, L_>(d, a, st)));
+    if (rc) return rc;
+    carry_fixup_kernel<T_><<<dim3(d.NC, d.BH), 128, 0, st>>>(carryB, carryU, (T_ *)dB, (T_ *)dU, dB_prev, dU_prev,
+                                                              d.T, d.P, d.D, d.L, d.NC);
+    rc = check_launch("carry_fixup");
+  });
+  return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,111 @@
+// Shared device/host helpers for the sm_100a scan kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/slinoss_b200.h"
+
+namespace slx {
+
+// ---- host-side status plumbing --------------------------------------------
+void set_error(const char *fmt, ...);
+int fail(int code, const char *fmt, ...);
+int check_launch(const char *what);  // cudaGetLastError -> status
+
+#define SLX_REQUIRE(cond, code, ...)            \
+  do {                                          \
+    if (!(cond)) return ::slx::fail(code, __VA_ARGS__); \
+  } while (0)
+
+inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// ---- element access in the activation dtype ---------------------------------
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+
+// ---- complex numbers as float2 ------------------------------------------------
+__device__ __forceinline__ float2 cmul(float2 a, float2 b) {
+  return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
+}
+__device__ __forceinline__ float2 cmulc(float2 a, float2 b) {  // a * conj(b)
+  return make_float2(a.x * b.x + a.y * b.y, a.y * b.x - a.x * b.y);
+}
+__device__ __forceinline__ float2 cconj(float2 a) { return make_float2(a.x, -a.y); }
+__device__ __forceinline__ float2 cadd(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
+__device__ __forceinline__ float2 csub(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
+__device__ __forceinline__ float2 cscale(float2 a, float s) { return make_float2(a.x * s, a.y * s); }
+
+// Per-chunk transition prefix in the stable split form of the reference
+// (slinoss/ops/v2x2ssd/reference.py:466-491): lp[t] = sum_{tau<=t} log|m_tau|,
+// ph[t] = normalised prod_{tau<=t} m_tau/|m_tau|.  Tokens >= valid act as m = 1.
+// Executed by warp 0 of the CTA; results land in shared memory (lp, ph of
+// length L) and the caller synchronises.  An exactly-zero |m| sets *bad_flag.
+__device__ __forceinline__ void chunk_prefix_warp0(const float *__restrict__ Mchunk, int L, int valid,
+                                                   float *lp, float2 *ph, float2 *mraw, int *bad_flag) {
+  const int lane = threadIdx.x & 31;
+  if ((threadIdx.x >> 5) != 0) return;
+  const int per = (L + 31) / 32;
+  const int t0 = lane * per;
+  float lsum = 0.f;
+  float2 psum = make_float2(1.f, 0.f);
+  for (int i = 0; i < per; ++i) {
+    int t = t0 + i;
+    if (t < L) {
+      float2 m = make_float2(1.f, 0.f);
+      if (t < valid) m = *reinterpret_cast<const float2 *>(Mchunk + 2 * (size_t)t);
+      float mag = hypotf(m.x, m.y);
+      if (mag == 0.f) {
+        if (bad_flag) atomicExch(bad_flag, 1);
+        mag = 1.f;
+        m = make_float2(1.f, 0.f);
+      }
+      mraw[t] = m;
+      lsum += logf(mag);
+      float inv = 1.f / mag;
+      psum = cmul(psum, make_float2(m.x * inv, m.y * inv));
+      lp[t] = lsum;
+      ph[t] = psum;
+    }
+  }
+  // exclusive scan of the per-lane totals
+  float lincl = lsum;
+  float2 pincl = psum;
+  for (int off = 1; off < 32; off <<= 1) {
+    float lo = __shfl_up_sync(0xffffffffu, lincl, off);
+    float px = __shfl_up_sync(0xffffffffu, pincl.x, off);
+    float py = __shfl_up_sync(0xffffffffu, pincl.y, off);
+    if (lane >= off) {
+      lincl += lo;
+      pincl = cmul(pincl, make_float2(px, py));
+    }
+  }
+  float lex = __shfl_up_sync(0xffffffffu, lincl, 1);
+  float pex_x = __shfl_up_sync(0xffffffffu, pincl.x, 1);
+  float pex_y = __shfl_up_sync(0xffffffffu, pincl.y, 1);
+  if (lane == 0) {
+    lex = 0.f;
+    pex_x = 1.f;
+    pex_y = 0.f;
+  }
+  for (int i = 0; i < per; ++i) {
+    int t = t0 + i;
+    if (t < L) {
+      float2 p = cmul(ph[t], make_float2(pex_x, pex_y));
+      float inv = rsqrtf(p.x * p.x + p.y * p.y);
+      ph[t] = make_float2(p.x * inv, p.y * inv);
+      lp[t] += lex;
+    }
+  }
+}
+
+}  // namespace slx

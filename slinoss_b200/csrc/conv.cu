@@ -1,0 +1,380 @@
+// Depthwise causal conv1d (widths 2..4) on channel-last activations for sm_100a.
+//
+// y[b,t,c] = bias[c] + sum_j w[c,j] * cat[b, t+j, c],  cat = [state (W-1), x]
+// (slinoss/layers/mixer.py:420-454; cross-correlation as F.conv1d).  The input
+// may be a column slice of a wider row-major matrix (row stride > channels),
+// which is how the mixer hands over the value slice of its input projection, so
+// no contiguous copy or transpose is ever made.
+//
+// One thread owns VEC adjacent channels (one 16-byte vector for half types) and
+// walks a tile of tokens with the last three inputs in registers: one vector
+// load and one vector store per channel-vector-token, i.e. the algorithmic
+// 4 bytes per channel-token forward and 6 backward for half types.
+#include <initializer_list>
+
+#include "common.cuh"
+
+namespace slx {
+
+constexpr int kConvThreads = 128;
+
+template <typename T, int VEC>
+__device__ __forceinline__ void ldv(const T *p, float (&v)[VEC]) {
+  if constexpr (VEC * sizeof(T) == 16) {
+    uint4 raw = *reinterpret_cast<const uint4 *>(p);
+    const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] = to_f(e[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] = to_f(p[i]);
+  }
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void stv(T *p, const float (&v)[VEC]) {
+  if constexpr (VEC * sizeof(T) == 16) {
+    uint4 raw;
+    T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) e[i] = from_f<T>(v[i]);
+    *reinterpret_cast<uint4 *>(p) = raw;
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) p[i] = from_f<T>(v[i]);
+  }
+}
+
+struct ConvDims {
+  int batch, T, C, W, silu;
+  long long xs, xbs;  // row stride / batch stride of x (elements)
+};
+
+// x at token index tau (may be negative: reads the carried state, else zero)
+template <typename T, int VEC>
+__device__ __forceinline__ void load_cat(const T *x, const T *state, const ConvDims &d, int b, int tau, int c0,
+                                         float (&v)[VEC]) {
+  if (tau >= 0) {
+    ldv<T, VEC>(x + (long long)b * d.xbs + (long long)tau * d.xs + c0, v);
+  } else {
+    int i = tau + (d.W - 1);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+      v[e] = (state && i >= 0) ? to_f(state[((long long)b * d.C + c0 + e) * (d.W - 1) + i]) : 0.f;
+  }
+}
+
+// taps right-aligned into a window of four: w4[k] multiplies x[t-3+k]
+template <typename T, int VEC>
+__device__ __forceinline__ void load_taps(const T *weight, const T *bias, const ConvDims &d, int c0,
+                                          float (&w4)[4][VEC], float (&bv)[VEC]) {
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      int j = k - (4 - d.W);
+      w4[k][e] = (j >= 0) ? to_f(weight[(long long)(c0 + e) * d.W + j]) : 0.f;
+    }
+    bv[e] = bias ? to_f(bias[c0 + e]) : 0.f;
+  }
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kConvThreads) cconv1d_fwd_kernel(const T *__restrict__ x,
+                                                                   const T *__restrict__ weight,
+                                                                   const T *__restrict__ bias,
+                                                                   const T *__restrict__ state, T *__restrict__ y,
+                                                                   T *__restrict__ next_state, ConvDims d, int tile) {
+  const int c0 = (blockIdx.x * kConvThreads + threadIdx.x) * VEC;
+  if (c0 >= d.C) return;
+  const int b = blockIdx.z;
+  const int t_lo = blockIdx.y * tile, t_hi = min(d.T, t_lo + tile);
+  float w4[4][VEC], bv[VEC];
+  load_taps<T, VEC>(weight, bias, d, c0, w4, bv);
+  float x0[VEC], x1[VEC], x2[VEC], x3[VEC];
+  load_cat<T, VEC>(x, state, d, b, t_lo - 3, c0, x0);
+  load_cat<T, VEC>(x, state, d, b, t_lo - 2, c0, x1);
+  load_cat<T, VEC>(x, state, d, b, t_lo - 1, c0, x2);
+  for (int t = t_lo; t < t_hi; ++t) {
+    ldv<T, VEC>(x + (long long)b * d.xbs + (long long)t * d.xs + c0, x3);
+    float o[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      float acc = bv[e];
+      acc = fmaf(w4[0][e], x0[e], acc);
+      acc = fmaf(w4[1][e], x1[e], acc);
+      acc = fmaf(w4[2][e], x2[e], acc);
+      acc = fmaf(w4[3][e], x3[e], acc);
+      if (d.silu) acc = acc / (1.f + expf(-acc));
+      o[e] = acc;
+      x0[e] = x1[e];
+      x1[e] = x2[e];
+      x2[e] = x3[e];
+    }
+    stv<T, VEC>(y + ((long long)b * d.T + t) * d.C + c0, o);
+  }
+  if (next_state && t_hi == d.T) {
+    for (int i = 0; i < d.W - 1; ++i) {
+      float v[VEC];
+      load_cat<T, VEC>(x, state, d, b, d.T - (d.W - 1) + i, c0, v);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e)
+        next_state[((long long)b * d.C + c0 + e) * (d.W - 1) + i] = from_f<T>(v[e]);
+    }
+  }
+}
+
+// dy with the SiLU derivative folded in (recomputes the pre-activation)
+template <typename T, int VEC>
+__device__ __forceinline__ void load_dyact(const T *dy, const ConvDims &d, int b, int t, int c0,
+                                           const float (&w4)[4][VEC], const float (&bv)[VEC], const float (&xa)[VEC],
+                                           const float (&xb)[VEC], const float (&xc)[VEC], const float (&xd)[VEC],
+                                           float (&g)[VEC]) {
+  if (t >= d.T) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) g[e] = 0.f;
+    return;
+  }
+  ldv<T, VEC>(dy + ((long long)b * d.T + t) * d.C + c0, g);
+  if (d.silu) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      float pre = bv[e];
+      pre = fmaf(w4[0][e], xa[e], pre);
+      pre = fmaf(w4[1][e], xb[e], pre);
+      pre = fmaf(w4[2][e], xc[e], pre);
+      pre = fmaf(w4[3][e], xd[e], pre);
+      float s = 1.f / (1.f + expf(-pre));
+      g[e] *= s * (1.f + pre * (1.f - s));
+    }
+  }
+}
+
+// part[(b*n_tiles + tile)][C][5] = (dw4[0..3], dbias) partial sums of this tile
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_kernel(
+    const T *__restrict__ x, const T *__restrict__ weight, const T *__restrict__ bias, const T *__restrict__ state,
+    const T *__restrict__ dy, const T *__restrict__ d_next, T *__restrict__ dx, float *__restrict__ dstate,
+    float *__restrict__ part, ConvDims d, int tile) {
+  const int c0 = (blockIdx.x * kConvThreads + threadIdx.x) * VEC;
+  if (c0 >= d.C) return;
+  const int b = blockIdx.z;
+  const int t_lo = blockIdx.y * tile, t_hi = min(d.T, t_lo + tile);
+  float w4[4][VEC], bv[VEC];
+  load_taps<T, VEC>(weight, bias, d, c0, w4, bv);
+  float x0[VEC], x1[VEC], x2[VEC], x3[VEC];
+  load_cat<T, VEC>(x, state, d, b, t_lo - 3, c0, x0);
+  load_cat<T, VEC>(x, state, d, b, t_lo - 2, c0, x1);
+  load_cat<T, VEC>(x, state, d, b, t_lo - 1, c0, x2);
+  float g0[VEC], g1[VEC], g2[VEC], g3[VEC];  // dyact[t-3..t]
+  float dw[4][VEC], db[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    g0[e] = g1[e] = g2[e] = 0.f;
+    db[e] = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) dw[k][e] = 0.f;
+  }
+  const int t_end = min(d.T + 3, t_hi + 3);
+  for (int t = t_lo; t < t_end; ++t) {
+    if (t < d.T) ldv<T, VEC>(x + (long long)b * d.xbs + (long long)t * d.xs + c0, x3);
+    load_dyact<T, VEC>(dy, d, b, t, c0, w4, bv, x0, x1, x2, x3, g3);
+    if (t < t_hi) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        dw[0][e] = fmaf(g3[e], x0[e], dw[0][e]);
+        dw[1][e] = fmaf(g3[e], x1[e], dw[1][e]);
+        dw[2][e] = fmaf(g3[e], x2[e], dw[2][e]);
+        dw[3][e] = fmaf(g3[e], x3[e], dw[3][e]);
+        db[e] += g3[e];
+      }
+    }
+    const int tau = t - 3;  // dx[tau] = sum_k w4[k] dyact[tau+3-k]
+    if (tau >= t_lo && tau < t_hi) {
+      float o[VEC];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        float acc = w4[0][e] * g3[e];
+        acc = fmaf(w4[1][e], g2[e], acc);
+        acc = fmaf(w4[2][e], g1[e], acc);
+        acc = fmaf(w4[3][e], g0[e], acc);
+        o[e] = acc;
+      }
+      const int i = tau - d.T + (d.W - 1);  // position inside next_state, if any
+      if (d_next && i >= 0) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[e] += to_f(d_next[((long long)b * d.C + c0 + e) * (d.W - 1) + i]);
+      }
+      stv<T, VEC>(dx + ((long long)b * d.T + tau) * d.C + c0, o);
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      x0[e] = x1[e];
+      x1[e] = x2[e];
+      x2[e] = x3[e];
+      g0[e] = g1[e];
+      g1[e] = g2[e];
+      g2[e] = g3[e];
+    }
+  }
+  float *pp = part + (((long long)b * gridDim.y + blockIdx.y) * d.C + c0) * 5;
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) pp[e * 5 + k] = dw[k][e];
+    pp[e * 5 + 4] = db[e];
+  }
+  // gradient of the carried state: cat index i < W-1  <->  x index tau = i-(W-1)
+  if (dstate && blockIdx.y == 0) {
+    // dyact[0..2] recomputed from scratch (tile 0 owns them, but they have been shifted out)
+    float xa[VEC], xb[VEC], xc[VEC], xd[VEC], ga[3][VEC];
+    load_cat<T, VEC>(x, state, d, b, -3, c0, xa);
+    load_cat<T, VEC>(x, state, d, b, -2, c0, xb);
+    load_cat<T, VEC>(x, state, d, b, -1, c0, xc);
+    for (int t = 0; t < 3; ++t) {
+      if (t < d.T) ldv<T, VEC>(x + (long long)b * d.xbs + (long long)t * d.xs + c0, xd);
+      load_dyact<T, VEC>(dy, d, b, t, c0, w4, bv, xa, xb, xc, xd, ga[t]);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        xa[e] = xb[e];
+        xb[e] = xc[e];
+        xc[e] = xd[e];
+      }
+    }
+    for (int i = 0; i < d.W - 1; ++i) {
+      const int tau = i - (d.W - 1);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          int s = tau + 3 - k;
+          if (s >= 0 && s < 3) acc = fmaf(w4[k][e], ga[s][e], acc);
+        }
+        int in = i - d.T;  // next_state index that aliases this state slot when T < W-1
+        if (d_next && in >= 0) acc += to_f(d_next[((long long)b * d.C + c0 + e) * (d.W - 1) + in]);
+        dstate[((long long)b * d.C + c0 + e) * (d.W - 1) + i] = acc;
+      }
+    }
+  }
+}
+
+__global__ void cconv1d_reduce_kernel(const float *__restrict__ part, float *__restrict__ dweight,
+                                      float *__restrict__ dbias, int n_parts, int C, int W) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float acc[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int p = 0; p < n_parts; ++p) {
+    const float *pp = part + ((long long)p * C + c) * 5;
+#pragma unroll
+    for (int k = 0; k < 5; ++k) acc[k] += pp[k];
+  }
+  for (int j = 0; j < W; ++j) dweight[(long long)c * W + j] = acc[j + (4 - W)];
+  if (dbias) dbias[c] = acc[4];
+}
+
+static int check_conv(const slx_conv_shape *s, ConvDims *d) {
+  SLX_REQUIRE(s != nullptr, SLX_E_NULL, "shape is NULL");
+  SLX_REQUIRE(s->batch > 0 && s->T > 0 && s->channels > 0, SLX_E_SHAPE, "cconv1d: sizes must be positive");
+  SLX_REQUIRE(s->width >= 2 && s->width <= 4, SLX_E_UNSUPPORTED, "cconv1d: width %d not in 2..4", s->width);
+  SLX_REQUIRE(s->dtype >= SLX_F32 && s->dtype <= SLX_F16, SLX_E_DTYPE, "cconv1d: bad dtype %d", s->dtype);
+  SLX_REQUIRE(s->x_stride >= s->channels, SLX_E_SHAPE, "cconv1d: x_stride smaller than channels");
+  SLX_REQUIRE(s->batch <= 65535, SLX_E_UNSUPPORTED, "cconv1d: batch exceeds 65535");
+  d->batch = s->batch; d->T = s->T; d->C = s->channels; d->W = s->width; d->silu = s->silu;
+  d->xs = s->x_stride; d->xbs = s->x_batch_stride;
+  return SLX_OK;
+}
+
+static int conv_tile(int T, bool bwd) {
+  int tile = bwd ? 128 : 64;
+  return tile < T ? tile : T;
+}
+
+template <typename T>
+static bool conv_vec_ok(const slx_conv_shape *s, std::initializer_list<const void *> ptrs) {
+  const int v = 16 / (int)sizeof(T);
+  bool ok = (s->channels % v == 0) && (s->x_stride % v == 0) && (s->x_batch_stride % v == 0);
+  for (const void *p : ptrs) ok = ok && (p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0);
+  return ok;
+}
+
+}  // namespace slx
+
+using namespace slx;
+
+#define SLX_CONV_T(dt, ...)                                          \
+  switch (dt) {                                                      \
+    case SLX_F32: { using T_ = float; __VA_ARGS__; } break;          \
+    case SLX_BF16: { using T_ = __nv_bfloat16; __VA_ARGS__; } break; \
+    default: { using T_ = __half; __VA_ARGS__; } break;              \
+  }
+
+extern "C" {
+
+int slx_cconv1d_fwd(const slx_conv_shape *s, const void *x, const void *weight, const void *bias, const void *state,
+                    void *y, void *next_state, void *stream) {
+  ConvDims d;
+  int rc = check_conv(s, &d);
+  if (rc) return rc;
+  SLX_REQUIRE(x && weight && y, SLX_E_NULL, "cconv1d_fwd: NULL tensor");
+  cudaStream_t st = as_stream(stream);
+  const int tile = conv_tile(d.T, false);
+  const int n_tiles = (d.T + tile - 1) / tile;
+  SLX_CONV_T(s->dtype, {
+    constexpr int VFULL = 16 / (int)sizeof(T_);
+    if (conv_vec_ok<T_>(s, {x, y})) {
+      int nvec = d.C / VFULL;
+      cconv1d_fwd_kernel<T_, VFULL><<<dim3((nvec + kConvThreads - 1) / kConvThreads, n_tiles, d.batch), kConvThreads, 0,
+                                      st>>>((const T_ *)x, (const T_ *)weight, (const T_ *)bias, (const T_ *)state,
+                                            (T_ *)y, (T_ *)next_state, d, tile);
+    } else {
+      cconv1d_fwd_kernel<T_, 1><<<dim3((d.C + kConvThreads - 1) / kConvThreads, n_tiles, d.batch), kConvThreads, 0,
+                                  st>>>((const T_ *)x, (const T_ *)weight, (const T_ *)bias, (const T_ *)state,
+                                        (T_ *)y, (T_ *)next_state, d, tile);
+    }
+  });
+  return check_launch("cconv1d_fwd");
+}
+
+size_t slx_cconv1d_bwd_workspace_bytes(const slx_conv_shape *s) {
+  ConvDims d;
+  if (check_conv(s, &d)) return 0;
+  const int tile = conv_tile(d.T, true);
+  const int n_tiles = (d.T + tile - 1) / tile;
+  return sizeof(float) * (size_t)d.batch * n_tiles * d.C * 5;
+}
+
+int slx_cconv1d_bwd(const slx_conv_shape *s, const void *x, const void *weight, const void *bias, const void *state,
+                    const void *dy, const void *d_next_state, void *dx, float *dweight, float *dbias, float *dstate,
+                    void *workspace, size_t workspace_bytes, void *stream) {
+  ConvDims d;
+  int rc = check_conv(s, &d);
+  if (rc) return rc;
+  SLX_REQUIRE(x && weight && dy && dx && dweight, SLX_E_NULL, "cconv1d_bwd: NULL tensor");
+  size_t need = slx_cconv1d_bwd_workspace_bytes(s);
+  SLX_REQUIRE(workspace && workspace_bytes >= need, SLX_E_WORKSPACE, "cconv1d_bwd: workspace of %zu bytes needed",
+              need);
+  cudaStream_t st = as_stream(stream);
+  const int tile = conv_tile(d.T, true);
+  const int n_tiles = (d.T + tile - 1) / tile;
+  float *part = static_cast<float *>(workspace);
+  SLX_CONV_T(s->dtype, {
+    constexpr int VFULL = 16 / (int)sizeof(T_);
+    if (conv_vec_ok<T_>(s, {x, dy, dx})) {
+      int nvec = d.C / VFULL;
+      cconv1d_bwd_kernel<T_, VFULL><<<dim3((nvec + kConvThreads - 1) / kConvThreads, n_tiles, d.batch), kConvThreads, 0,
+                                      st>>>((const T_ *)x, (const T_ *)weight, (const T_ *)bias, (const T_ *)state,
+                                            (const T_ *)dy, (const T_ *)d_next_state, (T_ *)dx, dstate, part, d,
+                                            tile);
+    } else {
+      cconv1d_bwd_kernel<T_, 1><<<dim3((d.C + kConvThreads - 1) / kConvThreads, n_tiles, d.batch), kConvThreads, 0,
+                                  st>>>((const T_ *)x, (const T_ *)weight, (const T_ *)bias, (const T_ *)state,
+                                        (const T_ *)dy, (const T_ *)d_next_state, (T_ *)dx, dstate, part, d, tile);
+    }
+  });
+  rc = check_launch("cconv1d_bwd");
+  if (rc) return rc;
+  cconv1d_reduce_kernel<<<(d.C + 127) / 128, 128, 0, st>>>(part, dweight, dbias, d.batch * n_tiles, d.C, d.W);
+  return check_launch("cconv1d_reduce");
+}
+
+}  // extern "C"

@@ -1,0 +1,638 @@
+// SLinOSSScanPrep forward/backward for sm_100a: bandwidth-bound, one lane group
+// per (batch, head, token) row, 128-bit vector loads/stores, deterministic
+// two-level reductions for the parameter gradients.
+//
+// Forward map (slinoss/layers/scanprep.py:351-357):
+//   U  = value.view(b,T,H,P).permute(0,2,1,3)
+//   B,C = interleave(rms_norm(bc) * scale)       (scanprep.py:297-336)
+//   M,K = coefficient map of the 13-wide params row (scanprep.py:208-286,
+//         ops/scanprep/reference.py:26-57)
+#include <initializer_list>
+
+#include "common.cuh"
+
+namespace slx {
+
+struct PrepHyper {
+  float dt_min, dt_max, r_min, r_max, theta_bound, k_max, z_thr2;
+};
+
+struct CoefOut {
+  float2 rho, kp, kc;
+};
+
+// intermediates kept for the backward
+struct CoefCtx {
+  float dt_u, dt, gamma, omega, e_gdt, r_struct, th_struct, r_dir_u, r_direct, th_t, th_direct;
+  float mix_r, mix_th, mix_kp, mix_kc, tk[4], r, sig_p1;
+  float2 rho, z, k1, k2, kps, kcs, kpl, kcl;
+  bool small;
+};
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+// torch.lerp: a + w (b-a) for w < 0.5, b - (b-a)(1-w) otherwise
+__device__ __forceinline__ float lerpf_(float a, float b, float w) {
+  float d = b - a;
+  return w < 0.5f ? fmaf(w, d, a) : b - d * (1.f - w);
+}
+__device__ __forceinline__ float2 cdiv(float2 a, float2 b) {
+  float inv = 1.f / (b.x * b.x + b.y * b.y);
+  return make_float2((a.x * b.x + a.y * b.y) * inv, (a.y * b.x - a.x * b.y) * inv);
+}
+
+__device__ __forceinline__ CoefOut coef_forward(const float *p, const PrepHyper &h, CoefCtx *ctx) {
+  const float kPi = 3.14159265358979323846f;
+  const float d_dt = h.dt_max - h.dt_min, d_r = h.r_max - h.r_min;
+  float dt_u = sigmoidf_(p[0]);
+  float dt = fmaf(d_dt, dt_u, h.dt_min);
+  float gamma = softplusf_(p[1]);
+  float omega = p[2];
+  float e_gdt = expf(-gamma * dt);
+  float r_struct = fmaf(d_r, e_gdt, h.r_min);
+  float th_struct = omega * dt;
+  float r_dir_u = sigmoidf_(p[3]);
+  float r_direct = fmaf(d_r, r_dir_u, h.r_min);
+  float th_t = tanhf(p[4]);
+  float th_direct = h.theta_bound * th_t;
+  float mix_r = sigmoidf_(p[5]), mix_th = sigmoidf_(p[6]);
+  float mix_kp = sigmoidf_(p[7]), mix_kc = sigmoidf_(p[8]);
+  float tk0 = tanhf(p[9]), tk1 = tanhf(p[10]), tk2 = tanhf(p[11]), tk3 = tanhf(p[12]);
+  float2 kpl = make_float2(h.k_max * tk0, h.k_max * tk1);
+  float2 kcl = make_float2(h.k_max * tk2, h.k_max * tk3);
+  float r = lerpf_(r_direct, r_struct, mix_r);
+  float th_raw = lerpf_(th_direct, th_struct, mix_th);
+  // principal angle in [-pi, pi): remainder(theta + pi, 2 pi) - pi
+  float rem = fmodf(th_raw + kPi, 2.f * kPi);
+  if (rem < 0.f) rem += 2.f * kPi;
+  float theta = rem - kPi;
+  float log_r = logf(r);
+  float sn, cs;
+  sincosf(theta, &sn, &cs);
+  float2 rho = make_float2(r * cs, r * sn);
+  float2 z = make_float2(log_r, theta);
+  bool small = (log_r * log_r + theta * theta) < h.z_thr2;
+  float2 k1, k2;
+  if (small) {
+    float2 z2 = cmul(z, z), z3 = cmul(z2, z);
+    k1 = make_float2(1.f + 0.5f * z.x + z2.x / 6.f + z3.x / 24.f, 0.5f * z.y + z2.y / 6.f + z3.y / 24.f);
+    k2 = make_float2(0.5f + z.x / 3.f + z2.x / 8.f + z3.x / 30.f, z.y / 3.f + z2.y / 8.f + z3.y / 30.f);
+  } else {
+    k1 = cdiv(make_float2(rho.x - 1.f, rho.y), z);
+    float2 num = cmul(rho, make_float2(z.x - 1.f, z.y));
+    num.x += 1.f;
+    k2 = cdiv(num, cmul(z, z));
+  }
+  float2 kps = cscale(k2, dt);
+  float2 kcs = csub(cscale(k1, dt), kps);
+  CoefOut o;
+  o.rho = rho;
+  o.kp = make_float2(lerpf_(kpl.x, kps.x, mix_kp), lerpf_(kpl.y, kps.y, mix_kp));
+  o.kc = make_float2(lerpf_(kcl.x, kcs.x, mix_kc), lerpf_(kcl.y, kcs.y, mix_kc));
+  if (ctx) {
+    ctx->dt_u = dt_u; ctx->dt = dt; ctx->gamma = gamma; ctx->omega = omega; ctx->e_gdt = e_gdt;
+    ctx->r_struct = r_struct; ctx->th_struct = th_struct; ctx->r_dir_u = r_dir_u; ctx->r_direct = r_direct;
+    ctx->th_t = th_t; ctx->th_direct = th_direct; ctx->mix_r = mix_r; ctx->mix_th = mix_th;
+    ctx->mix_kp = mix_kp; ctx->mix_kc = mix_kc; ctx->tk[0] = tk0; ctx->tk[1] = tk1; ctx->tk[2] = tk2;
+    ctx->tk[3] = tk3; ctx->r = r; ctx->sig_p1 = sigmoidf_(p[1]); ctx->rho = rho; ctx->z = z; ctx->k1 = k1;
+    ctx->k2 = k2; ctx->kps = kps; ctx->kcs = kcs; ctx->kpl = kpl; ctx->kcl = kcl; ctx->small = small;
+  }
+  return o;
+}
+
+// VJP of coef_forward: dp[13] from (dM, dKprev, dKcurr)
+__device__ __forceinline__ void coef_backward(const CoefCtx &c, const PrepHyper &h, float2 dm, float2 dkp, float2 dkc,
+                                              float *dp) {
+  const float d_dt = h.dt_max - h.dt_min, d_r = h.r_max - h.r_min;
+  auto rdot = [](float2 a, float2 g) { return a.x * g.x + a.y * g.y; };
+  float2 dkps = cscale(dkp, c.mix_kp), dkpl = cscale(dkp, 1.f - c.mix_kp);
+  float dmix_kp = rdot(csub(c.kps, c.kpl), dkp);
+  float2 dkcs = cscale(dkc, c.mix_kc), dkcl = cscale(dkc, 1.f - c.mix_kc);
+  float dmix_kc = rdot(csub(c.kcs, c.kcl), dkc);
+  float2 dk2 = cscale(csub(dkps, dkcs), c.dt);
+  float2 dk1 = cscale(dkcs, c.dt);
+  float ddt = rdot(c.k2, dkps) + rdot(csub(c.k1, c.k2), dkcs);
+  float2 k1p, k2p;
+  const float2 z = c.z;
+  if (c.small) {
+    float2 z2 = cmul(z, z);
+    k1p = make_float2(0.5f + z.x / 3.f + z2.x / 8.f, z.y / 3.f + z2.y / 8.f);
+    k2p = make_float2(1.f / 3.f + z.x / 4.f + z2.x / 10.f, z.y / 4.f + z2.y / 10.f);
+  } else {
+    k1p = c.k2;                                              // d/dz (e^z-1)/z
+    k2p = cdiv(csub(c.rho, cscale(c.k2, 2.f)), z);           // d/dz (e^z(z-1)+1)/z^2
+  }
+  // dz = conj(k1') dk1 + conj(k2') dk2 + conj(rho) dM
+  float2 dz = cadd(cadd(cmul(cconj(k1p), dk1), cmul(cconj(k2p), dk2)), cmul(cconj(c.rho), dm));
+  float dr = dz.x / c.r;
+  float dtheta = dz.y;
+  float dth_d = (1.f - c.mix_th) * dtheta, dth_s = c.mix_th * dtheta;
+  float dmix_th = (c.th_struct - c.th_direct) * dtheta;
+  float dr_d = (1.f - c.mix_r) * dr, dr_s = c.mix_r * dr;
+  float dmix_r = (c.r_struct - c.r_direct) * dr;
+  float dgamma = dr_s * d_r * c.e_gdt * (-c.dt);
+  ddt += dr_s * d_r * c.e_gdt * (-c.gamma);
+  float domega = dth_s * c.dt;
+  ddt += dth_s * c.omega;
+  auto dsig = [](float s) { return s * (1.f - s); };
+  dp[0] = ddt * d_dt * dsig(c.dt_u);
+  dp[1] = dgamma * c.sig_p1;
+  dp[2] = domega;
+  dp[3] = dr_d * d_r * dsig(c.r_dir_u);
+  dp[4] = dth_d * h.theta_bound * (1.f - c.th_t * c.th_t);
+  dp[5] = dmix_r * dsig(c.mix_r);
+  dp[6] = dmix_th * dsig(c.mix_th);
+  dp[7] = dmix_kp * dsig(c.mix_kp);
+  dp[8] = dmix_kc * dsig(c.mix_kc);
+  dp[9] = h.k_max * (1.f - c.tk[0] * c.tk[0]) * dkpl.x;
+  dp[10] = h.k_max * (1.f - c.tk[1] * c.tk[1]) * dkpl.y;
+  dp[11] = h.k_max * (1.f - c.tk[2] * c.tk[2]) * dkcl.x;
+  dp[12] = h.k_max * (1.f - c.tk[3] * c.tk[3]) * dkcl.y;
+}
+
+// ---- vector access ------------------------------------------------------------
+template <typename T, int VEC>
+__device__ __forceinline__ void load_vec(const T *p, float (&v)[VEC]) {
+  if constexpr (VEC * sizeof(T) == 16) {
+    uint4 raw = *reinterpret_cast<const uint4 *>(p);
+    const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] = to_f(e[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] = to_f(p[i]);
+  }
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void store_vec(T *p, const float (&v)[VEC]) {
+  if constexpr (VEC * sizeof(T) == 16) {
+    uint4 raw;
+    T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) e[i] = from_f<T>(v[i]);
+    *reinterpret_cast<uint4 *>(p) = raw;
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) p[i] = from_f<T>(v[i]);
+  }
+}
+
+template <int G>
+__device__ __forceinline__ float group_sum_f(float v) {
+#pragma unroll
+  for (int off = G / 2; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
+struct PrepDims {
+  int batch, T, H, P, N;
+  int normalize;
+  long long vs, ps, bs;  // row strides (elements)
+};
+
+// Rows are ordered (b, h, t) so that a CTA's consecutive rows write contiguous
+// output.  A group of G lanes handles one row; lane q of the group owns the
+// state lanes n in [VEC*(q + G*k), VEC*(q + G*k) + VEC).
+template <typename T, int VEC, int G>
+__global__ void __launch_bounds__(256) scanprep_fwd_kernel(const T *__restrict__ value, const T *__restrict__ params,
+                                                           const T *__restrict__ bc, const float *__restrict__ bias,
+                                                           const float *__restrict__ scale, T *__restrict__ U,
+                                                           float *__restrict__ M, float *__restrict__ K,
+                                                           T *__restrict__ Bo, T *__restrict__ Co, PrepDims d,
+                                                           PrepHyper hp) {
+  constexpr int GPB = 256 / G;  // rows per CTA pass
+  const int q = threadIdx.x % G;
+  const int grp = threadIdx.x / G;
+  const long long n_rows = (long long)d.batch * d.H * d.T;
+  const int D = 2 * d.N;
+  for (long long row0 = (long long)blockIdx.x * GPB; row0 < n_rows; row0 += (long long)gridDim.x * GPB) {
+    const long long row = row0 + grp;
+    const bool live = row < n_rows;
+    const long long rr = live ? row : 0;
+    const int t = (int)(rr % d.T);
+    const int h = (int)((rr / d.T) % d.H);
+    const int b = (int)(rr / ((long long)d.T * d.H));
+    const long long in_row = (long long)b * d.T + t;
+    // ---- U: copy P values ----
+    if (live) {
+      const T *src = value + in_row * d.vs + (long long)h * d.P;
+      T *dst = U + rr * d.P;
+      for (int p0 = q * VEC; p0 < d.P; p0 += G * VEC) {
+        float v[VEC];
+        load_vec<T, VEC>(src + p0, v);
+        store_vec<T, VEC>(dst + p0, v);
+      }
+    }
+    // ---- B, C ----
+    const T *bcr = bc + in_row * d.bs + (long long)h * 4 * d.N;
+    float ss[4] = {0.f, 0.f, 0.f, 0.f};
+    if (d.normalize) {
+      if (live) {
+        for (int n0 = q * VEC; n0 < d.N; n0 += G * VEC) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float v[VEC];
+            load_vec<T, VEC>(bcr + j * d.N + n0, v);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) ss[j] = fmaf(v[i], v[i], ss[j]);
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ss[j] = rsqrtf(group_sum_f<G>(ss[j]) / (float)d.N + 1e-5f);
+    }
+    if (live) {
+      for (int n0 = q * VEC; n0 < d.N; n0 += G * VEC) {
+        float y[4][VEC];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          load_vec<T, VEC>(bcr + j * d.N + n0, y[j]);
+          if (d.normalize) {
+            const float *sc = scale + ((long long)h * 4 + j) * d.N + n0;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) y[j][i] = (y[j][i] * ss[j]) * sc[i];
+          }
+        }
+        float ob[2][VEC], oc[2][VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          int o = 2 * i;
+          ob[o / VEC][o % VEC] = y[0][i];
+          ob[(o + 1) / VEC][(o + 1) % VEC] = y[1][i];
+          oc[o / VEC][o % VEC] = y[2][i];
+          oc[(o + 1) / VEC][(o + 1) % VEC] = y[3][i];
+        }
+        store_vec<T, VEC>(Bo + rr * D + 2 * n0, ob[0]);
+        store_vec<T, VEC>(Bo + rr * D + 2 * n0 + VEC, ob[1]);
+        store_vec<T, VEC>(Co + rr * D + 2 * n0, oc[0]);
+        store_vec<T, VEC>(Co + rr * D + 2 * n0 + VEC, oc[1]);
+      }
+    }
+    // ---- M, K ----
+    if (live && q == 0) {
+      float p[13];
+      const T *pr = params + in_row * d.ps + (long long)h * 13;
+#pragma unroll
+      for (int i = 0; i < 13; ++i) p[i] = to_f(pr[i]) + bias[h * 13 + i];
+      CoefOut o = coef_forward(p, hp, nullptr);
+      *reinterpret_cast<float2 *>(M + rr * 2) = o.rho;
+      *reinterpret_cast<float4 *>(K + rr * 4) = make_float4(o.kp.x, o.kp.y, o.kc.x, o.kc.y);
+    }
+  }
+}
+
+// Backward.  grid = (tiles over T, batch*H): every CTA works on one head, so the
+// per-head parameter gradients reduce inside the CTA first (registers ->
+// shared memory in a fixed order) and then across CTAs in a second kernel.
+// Partial layout: part[(bh * n_tiles + tile)][4*N + 13].
+template <typename T, int VEC, int G, int KMAX>
+__global__ void __launch_bounds__(256) scanprep_bwd_kernel(const T *__restrict__ params, const T *__restrict__ bc,
+                                                           const float *__restrict__ bias,
+                                                           const float *__restrict__ scale, const T *__restrict__ dU,
+                                                           const float *__restrict__ dM, const float *__restrict__ dK,
+                                                           const T *__restrict__ dB, const T *__restrict__ dC,
+                                                           T *__restrict__ d_value, T *__restrict__ d_params,
+                                                           T *__restrict__ d_bc, float *__restrict__ part, PrepDims d,
+                                                           PrepHyper hp, int rows_per_tile) {
+  constexpr int GPB = 256 / G;  // KMAX sweeps of VEC*G state lanes cover N
+  extern __shared__ float red[];  // GPB * (4N + 13)
+  const int q = threadIdx.x % G, grp = threadIdx.x / G;
+  const int bh = blockIdx.y, b = bh / d.H, h = bh % d.H;
+  const int D = 2 * d.N;
+  const int W = 4 * d.N + 13;
+  const int t_lo = blockIdx.x * rows_per_tile;
+  const int t_hi = min(d.T, t_lo + rows_per_tile);
+
+  float dsc[KMAX][4][VEC];
+#pragma unroll
+  for (int k = 0; k < KMAX; ++k)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) dsc[k][j][i] = 0.f;
+  float dbias[13];
+#pragma unroll
+  for (int i = 0; i < 13; ++i) dbias[i] = 0.f;
+
+  for (int tb = t_lo; tb < t_hi; tb += GPB) {
+    const int t = tb + grp;
+    const bool live = t < t_hi;
+    const int tt = live ? t : t_lo;
+    const long long in_row = (long long)b * d.T + tt;
+    const long long orow = ((long long)bh) * d.T + tt;
+    if (live) {
+      const T *src = dU + orow * d.P;
+      T *dst = d_value + in_row * ((long long)d.H * d.P) + (long long)h * d.P;
+      for (int p0 = q * VEC; p0 < d.P; p0 += G * VEC) {
+        float v[VEC];
+        load_vec<T, VEC>(src + p0, v);
+        store_vec<T, VEC>(dst + p0, v);
+      }
+    }
+    const T *bcr = bc + in_row * d.bs + (long long)h * 4 * d.N;
+    T *dbcr = d_bc + in_row * ((long long)d.H * 4 * d.N) + (long long)h * 4 * d.N;
+    float ss[4] = {0.f, 0.f, 0.f, 0.f}, gx[4] = {0.f, 0.f, 0.f, 0.f};
+    if (d.normalize) {
+      if (live) {
+        int k = 0;
+        for (int n0 = q * VEC; n0 < d.N; n0 += G * VEC, ++k) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float v[VEC];
+            load_vec<T, VEC>(bcr + j * d.N + n0, v);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) ss[j] = fmaf(v[i], v[i], ss[j]);
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ss[j] = rsqrtf(group_sum_f<G>(ss[j]) / (float)d.N + 1e-5f);
+    }
+    // second sweep: dy (de-interleaved), dscale, sum g*xhat
+    float xh[KMAX][4][VEC], gg[KMAX][4][VEC];
+    {
+      int k = 0;
+      for (int n0 = q * VEC; n0 < d.N && k < KMAX; n0 += G * VEC, ++k) {
+        float ib[2][VEC], ic[2][VEC];
+        if (live) {
+          load_vec<T, VEC>(dB + orow * D + 2 * n0, ib[0]);
+          load_vec<T, VEC>(dB + orow * D + 2 * n0 + VEC, ib[1]);
+          load_vec<T, VEC>(dC + orow * D + 2 * n0, ic[0]);
+          load_vec<T, VEC>(dC + orow * D + 2 * n0 + VEC, ic[1]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float x[VEC];
+          if (live) load_vec<T, VEC>(bcr + j * d.N + n0, x);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) {
+            int o = 2 * i + (j & 1);
+            float dy = 0.f;
+            if (live) dy = (j < 2) ? ib[o / VEC][o % VEC] : ic[o / VEC][o % VEC];
+            if (d.normalize) {
+              float xv = live ? x[i] * ss[j] : 0.f;
+              float g = dy * scale[((long long)h * 4 + j) * d.N + n0 + i];
+              xh[k][j][i] = xv;
+              gg[k][j][i] = g;
+              dsc[k][j][i] = fmaf(dy, xv, dsc[k][j][i]);
+              gx[j] = fmaf(g, xv, gx[j]);
+            } else {
+              gg[k][j][i] = dy;
+            }
+          }
+        }
+      }
+    }
+    if (d.normalize) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) gx[j] = group_sum_f<G>(gx[j]) / (float)d.N;
+    }
+    if (live) {
+      int k = 0;
+      for (int n0 = q * VEC; n0 < d.N && k < KMAX; n0 += G * VEC, ++k) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float o[VEC];
+#pragma unroll
+          for (int i = 0; i < VEC; ++i)
+            o[i] = d.normalize ? ss[j] * (gg[k][j][i] - xh[k][j][i] * gx[j]) : gg[k][j][i];
+          store_vec<T, VEC>(dbcr + j * d.N + n0, o);
+        }
+      }
+    }
+    // coefficient map VJP (one lane per row)
+    if (live && q == 0) {
+      float p[13], dp[13];
+      const T *pr = params + in_row * d.ps + (long long)h * 13;
+#pragma unroll
+      for (int i = 0; i < 13; ++i) p[i] = to_f(pr[i]) + bias[h * 13 + i];
+      CoefCtx ctx;
+      coef_forward(p, hp, &ctx);
+      float2 dm = *reinterpret_cast<const float2 *>(dM + orow * 2);
+      float4 dk = *reinterpret_cast<const float4 *>(dK + orow * 4);
+      coef_backward(ctx, hp, dm, make_float2(dk.x, dk.y), make_float2(dk.z, dk.w), dp);
+      T *dpr = d_params + in_row * ((long long)d.H * 13) + (long long)h * 13;
+#pragma unroll
+      for (int i = 0; i < 13; ++i) {
+        dpr[i] = from_f<T>(dp[i]);
+        dbias[i] += dp[i];
+      }
+    }
+  }
+  // ---- CTA-level reduction in a fixed order ----
+  {
+    float *mine = red + (size_t)grp * W;
+    if (d.normalize) {
+      int k = 0;
+      for (int n0 = q * VEC; n0 < d.N && k < KMAX; n0 += G * VEC, ++k)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) mine[j * d.N + n0 + i] = dsc[k][j][i];
+    }
+    if (q == 0)
+#pragma unroll
+      for (int i = 0; i < 13; ++i) mine[4 * d.N + i] = dbias[i];
+  }
+  __syncthreads();
+  float *outp = part + ((size_t)bh * gridDim.x + blockIdx.x) * W;
+  for (int e = threadIdx.x; e < W; e += 256) {
+    if (!d.normalize && e < 4 * d.N) {
+      outp[e] = 0.f;
+      continue;
+    }
+    float acc = 0.f;
+    for (int g = 0; g < GPB; ++g) acc += red[(size_t)g * W + e];
+    outp[e] = acc;
+  }
+}
+
+// d_scale[h][e], d_bias[h][i] = sum over batch and tiles of the partials, fixed order
+__global__ void scanprep_reduce_kernel(const float *__restrict__ part, float *__restrict__ d_bias,
+                                       float *__restrict__ d_scale, int batch, int H, int n_tiles, int N) {
+  const int W = 4 * N + 13;
+  const int h = blockIdx.y;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= W) return;
+  float acc = 0.f;
+  for (int b = 0; b < batch; ++b)
+    for (int tile = 0; tile < n_tiles; ++tile) acc += part[((size_t)(b * H + h) * n_tiles + tile) * W + e];
+  if (e < 4 * N) {
+    if (d_scale) d_scale[(size_t)h * 4 * N + e] = acc;
+  } else {
+    d_bias[h * 13 + (e - 4 * N)] = acc;
+  }
+}
+
+static PrepHyper make_hyper(const slx_prep_shape *s) {
+  PrepHyper h;
+  h.dt_min = s->dt_min; h.dt_max = s->dt_max; h.r_min = s->r_min; h.r_max = s->r_max;
+  h.theta_bound = s->theta_bound; h.k_max = s->k_max;
+  float e = s->eps > 1e-12f ? s->eps : 1e-12f;
+  float thr = sqrtf(e);
+  if (thr < 1e-4f) thr = 1e-4f;
+  h.z_thr2 = thr * thr;
+  return h;
+}
+
+static int check_prep(const slx_prep_shape *s, PrepDims *d) {
+  SLX_REQUIRE(s != nullptr, SLX_E_NULL, "shape is NULL");
+  SLX_REQUIRE(s->batch > 0 && s->T > 0 && s->heads > 0 && s->P > 0 && s->N > 0, SLX_E_SHAPE,
+              "scanprep: sizes must be positive");
+  SLX_REQUIRE(s->dtype >= SLX_F32 && s->dtype <= SLX_F16, SLX_E_DTYPE, "scanprep: bad dtype %d", s->dtype);
+  SLX_REQUIRE(s->value_stride >= (int64_t)s->heads * s->P && s->params_stride >= (int64_t)s->heads * 13 &&
+                  s->bc_stride >= (int64_t)s->heads * 4 * s->N,
+              SLX_E_SHAPE, "scanprep: row stride smaller than the row width");
+  SLX_REQUIRE((long long)s->batch * s->heads <= 65535, SLX_E_UNSUPPORTED, "scanprep: batch*heads exceeds 65535");
+  d->batch = s->batch; d->T = s->T; d->H = s->heads; d->P = s->P; d->N = s->N;
+  d->normalize = s->normalize_bc;
+  d->vs = s->value_stride; d->ps = s->params_stride; d->bs = s->bc_stride;
+  return SLX_OK;
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// vector width (elements) usable for this problem: 16-byte vectors when every
+// row start and row width is 16-byte aligned, else scalar
+template <typename T>
+static int pick_vec(const slx_prep_shape *s, std::initializer_list<const void *> ptrs) {
+  const int v = 16 / (int)sizeof(T);
+  bool ok = (s->N % v == 0) && (s->P % v == 0) && (s->value_stride % v == 0) && (s->bc_stride % v == 0);
+  for (const void *p : ptrs) ok = ok && (p == nullptr || aligned16(p));
+  return ok ? v : 1;
+}
+
+// lane-group width: 16 lanes x 16-byte vectors cover N = 128 half values in one
+// sweep; the scalar mapping uses a full warp per row
+template <int VEC>
+constexpr int prep_group() { return VEC == 1 ? 32 : 16; }
+
+template <typename T, int VEC>
+static int launch_prep_fwd(const slx_prep_shape *s, const PrepDims &d, const void *value, const void *params,
+                           const void *bc, const float *bias, const float *scale, void *U, float *M, float *K,
+                           void *B, void *C, cudaStream_t st) {
+  PrepHyper hp = make_hyper(s);
+  constexpr int G = prep_group<VEC>();
+  long long n_rows = (long long)d.batch * d.H * d.T;
+  long long blocks = (n_rows + (256 / G) - 1) / (256 / G);
+  if (blocks > 148LL * 64) blocks = 148LL * 64;
+  scanprep_fwd_kernel<T, VEC, G><<<(unsigned)blocks, 256, 0, st>>>(
+      (const T *)value, (const T *)params, (const T *)bc, bias, scale, (T *)U, M, K, (T *)B, (T *)C, d, hp);
+  return check_launch("scanprep_fwd");
+}
+
+struct PrepBwdPlan {
+  int G, kmax, rows_per_tile, n_tiles;
+  size_t smem, ws_bytes;
+};
+
+static PrepBwdPlan prep_bwd_plan(const slx_prep_shape *s, int VEC) {
+  PrepBwdPlan p;
+  p.G = VEC == 1 ? 32 : 16;
+  p.kmax = (s->N + VEC * p.G - 1) / (VEC * p.G);
+  p.rows_per_tile = 256;
+  p.n_tiles = (s->T + p.rows_per_tile - 1) / p.rows_per_tile;
+  int W = 4 * s->N + 13;
+  p.smem = sizeof(float) * (size_t)(256 / p.G) * W;
+  p.ws_bytes = sizeof(float) * (size_t)s->batch * s->heads * p.n_tiles * W;
+  return p;
+}
+
+template <typename T, int VEC>
+static int launch_prep_bwd(const slx_prep_shape *s, const PrepDims &d, const void *params, const void *bc,
+                           const float *bias, const float *scale, const void *dU, const float *dM, const float *dK,
+                           const void *dB, const void *dC, void *d_value, void *d_params, void *d_bc, float *d_bias,
+                           float *d_scale, float *part, cudaStream_t st) {
+  PrepHyper hp = make_hyper(s);
+  PrepBwdPlan pl = prep_bwd_plan(s, VEC);
+  SLX_REQUIRE(pl.kmax <= 4, SLX_E_UNSUPPORTED, "scanprep_bwd: N=%d too large for the lane mapping", d.N);
+  SLX_REQUIRE(pl.smem <= 200 * 1024, SLX_E_UNSUPPORTED, "scanprep_bwd: N=%d needs too much shared memory", d.N);
+  constexpr int G = prep_group<VEC>();
+#define SLX_PREP_BWD(KM)                                                                                      \
+  {                                                                                                           \
+    auto kern = scanprep_bwd_kernel<T, VEC, G, KM>;                                                           \
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);    \
+    if (e != cudaSuccess) return fail((int)e, "scanprep_bwd smem attribute: %s", cudaGetErrorString(e));      \
+    kern<<<dim3(pl.n_tiles, d.batch * d.H), 256, pl.smem, st>>>(                                              \
+        (const T *)params, (const T *)bc, bias, scale, (const T *)dU, dM, dK, (const T *)dB, (const T *)dC,   \
+        (T *)d_value, (T *)d_params, (T *)d_bc, part, d, hp, pl.rows_per_tile);                               \
+  }
+  if (pl.kmax <= 1) SLX_PREP_BWD(1)
+  else if (pl.kmax == 2) SLX_PREP_BWD(2)
+  else SLX_PREP_BWD(4)
+#undef SLX_PREP_BWD
+  int rc = check_launch("scanprep_bwd");
+  if (rc) return rc;
+  int W = 4 * d.N + 13;
+  scanprep_reduce_kernel<<<dim3((W + 127) / 128, d.H), 128, 0, st>>>(part, d_bias, d_scale, d.batch, d.H, pl.n_tiles,
+                                                                      d.N);
+  return check_launch("scanprep_reduce");
+}
+
+}  // namespace slx
+
+using namespace slx;
+
+#define SLX_PREP_T(dt, ...)                                          \
+  switch (dt) {                                                      \
+    case SLX_F32: { using T_ = float; __VA_ARGS__; } break;          \
+    case SLX_BF16: { using T_ = __nv_bfloat16; __VA_ARGS__; } break; \
+    default: { using T_ = __half; __VA_ARGS__; } break;              \
+  }
+
+extern "C" {
+
+int slx_scanprep_fwd(const slx_prep_shape *s, const void *value, const void *params, const void *bc,
+                     const float *bias, const float *scale, void *U, float *M, float *K, void *B, void *C,
+                     void *stream) {
+  PrepDims d;
+  int rc = check_prep(s, &d);
+  if (rc) return rc;
+  SLX_REQUIRE(value && params && bc && bias && U && M && K && B && C, SLX_E_NULL, "scanprep_fwd: NULL tensor");
+  SLX_REQUIRE(!s->normalize_bc || scale, SLX_E_NULL, "scanprep_fwd: scale is NULL with normalize_bc set");
+  cudaStream_t st = as_stream(stream);
+  SLX_PREP_T(s->dtype, {
+    int vec = pick_vec<T_>(s, {value, bc, U, B, C});
+    constexpr int VFULL = 16 / (int)sizeof(T_);
+    if (vec == VFULL) rc = launch_prep_fwd<T_, VFULL>(s, d, value, params, bc, bias, scale, U, M, K, B, C, st);
+    else rc = launch_prep_fwd<T_, 1>(s, d, value, params, bc, bias, scale, U, M, K, B, C, st);
+  });
+  return rc;
+}
+
+size_t slx_scanprep_bwd_workspace_bytes(const slx_prep_shape *s) {
+  PrepDims d;
+  if (check_prep(s, &d)) return 0;
+  // the scalar mapping needs the most tiles-independent space; both use the same tile count
+  return prep_bwd_plan(s, 1).ws_bytes;
+}
+
+int slx_scanprep_bwd(const slx_prep_shape *s, const void *params, const void *bc, const float *bias,
+                     const float *scale, const void *dU, const float *dM, const float *dK, const void *dB,
+                     const void *dC, void *d_value, void *d_params, void *d_bc, float *d_bias, float *d_scale,
+                     void *workspace, size_t workspace_bytes, void *stream) {
+  PrepDims d;
+  int rc = check_prep(s, &d);
+  if (rc) return rc;
+  SLX_REQUIRE(params && bc && bias && dU && dM && dK && dB && dC && d_value && d_params && d_bc && d_bias, SLX_E_NULL,
+              "scanprep_bwd: NULL tensor");
+  SLX_REQUIRE(!s->normalize_bc || (scale && d_scale), SLX_E_NULL, "scanprep_bwd: scale/d_scale NULL");
+  size_t need = slx_scanprep_bwd_workspace_bytes(s);
+  SLX_REQUIRE(workspace && workspace_bytes >= need, SLX_E_WORKSPACE, "scanprep_bwd: workspace of %zu bytes needed",
+              need);
+  cudaStream_t st = as_stream(stream);
+  float *part = static_cast<float *>(workspace);
+  SLX_PREP_T(s->dtype, {
+    int vec = pick_vec<T_>(s, {bc, dU, dB, dC, d_value, d_bc});
+    constexpr int VFULL = 16 / (int)sizeof(T_);
+    if (vec == VFULL)
+      rc = launch_prep_bwd<T_, VFULL>(s, d, params, bc, bias, scale, dU, dM, dK, dB, dC, d_value, d_params, d_bc,
+                                      d_bias, d_scale, part, st);
+    else
+      rc = launch_prep_bwd<T_, 1>(s, d, params, bc, bias, scale, dU, dM, dK, dB, dC, d_value, d_params, d_bc, d_bias,
+                                  d_scale, part, st);
+  });
+  return rc;
+}
+
+}  // extern "C"

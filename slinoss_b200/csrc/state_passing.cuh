@@ -1,0 +1,158 @@
+// Bandwidth-bound cross-chunk kernels: forward/backward state passing, the
+// chunk-level dot products that feed dM, and the boundary-carry fix-up.
+#pragma once
+
+#include "common.cuh"
+
+namespace slx {
+
+template <int VEC>
+struct VecT;
+template <>
+struct VecT<2> {
+  using type = float2;
+};
+template <>
+struct VecT<4> {
+  using type = float4;
+};
+
+__device__ __forceinline__ float2 axpy_c(float2 m, float2 z, float2 v) {  // m*z + v
+  return make_float2(fmaf(m.x, z.x, fmaf(-m.y, z.y, v.x)), fmaf(m.x, z.y, fmaf(m.y, z.x, v.y)));
+}
+__device__ __forceinline__ float4 axpy_c(float2 m, float4 z, float4 v) {
+  float2 a = axpy_c(m, make_float2(z.x, z.y), make_float2(v.x, v.y));
+  float2 b = axpy_c(m, make_float2(z.z, z.w), make_float2(v.z, v.w));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ float2 vzero(float2) { return make_float2(0.f, 0.f); }
+__device__ __forceinline__ float4 vzero(float4) { return make_float4(0.f, 0.f, 0.f, 0.f); }
+// sum over the complex lanes of conj(a) * b
+__device__ __forceinline__ float2 cdot(float2 a, float2 b) { return cmul(cconj(a), b); }
+__device__ __forceinline__ float2 cdot(float4 a, float4 b) {
+  return cadd(cmul(make_float2(a.x, -a.y), make_float2(b.x, b.y)), cmul(make_float2(a.z, -a.w), make_float2(b.z, b.w)));
+}
+
+// starts[c] = z; z = m_chunk[c] * z + inc[c]     (reference.py:439-457)
+// One thread owns VEC/2 complex state lanes for the whole sequence of chunks;
+// consecutive threads own consecutive lanes, so every access is a full-width
+// coalesced 8/16-byte vector.  `starts` may alias `inc`: each chunk's increment
+// is read before its slot is overwritten.
+template <int VEC>
+__global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc, const float *__restrict__ m_chunk,
+                                                                const float *__restrict__ init, float *starts,
+                                                                float *__restrict__ final_state, int NC,
+                                                                int n_vec /* P*D/VEC */) {
+  using V = typename VecT<VEC>::type;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int bh = blockIdx.y;
+  if (i >= n_vec) return;
+  const size_t per = (size_t)n_vec;
+  const V *incv = reinterpret_cast<const V *>(inc) + (size_t)bh * NC * per + i;
+  V *stv = reinterpret_cast<V *>(starts) + (size_t)bh * NC * per + i;
+  const float2 *mc = reinterpret_cast<const float2 *>(m_chunk) + (size_t)bh * NC;
+  V z = init ? reinterpret_cast<const V *>(init)[(size_t)bh * per + i] : vzero(V());
+  int c = 0;
+  for (; c + 4 <= NC; c += 4) {
+    V v0 = incv[(size_t)(c + 0) * per], v1 = incv[(size_t)(c + 1) * per];
+    V v2 = incv[(size_t)(c + 2) * per], v3 = incv[(size_t)(c + 3) * per];
+    float2 m0 = mc[c], m1 = mc[c + 1], m2 = mc[c + 2], m3 = mc[c + 3];
+    stv[(size_t)(c + 0) * per] = z;
+    z = axpy_c(m0, z, v0);
+    stv[(size_t)(c + 1) * per] = z;
+    z = axpy_c(m1, z, v1);
+    stv[(size_t)(c + 2) * per] = z;
+    z = axpy_c(m2, z, v2);
+    stv[(size_t)(c + 3) * per] = z;
+    z = axpy_c(m3, z, v3);
+  }
+  for (; c < NC; ++c) {
+    V v = incv[(size_t)c * per];
+    float2 m = mc[c];
+    stv[(size_t)c * per] = z;
+    z = axpy_c(m, z, v);
+  }
+  reinterpret_cast<V *>(final_state)[(size_t)bh * per + i] = z;
+}
+
+// Reverse pass: g = d_final; for c = NC-1..0:
+//   zdot_partial[c] = sum conj(end_state_c) * g      (end_state_c = starts[c+1] or final)
+//   d_inc[c] = g;  g = dZ0[c] + conj(m_chunk[c]) * g
+// d_initial = g.  d_inc may alias dZ0.
+template <int VEC>
+__global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0, const float *__restrict__ m_chunk,
+                                                                const float *__restrict__ starts,
+                                                                const float *__restrict__ final_state,
+                                                                const float *__restrict__ d_final, float *d_inc,
+                                                                float *__restrict__ d_initial,
+                                                                float *__restrict__ zdot_partials, int NC, int n_vec) {
+  using V = typename VecT<VEC>::type;
+  __shared__ float2 red[8];
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int bh = blockIdx.y;
+  const bool live = i < n_vec;
+  const int iv = live ? i : 0;
+  const size_t per = (size_t)n_vec;
+  const V *dzv = reinterpret_cast<const V *>(dZ0) + (size_t)bh * NC * per + iv;
+  V *div = reinterpret_cast<V *>(d_inc) + (size_t)bh * NC * per + iv;
+  const V *stv = reinterpret_cast<const V *>(starts) + (size_t)bh * NC * per + iv;
+  const float2 *mc = reinterpret_cast<const float2 *>(m_chunk) + (size_t)bh * NC;
+  V g = (d_final && live) ? reinterpret_cast<const V *>(d_final)[(size_t)bh * per + iv] : vzero(V());
+  V endst = reinterpret_cast<const V *>(final_state)[(size_t)bh * per + iv];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int c = NC - 1; c >= 0; --c) {
+    V dz = dzv[(size_t)c * per];
+    V st = stv[(size_t)c * per];  // start of chunk c = end state of chunk c-1 (next iteration)
+    float2 m = mc[c];
+    float2 part = live ? cdot(endst, g) : make_float2(0.f, 0.f);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      part.x += __shfl_xor_sync(0xffffffffu, part.x, off);
+      part.y += __shfl_xor_sync(0xffffffffu, part.y, off);
+    }
+    if (lane == 0) red[warp] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float2 acc = red[0];
+      for (int w = 1; w < (int)(blockDim.x >> 5); ++w) acc = cadd(acc, red[w]);
+      reinterpret_cast<float2 *>(zdot_partials)[((size_t)bh * NC + c) * gridDim.x + blockIdx.x] = acc;
+    }
+    __syncthreads();
+    if (live) div[(size_t)c * per] = g;
+    g = axpy_c(cconj(m), g, dz);
+    endst = st;
+  }
+  if (d_initial && live) reinterpret_cast<V *>(d_initial)[(size_t)bh * per + iv] = g;
+}
+
+__global__ void zdot_reduce_kernel(const float *__restrict__ partials, float *__restrict__ zdot, int n_rows, int nblk) {
+  int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n_rows) return;
+  const float2 *p = reinterpret_cast<const float2 *>(partials) + (size_t)r * nblk;
+  float2 acc = make_float2(0.f, 0.f);
+  for (int b = 0; b < nblk; ++b) acc = cadd(acc, p[b]);
+  reinterpret_cast<float2 *>(zdot)[r] = acc;
+}
+
+// Adds the gradient a chunk sends to the token before it (prev-tap terms of its
+// first token) to the last row of the previous chunk; chunk 0's carry is the
+// gradient of the streaming inputs (B_prev, U_prev).
+template <typename T>
+__global__ void carry_fixup_kernel(const float *__restrict__ carryB, const float *__restrict__ carryU, T *dB, T *dU,
+                                   float *dB_prev, float *dU_prev, int T_len, int P, int D, int L, int NC) {
+  const int c = blockIdx.x, bh = blockIdx.y;
+  const float *cb = carryB + ((size_t)bh * NC + c) * D;
+  const float *cu = carryU + ((size_t)bh * NC + c) * P;
+  if (c == 0) {
+    if (dB_prev)
+      for (int i = threadIdx.x; i < D; i += blockDim.x) dB_prev[(size_t)bh * D + i] = cb[i];
+    if (dU_prev)
+      for (int i = threadIdx.x; i < P; i += blockDim.x) dU_prev[(size_t)bh * P + i] = cu[i];
+    return;
+  }
+  const size_t row = (size_t)bh * T_len + (size_t)c * L - 1;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) dB[row * D + i] = from_f<T>(to_f(dB[row * D + i]) + cb[i]);
+  for (int i = threadIdx.x; i < P; i += blockDim.x) dU[row * P + i] = from_f<T>(to_f(dU[row * P + i]) + cu[i]);
+}
+
+}  // namespace slx

@@ -1,0 +1,318 @@
+"""``v2x2ssd`` on B200: host side of the chunked scan.
+
+``v2x2ssd_b200`` has the signature, return values and error behaviour of the
+reference's ``slinoss.ops.v2x2ssd.v2x2ssd_cute`` (slinoss/ops/v2x2ssd/cute/
+api.py:52-172); the stage functions mirror ``chunk_increment_cute`` /
+``state_passing_cute`` / ``chunk_scan_cute`` (cute/kernels/fwd/__init__.py:740,
+897,1125).  All arithmetic happens in the sm_100a kernels behind the C ABI;
+this file validates, allocates outputs with torch and wires autograd.
+"""
+
+from __future__ import annotations
+
+from ctypes import byref
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _lib
+
+_ACT_DTYPES = (torch.float32, torch.bfloat16, torch.float16)
+_CHUNKS = (16, 32, 64, 128)
+
+
+def _check_contiguous(name: str, x: torch.Tensor) -> None:
+    if not x.is_contiguous():
+        raise ValueError(f"{name} must be contiguous; got strides {x.stride()}.")
+
+
+def _validate_inputs(U, M, K, B, C, initial_states, B_prev, U_prev) -> Tuple[int, int, int, int, int]:
+    """Same checks and messages as reference.py:124-204 (_validate_inputs)."""
+    tensors = (U, M, K, B, C)
+    if not all(torch.is_floating_point(t) for t in tensors):
+        raise ValueError("U, M, K, B, and C must be floating-point tensors.")
+    device = U.device
+    if not all(t.device == device for t in tensors):
+        raise ValueError(f"All inputs must be on the same device. Got {[t.device for t in tensors]}.")
+    for name, t in (("U", U), ("M", M), ("K", K), ("B", B), ("C", C)):
+        _check_contiguous(name, t)
+    if U.ndim != 4:
+        raise ValueError(f"U must be (batch,heads,T,P). Got {tuple(U.shape)}.")
+    if M.ndim != 4 or M.shape[-1] != 2:
+        raise ValueError(f"M must be (batch,heads,T,2). Got {tuple(M.shape)}.")
+    if K.ndim != 5 or K.shape[-2:] != (2, 2):
+        raise ValueError(f"K must be (batch,heads,T,2,2). Got {tuple(K.shape)}.")
+    if B.ndim != 4:
+        raise ValueError(f"B must be (batch,heads,T,2N). Got {tuple(B.shape)}.")
+    if C.ndim != 4:
+        raise ValueError(f"C must be (batch,heads,T,2N). Got {tuple(C.shape)}.")
+    b, h, T, P = map(int, U.shape)
+    for name, t in (("M", M), ("K", K), ("B", B), ("C", C)):
+        if tuple(t.shape[:3]) != (b, h, T):
+            raise ValueError(f"Leading (batch,heads,T) dims of {name} must match U.")
+    D = int(B.shape[-1])
+    if D % 2 != 0:
+        raise ValueError(f"B/C 2N dim must be divisible by 2. Got {D}.")
+    if tuple(C.shape) != (b, h, T, D):
+        raise ValueError("C must match B exactly.")
+    if (B_prev is None) ^ (U_prev is None):
+        raise ValueError("B_prev and U_prev must be passed together (or both omitted).")
+    if initial_states is not None:
+        if tuple(initial_states.shape) != (b, h, P, D):
+            raise ValueError("initial_states must be (batch,heads,P,2N) "
+                             f"={(b, h, P, D)}. Got {tuple(initial_states.shape)}.")
+        _check_contiguous("initial_states", initial_states)
+        if initial_states.device != device:
+            raise ValueError("initial_states must be on the same device as inputs.")
+    if B_prev is not None:
+        if tuple(B_prev.shape) != (b, h, D):
+            raise ValueError(f"B_prev must be (batch,heads,2N)={(b, h, D)}. Got {tuple(B_prev.shape)}.")
+        if tuple(U_prev.shape) != (b, h, P):
+            raise ValueError(f"U_prev must be (batch,heads,P)={(b, h, P)}. Got {tuple(U_prev.shape)}.")
+        _check_contiguous("B_prev", B_prev)
+        _check_contiguous("U_prev", U_prev)
+        if B_prev.device != device or U_prev.device != device:
+            raise ValueError("B_prev and U_prev must be on the same device as inputs.")
+    return b, h, T, D // 2, P
+
+
+def _resolve_dtypes(input_dtypes, compute_dtype, output_dtype, default_output_dtype):
+    """reference.py:59-80 (_resolve_dtypes)."""
+    if compute_dtype is None:
+        promoted = input_dtypes[0]
+        for dt in input_dtypes[1:]:
+            promoted = torch.promote_types(promoted, dt)
+        rdtype = torch.float32 if promoted in (torch.float16, torch.bfloat16) else promoted
+    else:
+        rdtype = compute_dtype
+    if rdtype not in (torch.float32, torch.float64):
+        raise ValueError(f"compute_dtype must be float32 or float64, got {rdtype}.")
+    odtype = default_output_dtype if output_dtype is None else output_dtype
+    if odtype not in (torch.float16, torch.bfloat16, torch.float32, torch.float64):
+        raise ValueError(f"output_dtype must be a real floating dtype, got {odtype}.")
+    return rdtype, odtype
+
+
+def _resolve_empty_outputs(b, h, P, D, device, odtype, initial_states, B_prev, U_prev):
+    """T == 0 semantics of reference.py:670-701."""
+    Y = torch.empty((b, h, 0, P), device=device, dtype=odtype)
+    final = (torch.zeros((b, h, P, D), device=device, dtype=odtype) if initial_states is None
+             else initial_states.to(dtype=odtype).contiguous())
+    if B_prev is None:
+        B_last = torch.zeros((b, h, D), device=device, dtype=odtype)
+        U_last = torch.zeros((b, h, P), device=device, dtype=odtype)
+    else:
+        B_last = B_prev.to(dtype=odtype).contiguous()
+        U_last = U_prev.to(dtype=odtype).contiguous()
+    return Y, final, B_last, U_last
+
+
+def _require_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and t.device.type != "cuda":
+            raise ValueError("slinoss_b200 v2x2ssd requires CUDA tensors.")
+
+
+def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    return None if t is None else t.detach().to(torch.float32).contiguous()
+
+
+def _shape(b, h, T, P, N, L, dtype) -> _lib.ScanShape:
+    if L not in _CHUNKS:
+        raise ValueError(f"chunk_size must be one of {_CHUNKS} for the sm_100a kernels. Got {L}.")
+    return _lib.ScanShape(b * h, T, P, N, L, _lib.dtype_code(dtype))
+
+
+# --------------------------------------------------------------------------- #
+# stage-level entry points
+# --------------------------------------------------------------------------- #
+
+def chunk_increment_b200(U, M, K, B, *, B_prev=None, U_prev=None, chunk_size: int):
+    """Stage 1 -> ``(inc (b,h,C,P,2N) fp32, m_chunk (b,h,C,2) fp32)``."""
+    _require_cuda(U, M, K, B)
+    b, h, T, P = map(int, U.shape)
+    D = int(B.shape[-1])
+    L = int(chunk_size)
+    NC = (T + L - 1) // L
+    s = _shape(b, h, T, P, D // 2, L, U.dtype)
+    inc = torch.empty((b, h, NC, P, D), device=U.device, dtype=torch.float32)
+    mch = torch.empty((b, h, NC, 2), device=U.device, dtype=torch.float32)
+    bp, up = _f32(B_prev), _f32(U_prev)
+    _lib.check(_lib.lib().slx_chunk_increment_fwd(
+        byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), _lib.ptr(bp), _lib.ptr(up),
+        inc.data_ptr(), mch.data_ptr(), _lib.stream_ptr(U.device)), "chunk_increment")
+    return inc, mch
+
+
+def state_passing_b200(inc, m_chunk, *, initial_states=None):
+    """Stage 2 -> ``(chunk_starts, final_state)`` fp32."""
+    _require_cuda(inc, m_chunk, initial_states)
+    b, h, NC, P, D = map(int, inc.shape)
+    init = _f32(initial_states)
+    starts = torch.empty_like(inc)
+    final = torch.empty((b, h, P, D), device=inc.device, dtype=torch.float32)
+    _lib.check(_lib.lib().slx_state_passing_fwd(
+        b * h, NC, P, D // 2, inc.data_ptr(), m_chunk.data_ptr(), _lib.ptr(init), starts.data_ptr(),
+        final.data_ptr(), _lib.stream_ptr(inc.device)), "state_passing")
+    return starts, final
+
+
+def chunk_scan_b200(U, M, K, B, C, chunk_starts, *, B_prev=None, U_prev=None, chunk_size: int):
+    """Stage 3 -> ``Y (b,h,T,P)`` in ``U.dtype``."""
+    _require_cuda(U, M, K, B, C, chunk_starts)
+    b, h, T, P = map(int, U.shape)
+    D = int(B.shape[-1])
+    s = _shape(b, h, T, P, D // 2, int(chunk_size), U.dtype)
+    Y = torch.empty_like(U)
+    bp, up = _f32(B_prev), _f32(U_prev)
+    _lib.check(_lib.lib().slx_chunk_scan_fwd(
+        byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
+        chunk_starts.data_ptr(), _lib.ptr(bp), _lib.ptr(up), Y.data_ptr(), _lib.stream_ptr(U.device)),
+        "chunk_scan")
+    return Y
+
+
+def _fwd_impl(U, M, K, B, C, init32, bp32, up32, L):
+    """Three stages back to back.  Returns (Y, final32, chunk_starts, m_chunk)."""
+    b, h, T, P = map(int, U.shape)
+    D = int(B.shape[-1])
+    NC = (T + L - 1) // L
+    s = _shape(b, h, T, P, D // 2, L, U.dtype)
+    dev = U.device
+    Y = torch.empty_like(U)
+    final = torch.empty((b, h, P, D), device=dev, dtype=torch.float32)
+    starts = torch.empty((b, h, NC, P, D), device=dev, dtype=torch.float32)
+    mch = torch.empty((b, h, NC, 2), device=dev, dtype=torch.float32)
+    _lib.check(_lib.lib().slx_v2x2ssd_fwd(
+        byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
+        _lib.ptr(init32), _lib.ptr(bp32), _lib.ptr(up32), Y.data_ptr(), final.data_ptr(),
+        starts.data_ptr(), mch.data_ptr(), _lib.stream_ptr(dev)), "v2x2ssd forward")
+    return Y, final, starts, mch
+
+
+def _bwd_impl(U, M, K, B, C, bp32, up32, starts, mch, final32, dY, d_final32, L, *,
+              want_initial: bool, want_prev: bool):
+    b, h, T, P = map(int, U.shape)
+    D = int(B.shape[-1])
+    s = _shape(b, h, T, P, D // 2, L, U.dtype)
+    dev = U.device
+    dU, dB, dC = torch.empty_like(U), torch.empty_like(B), torch.empty_like(C)
+    dM = torch.empty((b, h, T, 2), device=dev, dtype=torch.float32)
+    dK = torch.empty((b, h, T, 2, 2), device=dev, dtype=torch.float32)
+    d_init = torch.empty((b, h, P, D), device=dev, dtype=torch.float32) if want_initial else None
+    dBp = torch.empty((b, h, D), device=dev, dtype=torch.float32) if want_prev else None
+    dUp = torch.empty((b, h, P), device=dev, dtype=torch.float32) if want_prev else None
+    L_ = _lib.lib()
+    nbytes = int(L_.slx_v2x2ssd_bwd_workspace_bytes(byref(s)))
+    ws = torch.empty((nbytes,), device=dev, dtype=torch.uint8)
+    _lib.check(L_.slx_v2x2ssd_bwd(
+        byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
+        _lib.ptr(bp32), _lib.ptr(up32), starts.data_ptr(), mch.data_ptr(), final32.data_ptr(),
+        dY.data_ptr(), _lib.ptr(d_final32), dU.data_ptr(), dM.data_ptr(), dK.data_ptr(),
+        dB.data_ptr(), dC.data_ptr(), _lib.ptr(d_init), _lib.ptr(dBp), _lib.ptr(dUp),
+        ws.data_ptr(), nbytes, _lib.stream_ptr(dev)), "v2x2ssd backward")
+    return dU, dM, dK, dB, dC, d_init, dBp, dUp
+
+
+class _V2x2SSDFn(torch.autograd.Function):
+    """Autograd node; same inputs/outputs as the reference's
+    ``_V2x2SSDCuTeTrainingFn`` (cute/autograd.py:40-266)."""
+
+    @staticmethod
+    def forward(ctx, U, M, K, B, C, initial_states, B_prev, U_prev, L, odtype, return_state):
+        init32, bp32, up32 = _f32(initial_states), _f32(B_prev), _f32(U_prev)
+        Y, final32, starts, mch = _fwd_impl(U.detach(), M.detach(), K.detach(), B.detach(),
+                                            C.detach(), init32, bp32, up32, L)
+        ctx.L = L
+        ctx.return_state = return_state
+        ctx.has_init = initial_states is not None
+        ctx.has_prev = B_prev is not None
+        ctx.init_dtype = None if initial_states is None else initial_states.dtype
+        ctx.prev_dtype = None if B_prev is None else B_prev.dtype
+        saved = [U, M, K, B, C, mch, starts, final32]
+        if ctx.has_prev:
+            saved += [bp32, up32]
+        ctx.save_for_backward(*[t.detach() for t in saved])
+        Y = Y.to(odtype)
+        if not return_state:
+            return Y
+        B_last = B.detach()[:, :, -1, :].to(odtype).contiguous()
+        U_last = U.detach()[:, :, -1, :].to(odtype).contiguous()
+        return Y, final32.to(odtype), B_last, U_last
+
+    @staticmethod
+    def backward(ctx, *grads):
+        saved = ctx.saved_tensors
+        U, M, K, B, C, mch, starts, final32 = saved[:8]
+        bp32, up32 = (saved[8], saved[9]) if ctx.has_prev else (None, None)
+        if ctx.return_state:
+            dY, d_final, dB_last, dU_last = grads
+        else:
+            (dY,) = grads
+            d_final = dB_last = dU_last = None
+        dU = dM = dK = dB = dC = d_init = dBp = dUp = None
+        if dY is not None or d_final is not None:
+            dYc = (torch.zeros_like(U) if dY is None else dY.to(U.dtype).contiguous())
+            dfin = None if d_final is None else d_final.to(torch.float32).contiguous()
+            dU, dM, dK, dB, dC, d_init, dBp, dUp = _bwd_impl(
+                U, M, K, B, C, bp32, up32, starts, mch, final32, dYc, dfin, ctx.L,
+                want_initial=ctx.has_init, want_prev=ctx.has_prev)
+        if dB_last is not None:
+            if dB is None:
+                dB = torch.zeros_like(B)
+            dB[:, :, -1, :].add_(dB_last.to(B.dtype))
+        if dU_last is not None:
+            if dU is None:
+                dU = torch.zeros_like(U)
+            dU[:, :, -1, :].add_(dU_last.to(U.dtype))
+        if d_init is not None:
+            d_init = d_init.to(ctx.init_dtype)
+        if dBp is not None:
+            dBp, dUp = dBp.to(ctx.prev_dtype), dUp.to(ctx.prev_dtype)
+        return dU, dM, dK, dB, dC, d_init, dBp, dUp, None, None, None
+
+
+@torch.compiler.disable
+def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=None, U_prev=None,
+                 compute_dtype: Optional[torch.dtype] = None,
+                 output_dtype: Optional[torch.dtype] = None, return_state: bool = False):
+    """Drop-in for ``v2x2ssd_cute`` (cute/api.py:52): returns ``Y`` or
+    ``(Y, final_state, B_last, U_last)``; differentiable in all eight inputs."""
+    b, h, T, N, P = _validate_inputs(U, M, K, B, C, initial_states, B_prev, U_prev)
+    if U.device.type != "cuda":
+        raise ValueError("slinoss_b200 v2x2ssd requires CUDA tensors.")
+    if chunk_size <= 0:
+        raise ValueError(f"chunk_size must be positive. Got {chunk_size}.")
+    D = 2 * N
+    rdtype, odtype = _resolve_dtypes([U.dtype, M.dtype, K.dtype, B.dtype, C.dtype], compute_dtype,
+                                     output_dtype, U.dtype)
+    if rdtype != torch.float32:
+        raise ValueError("The sm_100a v2x2ssd path supports only float32 compute. "
+                         f"Got compute_dtype={rdtype}.")
+    if T == 0:
+        out = _resolve_empty_outputs(b, h, P, D, U.device, odtype, initial_states, B_prev, U_prev)
+        return out if return_state else out[0]
+    # the kernels take U, B, C in one activation dtype and M, K in fp32
+    act = torch.promote_types(torch.promote_types(U.dtype, B.dtype), C.dtype)
+    if act not in _ACT_DTYPES:
+        raise TypeError(f"U/B/C must be float32, bfloat16 or float16. Got {act}.")
+    if odtype == torch.float32 and act != torch.float32:
+        act = torch.float32  # a wider output must not be rounded through the half store
+    Ua, Ba, Ca = (t if t.dtype == act else t.to(act) for t in (U, B, C))
+    Mf = M if M.dtype == torch.float32 else M.to(torch.float32)
+    Kf = K if K.dtype == torch.float32 else K.to(torch.float32)
+    needs_grad = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (U, M, K, B, C, initial_states, B_prev, U_prev))
+    if needs_grad:
+        return _V2x2SSDFn.apply(Ua, Mf, Kf, Ba, Ca, initial_states, B_prev, U_prev, int(chunk_size),
+                                odtype, bool(return_state))
+    Y, final32, _, _ = _fwd_impl(Ua, Mf, Kf, Ba, Ca, _f32(initial_states), _f32(B_prev),
+                                 _f32(U_prev), int(chunk_size))
+    Y = Y.to(odtype)
+    if not return_state:
+        return Y
+    return (Y, final32.to(odtype), B[:, :, -1, :].to(odtype).contiguous(),
+            U[:, :, -1, :].to(odtype).contiguous())
+
+
+__all__ = ["v2x2ssd_b200", "chunk_increment_b200", "state_passing_b200", "chunk_scan_b200"]

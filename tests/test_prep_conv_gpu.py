@@ -1,0 +1,204 @@
+"""GPU parity of SLinOSSScanPrep and the depthwise causal conv against the
+pinned oracle (oracle/prep.py) and the reference's fixtures, through the C ABI."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import prep as oprep
+from util import golden, rel_err
+
+pytestmark = pytest.mark.gpu
+
+BIAS_NAMES = ("dt_bias", "gamma_bias", "omega_bias", "mix_r_bias", "mix_theta_bias",
+              "mix_k_prev_bias", "mix_k_curr_bias")
+
+
+def _np(t):
+    return t.detach().float().cpu().numpy().astype(np.float64)
+
+
+def _cu(x, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(dtype).cuda()
+
+
+def _run_prep(value, params, bc, pars, hp, H, N, P, gouts=None, normalize=True):
+    import slinoss_b200 as sb
+
+    leaves = [value, params, bc] + [pars[n] for n in BIAS_NAMES] + [pars["b_scale"], pars["c_scale"]]
+    for t in leaves:
+        t.requires_grad_(True)
+    si = sb.scanprep_b200(value, params, bc, n_heads=H, d_state=N, d_head=P, normalize_bc=normalize,
+                          **hp, **{n: pars[n] for n in BIAS_NAMES}, b_scale=pars["b_scale"],
+                          c_scale=pars["c_scale"])
+    outs = [si.U, si.M, si.K, si.B, si.C]
+    grads = None
+    if gouts is not None:
+        grads = torch.autograd.grad(outs, leaves, gouts)
+    return outs, grads
+
+
+def test_prep_golden_fp32():
+    g = golden("prep_f32.npz")
+    H, _, N = g["b_scale"].shape
+    P = g["value"].shape[-1] // H
+    hp = {k[3:]: float(v) for k, v in g.items() if k.startswith("hp_")}
+    pars = {n: _cu(g[n]) for n in BIAS_NAMES + ("b_scale", "c_scale")}
+    gouts = [_cu(g["g" + n]) for n in "UMKBC"]
+    outs, grads = _run_prep(_cu(g["value"]), _cu(g["params"]), _cu(g["bc"]), pars, hp, H, N, P, gouts)
+    assert torch.equal(outs[0].cpu(), torch.from_numpy(g["U"]))
+    assert rel_err(_np(outs[1]), g["M"]) < 2e-6
+    # FOH taps: (rho-1)/z cancels in fp32 (in the reference too); see tests/test_oracle_pins.py
+    assert rel_err(_np(outs[2]), g["K"]) < 1e-4
+    assert rel_err(_np(outs[3]), g["B"]) < 2e-6 and rel_err(_np(outs[4]), g["C"]) < 2e-6
+    assert rel_err(_np(grads[0]), g["d_value"]) < 1e-7
+    assert rel_err(_np(grads[1]), g["d_params"]) < 2e-4
+    assert rel_err(_np(grads[2]), g["d_bc"]) < 2e-5
+    b, T = g["value"].shape[:2]
+    for i, n in enumerate(BIAS_NAMES):
+        floor = 2e-5 * b * T
+        assert np.all(np.abs(_np(grads[3 + i]) - g["d_" + n]) <= 2e-4 * np.abs(g["d_" + n]) + floor), n
+    assert rel_err(_np(grads[10]), g["d_b_scale"]) < 2e-5
+    assert rel_err(_np(grads[11]), g["d_c_scale"]) < 2e-5
+
+
+@pytest.mark.parametrize("dtype,N,P,H,b,T", [
+    (torch.bfloat16, 128, 64, 4, 2, 300),   # headline head shape, 16-byte vector path
+    (torch.float16, 64, 64, 3, 1, 130),
+    (torch.float32, 16, 32, 4, 2, 256),     # BASELINE config 0 shape
+    (torch.float32, 5, 6, 2, 1, 33),        # scalar path (nothing 16-byte aligned)
+    (torch.bfloat16, 64, 64, 12, 1, 70),    # config-1 head shape; inputs are slices of one projection
+])
+def test_prep_seeded_vs_oracle(dtype, N, P, H, b, T):
+    gen = torch.Generator().manual_seed(N + T)
+    wv, wp, wb = H * P, H * 13, H * 4 * N
+    # one wide projection output, sliced like the mixer does (mixer.py:552-557)
+    proj = torch.randn(b, T, wv + wv + wp + wb, generator=gen).to(dtype).cuda()
+    value = proj[..., wv:2 * wv]
+    params = proj[..., 2 * wv:2 * wv + wp] * 1.5
+    bc = proj[..., 2 * wv + wp:].view(b, T, H, 4, N)
+    pars = {n: (0.5 * torch.randn(H, generator=gen)).cuda() for n in BIAS_NAMES}
+    pars["b_scale"] = (1 + 0.3 * torch.randn(H, 2, N, generator=gen)).cuda()
+    pars["c_scale"] = (1 + 0.3 * torch.randn(H, 2, N, generator=gen)).cuda()
+    hp = dict(dt_min=1e-4, dt_max=1e-1, r_min=0.9, r_max=1.0, theta_bound=float(np.pi), k_max=0.5, eps=1e-8)
+    shapes = [(b, H, T, P), (b, H, T, 2), (b, H, T, 2, 2), (b, H, T, 2 * N), (b, H, T, 2 * N)]
+    odt = [dtype, torch.float32, torch.float32, dtype, dtype]
+    gouts = [torch.randn(s, generator=gen).to(d).cuda() for s, d in zip(shapes, odt)]
+    v0, p0, c0 = value.detach().clone(), params.detach().clone(), bc.detach().clone()
+    outs, grads = _run_prep(value.detach(), params.detach().contiguous(), bc.detach(), pars, hp, H, N, P, gouts)
+
+    cfg = oprep.PrepConfig(n_heads=H, d_state=N, d_head=P, **hp)
+    bias = oprep.flat_bias(*(_np(pars[n]) for n in BIAS_NAMES))
+    scale = np.concatenate([_np(pars["b_scale"]), _np(pars["c_scale"])], axis=1)
+    p4 = _np(p0).reshape(b, T, H, 13)
+    Mo, Ko = oprep.coefficients_fwd(p4, bias, cfg)
+    Bo, Co = oprep.pack_bc_fwd(_np(c0), scale, cfg)
+    half = dtype != torch.float32
+    tol_bc = 4e-3 if half else 2e-6
+    assert torch.equal(outs[0], v0.view(b, T, H, P).permute(0, 2, 1, 3))
+    assert rel_err(_np(outs[1]), Mo) < 2e-6
+    assert rel_err(_np(outs[2]), Ko) < 2e-4
+    assert rel_err(_np(outs[3]), Bo) < tol_bc and rel_err(_np(outs[4]), Co) < tol_bc
+    dp, dbias = oprep.coefficients_bwd(p4, bias, cfg, _np(gouts[1]), _np(gouts[2]))
+    dbc, dscale = oprep.pack_bc_bwd(_np(c0), scale, cfg, _np(gouts[3]), _np(gouts[4]))
+    tol_g = 6e-3 if half else 3e-4
+    assert rel_err(_np(grads[0]), oprep.pack_u_bwd(_np(gouts[0]))) < 1e-7
+    assert rel_err(_np(grads[1]).reshape(b, T, H, 13), dp) < tol_g
+    assert rel_err(_np(grads[2]), dbc) < tol_g
+    for i, slot in enumerate(oprep.BIAS_SLOTS):
+        mag = np.abs(dp[..., slot]).sum(axis=(0, 1))
+        assert np.all(np.abs(_np(grads[3 + i]) - dbias[:, slot]) <= 3e-4 * mag + 1e-6), BIAS_NAMES[i]
+    assert rel_err(_np(grads[10]), dscale[:, :2]) < 3e-4
+    assert rel_err(_np(grads[11]), dscale[:, 2:]) < 3e-4
+    # deterministic reductions: a second run is bitwise equal
+    _, grads2 = _run_prep(v0, p0.contiguous(), c0, pars, hp, H, N, P, gouts)
+    for a_, b_ in zip(grads, grads2):
+        assert torch.equal(a_, b_)
+
+
+@pytest.mark.parametrize("tag", ["w4_state", "w4_nostate", "w2_state", "w4_short"])
+@pytest.mark.parametrize("silu", [False, True])
+def test_conv_golden(tag, silu):
+    import slinoss_b200 as sb
+
+    g = {k.split(".", 1)[1]: v for k, v in golden("conv_f64.npz").items() if k.startswith(tag + ".")}
+    x, w, bias = (_cu(g[k]).requires_grad_(True) for k in ("x", "w", "bias"))
+    st = _cu(g["state"]).requires_grad_(True) if "state" in g else None
+    y, nxt = sb.cconv1d_b200(x, w, bias, st, activation="silu" if silu else None)
+    sfx = "_silu" if silu else ""
+    assert rel_err(_np(y), g["y" + sfx]) < 2e-6
+    assert rel_err(_np(nxt), g["next_state"]) < 1e-7
+    leaves = [x, w, bias] + ([st] if st is not None else [])
+    if silu:
+        grads = torch.autograd.grad(y, leaves[:3], _cu(g["dy"]))
+    else:
+        grads = torch.autograd.grad([y, nxt], leaves, [_cu(g["dy"]), _cu(g["d_next"])])
+    assert rel_err(_np(grads[0]), g["dx" + sfx]) < 3e-6
+    assert rel_err(_np(grads[1]), g["dw" + sfx]) < 3e-6
+    assert rel_err(_np(grads[2]), g["dbias" + sfx]) < 3e-6
+    if not silu and st is not None:
+        assert rel_err(_np(grads[3]), g["dstate"]) < 3e-6
+
+
+@pytest.mark.parametrize("dtype,b,T,C,W,with_state", [
+    (torch.bfloat16, 2, 300, 768, 4, True),     # config-1 width; strided slice input
+    (torch.bfloat16, 1, 130, 1024, 4, False),
+    (torch.float16, 2, 65, 96, 3, True),
+    (torch.float32, 2, 77, 20, 4, True),        # scalar path
+])
+def test_conv_seeded_vs_oracle(dtype, b, T, C, W, with_state):
+    import slinoss_b200 as sb
+
+    gen = torch.Generator().manual_seed(C + T)
+    wide = torch.randn(b, T, 2 * C + 24, generator=gen).to(dtype).cuda()
+    x = wide[..., C:2 * C]  # column slice, row stride 2C+24
+    w = (0.5 * torch.randn(C, W, generator=gen)).to(dtype).cuda().requires_grad_(True)
+    bias = (0.5 * torch.randn(C, generator=gen)).to(dtype).cuda().requires_grad_(True)
+    st = torch.randn(b, C, W - 1, generator=gen).to(dtype).cuda().requires_grad_(True) if with_state else None
+    xl = x.detach().clone().requires_grad_(True)
+    xs = wide.detach().clone().requires_grad_(True)
+    y, nxt = sb.cconv1d_b200(xs[..., C:2 * C], w, bias, st)
+    dy = torch.randn(b, T, C, generator=gen).to(dtype).cuda()
+    dn = torch.randn(b, C, W - 1, generator=gen).to(dtype).cuda()
+    leaves = [xs, w, bias] + ([st] if st is not None else [])
+    grads = torch.autograd.grad([y, nxt], leaves, [dy, dn])
+    yo, nxo, _ = oprep.cconv1d_fwd(_np(xl), _np(w), _np(bias), None if st is None else _np(st))
+    dxo, dwo, dbo, dso = oprep.cconv1d_bwd(_np(xl), _np(w), _np(bias), None if st is None else _np(st),
+                                           _np(dy), d_next_state=_np(dn))
+    half = dtype != torch.float32
+    tol = 4e-3 if half else 3e-6
+    assert rel_err(_np(y), yo) < tol and rel_err(_np(nxt), nxo) < 1e-7
+    assert rel_err(_np(grads[0][..., C:2 * C]), dxo) < tol
+    assert float(grads[0][..., :C].abs().max()) == 0.0
+    # weight/bias gradients are fp32 sums rounded once to the parameter dtype
+    assert rel_err(_np(grads[1]), dwo) < tol and rel_err(_np(grads[2]), dbo) < tol
+    if st is not None:
+        assert rel_err(_np(grads[3]), dso) < tol
+
+
+def test_backends_on_a_fake_owner():
+    """The backend objects read only attributes of their owner, like the
+    reference's fakes in tests/test_mixer.py:18-74."""
+    import types
+
+    import slinoss_b200 as sb
+
+    H, N, P, b, T = 2, 16, 32, 1, 40
+    gen = torch.Generator().manual_seed(0)
+    owner = types.SimpleNamespace(
+        n_heads=H, d_state=N, d_head=P, normalize_bc=True, dt_min=1e-4, dt_max=1e-1, r_min=0.9,
+        r_max=1.0, theta_bound=float(np.pi), k_max=0.5, eps=1e-8,
+        **{n: torch.zeros(H).cuda() for n in BIAS_NAMES},
+        b_scale=torch.ones(H, 2, N).cuda(), c_scale=torch.ones(H, 2, N).cuda())
+    value = torch.randn(b, T, H * P, generator=gen).cuda()
+    params = torch.randn(b, T, H * 13, generator=gen).cuda()
+    bc = torch.randn(b, T, H, 4, N, generator=gen).cuda()
+    si = sb.B200ScanPrepBackend()(owner, sb.ScanPrepInputs(value=value, params=params, bc=bc))
+    assert si.U.shape == (b, H, T, P) and si.K.shape == (b, H, T, 2, 2)
+    mixer = types.SimpleNamespace(d_conv=4, dw_weight=torch.randn(H * P, 4, generator=gen).cuda(),
+                                  dw_bias=torch.zeros(H * P).cuda())
+    y, nxt = sb.B200CConv1dBackend()(mixer, value, None)
+    assert y.shape == value.shape and nxt.shape == (b, H * P, 3)
+    assert torch.equal(nxt, value[:, -3:, :].transpose(1, 2))

@@ -1,0 +1,175 @@
+"""GPU parity of the v2x2ssd scan against the pinned CPU oracle and the golden
+fixtures produced by the reference.  Everything goes through the C ABI.
+
+Tolerances (relative L2 error, the north-star metric): 1e-5 for fp32 inputs,
+2e-2 for bf16/fp16 inputs with fp32 state.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import SCAN_GRADS, make_scan_inputs, oracle_fwd_bwd, run_b200_fwd_bwd, to_np
+from util import golden, rel_err
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-5
+TOL_HALF = 2e-2
+
+
+def _cuda(x, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(x))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda()
+
+
+def _golden_inputs(g, dtype):
+    inp = dict(U=_cuda(g["U"], dtype), M=_cuda(g["M"], torch.float32), K=_cuda(g["K"], torch.float32),
+               B=_cuda(g["B"], dtype), C=_cuda(g["C"], dtype), dY=_cuda(g["dY"], dtype),
+               initial_states=None, B_prev=None, U_prev=None, d_final=None)
+    if "initial_states" in g:
+        inp["initial_states"] = _cuda(g["initial_states"], torch.float32)
+    if "B_prev" in g:
+        inp["B_prev"] = _cuda(g["B_prev"], dtype)
+        inp["U_prev"] = _cuda(g["U_prev"], dtype)
+    if "d_final" in g:
+        inp["d_final"] = _cuda(g["d_final"], torch.float32)
+    return inp
+
+
+def test_golden_small_stages_and_gradients():
+    import slinoss_b200 as sb
+
+    g = golden("scan_small_f64.npz")
+    L = int(g["chunk_size"])
+    inp = _golden_inputs(g, torch.float32)
+    inc, mch = sb.chunk_increment_b200(inp["U"], inp["M"], inp["K"], inp["B"], B_prev=inp["B_prev"],
+                                       U_prev=inp["U_prev"], chunk_size=L)
+    assert rel_err(to_np(inc), g["inc"]) < TOL_F32
+    assert rel_err(to_np(mch), g["m_chunk"]) < TOL_F32
+    starts, fin = sb.state_passing_b200(inc, mch, initial_states=inp["initial_states"])
+    assert rel_err(to_np(starts), g["chunk_starts"]) < TOL_F32
+    assert rel_err(to_np(fin), g["final_state"]) < TOL_F32
+    Y3 = sb.chunk_scan_b200(inp["U"], inp["M"], inp["K"], inp["B"], inp["C"], starts,
+                            B_prev=inp["B_prev"], U_prev=inp["U_prev"], chunk_size=L)
+    assert rel_err(to_np(Y3), g["Y_stage3"]) < TOL_F32
+    Y, fin2, grads = run_b200_fwd_bwd(inp, L)
+    assert rel_err(to_np(Y), g["Y"]) < TOL_F32
+    assert rel_err(to_np(fin2), g["final_state"]) < TOL_F32
+    for name in SCAN_GRADS:
+        assert rel_err(to_np(grads[name]), g[name]) < TOL_F32, name
+
+
+def test_golden_cfg0_fp32():
+    g = golden("scan_cfg0_f32.npz")
+    inp = _golden_inputs(g, torch.float32)
+    Y, fin, grads = run_b200_fwd_bwd(inp, int(g["chunk_size"]), with_final_grad=False)
+    Yo, fino, go = oracle_fwd_bwd(inp, with_final_grad=False)
+    assert rel_err(to_np(Y), Yo) < TOL_F32 and rel_err(to_np(fin), fino) < TOL_F32
+    for name in ("dU", "dM", "dK", "dB", "dC"):
+        assert rel_err(to_np(grads[name]), go[name]) < TOL_F32, name
+        # against the reference's own fp32 numbers (which carry fp32 noise themselves)
+        assert rel_err(to_np(grads[name]), g[name]) < 3e-5, name
+    assert rel_err(to_np(Y), g["Y"]) < 1e-5
+
+
+def test_golden_bf16():
+    g = golden("scan_bf16.npz")
+    inp = _golden_inputs(g, torch.bfloat16)
+    Y, fin, grads = run_b200_fwd_bwd(inp, int(g["chunk_size"]))
+    assert rel_err(to_np(Y), g["Y"]) < TOL_HALF
+    assert rel_err(to_np(fin), g["final_state"]) < TOL_HALF
+    for name in ("dU", "dM", "dK", "dB", "dC"):
+        assert rel_err(to_np(grads[name]), g[name]) < TOL_HALF, name
+
+
+CASES = [
+    # b, h, T, N, P, L, dtype, streaming, with_init, dist
+    (1, 2, 1, 4, 8, 16, torch.float32, True, True, "tests"),       # single token
+    (2, 2, 50, 5, 7, 16, torch.float32, True, True, "tests"),      # odd sizes, ragged tail
+    (1, 3, 100, 16, 32, 32, torch.float32, False, True, "tests"),
+    (2, 2, 130, 24, 64, 64, torch.float32, True, False, "tests"),
+    (1, 2, 256, 16, 32, 128, torch.float32, True, True, "tests"),
+    (1, 2, 300, 64, 64, 64, torch.bfloat16, True, True, "tests"),
+    (1, 2, 384, 128, 64, 128, torch.bfloat16, False, False, "cfg2"),
+    (2, 2, 256, 128, 64, 64, torch.bfloat16, True, True, "cfg2"),
+    (1, 2, 200, 32, 64, 64, torch.float16, True, True, "tests"),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: f"b{c[0]}h{c[1]}T{c[2]}N{c[3]}P{c[4]}L{c[5]}{str(c[6])[6:]}")
+def test_seeded_parity_against_oracle(case):
+    b, h, T, N, P, L, dtype, streaming, with_init, dist = case
+    inp = make_scan_inputs(b, h, T, N, P, dtype, seed=T + N, streaming=streaming, with_init=with_init,
+                           dist=dist)
+    Y, fin, grads = run_b200_fwd_bwd(inp, L)
+    Yo, fino, go = oracle_fwd_bwd(inp)
+    tol = TOL_F32 if dtype == torch.float32 else TOL_HALF
+    errs = {"Y": rel_err(to_np(Y), Yo), "final": rel_err(to_np(fin), fino)}
+    for name in SCAN_GRADS:
+        if grads[name] is not None:
+            errs[name] = rel_err(to_np(grads[name]), go[name])
+    bad = {k: v for k, v in errs.items() if not v < tol}
+    assert not bad, f"tolerance {tol}: {errs}"
+
+
+def test_segment_chaining_equals_single_pass():
+    """Two chained calls through the carried state reproduce one call
+    (reference tests/test_v2x2ssd_cute.py:818-929)."""
+    import slinoss_b200 as sb
+
+    inp = make_scan_inputs(1, 2, 192, 16, 32, torch.float32, seed=5, streaming=True, with_init=True)
+    full = sb.v2x2ssd_b200(inp["U"], inp["M"], inp["K"], inp["B"], inp["C"], chunk_size=32,
+                           initial_states=inp["initial_states"], B_prev=inp["B_prev"],
+                           U_prev=inp["U_prev"], return_state=True)
+    cut = 80  # not a multiple of the chunk
+    sl = lambda t, a, b_: t[:, :, a:b_].contiguous()
+    y1, s1, b1, u1 = sb.v2x2ssd_b200(*(sl(inp[k], 0, cut) for k in "UMKBC"), chunk_size=32,
+                                     initial_states=inp["initial_states"], B_prev=inp["B_prev"],
+                                     U_prev=inp["U_prev"], return_state=True)
+    y2, s2, b2, u2 = sb.v2x2ssd_b200(*(sl(inp[k], cut, 192) for k in "UMKBC"), chunk_size=32,
+                                     initial_states=s1, B_prev=b1, U_prev=u1, return_state=True)
+    assert rel_err(to_np(torch.cat([y1, y2], dim=2)), to_np(full[0])) < TOL_F32
+    assert rel_err(to_np(s2), to_np(full[1])) < TOL_F32
+    assert torch.equal(b2, full[2]) and torch.equal(u2, full[3])
+
+
+def test_bitwise_repeatable():
+    inp = make_scan_inputs(1, 2, 256, 64, 64, torch.bfloat16, seed=9, streaming=True, with_init=True)
+    a = run_b200_fwd_bwd(inp, 64)
+    b = run_b200_fwd_bwd(inp, 64)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    for name in SCAN_GRADS:
+        assert torch.equal(a[2][name], b[2][name]), name
+
+
+def test_no_grad_and_empty_sequence():
+    import slinoss_b200 as sb
+
+    inp = make_scan_inputs(1, 2, 64, 8, 16, torch.float32, seed=3)
+    with torch.no_grad():
+        y = sb.v2x2ssd_b200(inp["U"], inp["M"], inp["K"], inp["B"], inp["C"], chunk_size=32)
+    Yo, _, _ = oracle_fwd_bwd(inp)
+    assert rel_err(to_np(y), Yo) < TOL_F32
+    e = lambda t: t[:, :, :0].contiguous()
+    out = sb.v2x2ssd_b200(e(inp["U"]), e(inp["M"]), e(inp["K"]), e(inp["B"]), e(inp["C"]), chunk_size=32,
+                          return_state=True)
+    assert out[0].shape == (1, 2, 0, 16) and float(out[1].abs().sum()) == 0.0
+
+
+def test_backend_object_matches_op():
+    import slinoss_b200 as sb
+
+    inp = make_scan_inputs(1, 2, 96, 16, 32, torch.bfloat16, seed=4, streaming=True, with_init=True)
+    be = sb.B200ScanBackend()
+    st = sb.ScanState(state=inp["initial_states"], b_prev=inp["B_prev"], u_prev=inp["U_prev"])
+    y, nxt = be(sb.ScanInputs(inp["U"], inp["M"], inp["K"], inp["B"], inp["C"]), chunk_size=32, state=st)
+    ref = sb.v2x2ssd_b200(inp["U"], inp["M"], inp["K"], inp["B"], inp["C"], chunk_size=32,
+                          initial_states=inp["initial_states"], B_prev=inp["B_prev"],
+                          U_prev=inp["U_prev"], return_state=True)
+    assert torch.equal(y, ref[0]) and torch.equal(nxt.state, ref[1])
+    assert nxt.state.dtype == torch.bfloat16 and nxt.b_prev.shape == (1, 2, 32)
