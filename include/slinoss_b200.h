@@ -113,6 +113,21 @@ int slx_state_passing_bwd(int32_t batch_heads, int32_t n_chunks, int32_t P,
                           float *d_initial /*[opt]*/, float *zdot,
                           float *zdot_partials /* workspace */, void *stream);
 
+/* Per-chunk backward given d_inc (from slx_state_passing_bwd) and zdot: writes
+ * dU, dB, dC (activation dtype; the last row of every chunk still lacks the
+ * carry of the following chunk), dM, dK (fp32) and the carries
+ * carryB (BH,NC,2N), carryU (BH,NC,P) fp32: the gradient each chunk sends to the
+ * token before it.  Replaces the chunk_scan and chunk_increment backward
+ * kernels of cute/kernels/bwd/__init__.py:930-1042 (scan_db, scan_dcdr,
+ * scan_param, scan_du, inc_db, inc_boundary, inc_param, inc_du). */
+int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M,
+                       const float *K, const void *B, const void *C,
+                       const float *B_prev /*[opt]*/, const float *U_prev /*[opt]*/,
+                       const float *chunk_starts, const float *d_inc,
+                       const float *zdot, const void *dY, void *dU, float *dM,
+                       float *dK, void *dB, void *dC, float *carryB,
+                       float *carryU, void *stream);
+
 /* Full backward of the scan: what torch.autograd computes through
  * reference.py:1195; replaces cute/kernels/bwd/__init__.py:1310
  * v2x2ssd_bwd_stateful_cute.  Gradients dU,dB,dC in the activation dtype;

@@ -261,6 +261,25 @@ int slx_state_passing_bwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const fl
                           zdot_partials, as_stream(stream));
 }
 
+int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
+                       const void *C, const float *B_prev, const float *U_prev, const float *chunk_starts,
+                       const float *d_inc, const float *zdot, const void *dY, void *dU, float *dM, float *dK,
+                       void *dB, void *dC, float *carryB, float *carryU, void *stream) {
+  ScanDims d;
+  int rc = check_shape(s, &d);
+  if (rc) return rc;
+  SLX_REQUIRE(U && M && K && B && C && chunk_starts && d_inc && zdot && dY && dU && dM && dK && dB && dC && carryB &&
+                  carryU,
+              SLX_E_NULL, "chunk_scan_bwd: NULL tensor");
+  SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
+  SLX_DISPATCH_T(s->dtype, {
+    ScanBwdArgs<T_> a{(const T_ *)U, (const T_ *)B, (const T_ *)C, (const T_ *)dY, M, K, chunk_starts, d_inc, zdot,
+                      B_prev, U_prev, (T_ *)dU, (T_ *)dB, (T_ *)dC, dM, dK, carryB, carryU, d};
+    SLX_DISPATCH_L(d.L, rc = (launch_scan_bwd<T_, L_>(d, a, as_stream(stream))));
+  });
+  return rc;
+}
+
 int slx_v2x2ssd_bwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
                     const void *C, const float *B_prev, const float *U_prev, const float *chunk_starts,
                     const float *m_chunk, const float *final_state, const void *dY, const float *d_final, void *dU,
@@ -290,11 +309,10 @@ int slx_v2x2ssd_bwd(const slx_scan_shape *s, const void *U, const float *M, cons
   rc = launch_state_bwd(d.BH, d.NC, d.P, d.N, d_inc, m_chunk, chunk_starts, final_state, d_final, d_inc, d_initial,
                         zdot, partials, st);
   if (rc) return rc;
+  rc = slx_chunk_scan_bwd(s, U, M, K, B, C, B_prev, U_prev, chunk_starts, d_inc, zdot, dY, dU, dM, dK, dB, dC, carryB,
+                          carryU, stream);
+  if (rc) return rc;
   SLX_DISPATCH_T(s->dtype, {
-    ScanBwdArgs<T_> a{(const T_ *)U, (const T_ *)B, (const T_ *)C, (const T_ *)dY, M, K, chunk_starts, d_inc, zdot,
-                      B_prev, U_prev, (T_ *)dU, (T_ *)dB, (T_ *)dC, dM, dK, carryB, carryU, d};
-    SLX_DISPATCH_L(d.L, rc = (launch_scan_bwd<T_, L_>(d, a, st)));
-    if (rc) return rc;
     carry_fixup_kernel<T_><<<dim3(d.NC, d.BH), 128, 0, st>>>(carryB, carryU, (T_ *)dB, (T_ *)dU, dB_prev, dU_prev,
                                                               d.T, d.P, d.D, d.L, d.NC);
     rc = check_launch("carry_fixup");

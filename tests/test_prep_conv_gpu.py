@@ -113,7 +113,7 @@ def test_prep_seeded_vs_oracle(dtype, N, P, H, b, T):
     assert rel_err(_np(grads[10]), dscale[:, :2]) < 3e-4
     assert rel_err(_np(grads[11]), dscale[:, 2:]) < 3e-4
     # deterministic reductions: a second run is bitwise equal
-    _, grads2 = _run_prep(v0, p0.contiguous(), c0, pars, hp, H, N, P, gouts)
+    _, grads2 = _run_prep(value.detach(), params.detach().contiguous(), bc.detach(), pars, hp, H, N, P, gouts)
     for a_, b_ in zip(grads, grads2):
         assert torch.equal(a_, b_)
 
