@@ -207,6 +207,17 @@ int slx_cconv1d_bwd(const slx_conv_shape *s, const void *x, const void *weight,
                     float *dbias, float *dstate, void *workspace,
                     size_t workspace_bytes, void *stream);
 
+/* ---- diagnostics ----------------------------------------------------------- */
+
+/* Self-test of the tcgen05 tile engine (no counterpart in the reference): one
+ * CTA computes a small bf16 product with fp32 accumulation in tensor memory.
+ * mode 0: C[128x128] = A[128x64] B[128x64]^T;  mode 1: C[128x64] = A[128x128]
+ * B[128x64];  mode 2: C[128x64] = A[128x128]^T B[128x64];  mode 3: C[128x64] =
+ * A[128x64] B[64x64]^T.  A, B row-major bf16; *status (device int) becomes 1 if
+ * a bounded wait ran out. */
+int slx_umma_selftest(int mode, const void *A, const void *B, float *C,
+                      int *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

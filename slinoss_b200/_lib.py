@@ -56,6 +56,7 @@ SIGNATURES = {
     "slx_scanprep_fwd": (c_int32, [POINTER(PrepShape)] + [_P] * 11),
     "slx_scanprep_bwd_workspace_bytes": (c_size_t, [POINTER(PrepShape)]),
     "slx_scanprep_bwd": (c_int32, [POINTER(PrepShape)] + [_P] * 15 + [c_size_t, _P]),
+    "slx_umma_selftest": (c_int32, [c_int32] + [_P] * 5),
     "slx_cconv1d_fwd": (c_int32, [POINTER(ConvShape)] + [_P] * 7),
     "slx_cconv1d_bwd_workspace_bytes": (c_size_t, [POINTER(ConvShape)]),
     "slx_cconv1d_bwd": (c_int32, [POINTER(ConvShape)] + [_P] * 11 + [c_size_t, _P]),

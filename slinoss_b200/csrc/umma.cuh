@@ -1,0 +1,167 @@
+// Blackwell (sm_100a) tensor-core tile primitives in inline PTX: tcgen05.mma
+// with shared-memory operand descriptors, TMEM allocation and loads, mbarrier
+// completion with bounded waits.
+//
+// Shared-memory operand tiles are always [R rows][64 halfs] with 128-byte rows,
+// stored with the 128-byte swizzle (16-byte chunk index XOR row%8) at a
+// 1024-byte aligned base.  Such a tile is, without any data movement,
+//   * a K-major operand   (rows = M/N index, the 64 columns = 4 K-steps of 16), or
+//   * an MN-major operand (rows = K index, the 64 columns = 64 M/N indices).
+// Wider matrices are split into 64-column blocks, each one such tile.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace slx {
+namespace umma {
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- descriptors ------------------------------------------------------------
+// 64-bit shared-memory matrix descriptor, SWIZZLE_128B, sm_100 version field.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= static_cast<uint64_t>(1) << 46;  // descriptor version (Blackwell)
+  d |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
+  return d;
+}
+// K-major view of a [R][64] tile: K-step kk (16 halfs = 32 bytes) of the block.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_saddr, int kk) {
+  return make_desc(tile_saddr + 32u * kk, 16u, 1024u);
+}
+// MN-major view: K-step kk = rows [16kk, 16kk+16); MN blocks of 64 are
+// block_stride_bytes apart (irrelevant when the MN extent is 64).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_saddr, int kk, uint32_t block_stride_bytes) {
+  return make_desc(tile_saddr + 2048u * kk, block_stride_bytes, 1024u);
+}
+
+// 32-bit instruction descriptor for kind::f16 with fp32 accumulation.
+// fmt: 0 = fp16 operands, 1 = bf16 operands.
+__host__ __device__ constexpr uint32_t make_idesc(int M, int N, bool a_mn_major, bool b_mn_major, int fmt) {
+  return (1u << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) |
+         ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+         (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+template <typename T>
+struct HalfFmt;
+template <>
+struct HalfFmt<__half> {
+  static constexpr int value = 0;
+};
+template <>
+struct HalfFmt<__nv_bfloat16> {
+  static constexpr int value = 1;
+};
+
+// ---- issue / completion -------------------------------------------------------
+// D[tmem] (+)= A * B, issued by ONE thread.
+__device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on an mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void commit(uint32_t mbar_saddr) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar_saddr)
+               : "memory");
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// make generic-proxy shared-memory writes visible to the tensor-core (async) proxy
+__device__ __forceinline__ void fence_smem_to_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_init(uint32_t mbar_saddr, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar_saddr), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+// Bounded wait: gives up after `max_tries` polls (each poll itself blocks for a
+// hardware-defined short time) and reports failure instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait(uint32_t mbar_saddr, uint32_t parity, int max_tries = 1 << 20) {
+  for (int i = 0; i < max_tries; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(mbar_saddr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+// ---- tensor memory ----------------------------------------------------------------
+// One full warp allocates `ncols` (power of two >= 32) columns; the base address
+// is written to *slot (shared memory).
+__device__ __forceinline__ void tmem_alloc(uint32_t *slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(ncols) : "memory");
+}
+
+// Each thread of the warp reads 32 consecutive fp32 columns of its own lane
+// (lane = 32*(warp%4) + laneid must be encoded in taddr bits 31..16 by the caller).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int lane, int col) {
+  return base + (static_cast<uint32_t>(lane) << 16) + static_cast<uint32_t>(col);
+}
+
+// ---- swizzled shared-memory tile access -----------------------------------------------
+// byte offset of 16-byte chunk j (0..7) of row r inside a [R][64] swizzled tile
+__device__ __forceinline__ uint32_t swz_off(int r, int j) {
+  return static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(j ^ (r & 7)) << 4);
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, __nv_bfloat16) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, __half) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+__device__ __forceinline__ float2 unpack2(uint32_t w, __nv_bfloat16) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&w));
+}
+__device__ __forceinline__ float2 unpack2(uint32_t w, __half) {
+  return __half22float2(*reinterpret_cast<__half2 *>(&w));
+}
+
+}  // namespace umma
+}  // namespace slx
