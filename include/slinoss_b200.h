@@ -209,6 +209,17 @@ int slx_cconv1d_bwd(const slx_conv_shape *s, const void *x, const void *weight,
 
 /* ---- diagnostics ----------------------------------------------------------- */
 
+/* Half inputs with chunk 128, P 64 and 2N in {64,128,192,256} run on the
+ * tcgen05 tensor-core kernels; everything else, and everything after
+ * slx_set_tensor_path(0), runs on the fp32-exact CUDA-core kernels.  Returns the
+ * previous setting.  (Process-wide switch for tests; no reference counterpart.) */
+int slx_set_tensor_path(int enable);
+
+/* Synchronising read-and-clear of the device status word of the tensor-core
+ * kernels: *host_out != 0 means a bounded wait on an MMA completion barrier ran
+ * out and the affected launch produced undefined values. */
+int slx_read_tc_status(int *host_out);
+
 /* Self-test of the tcgen05 tile engine (no counterpart in the reference): one
  * CTA computes a small bf16 product with fp32 accumulation in tensor memory.
  * mode 0: C[128x128] = A[128x64] B[128x64]^T;  mode 1: C[128x64] = A[128x128]

@@ -56,6 +56,8 @@ SIGNATURES = {
     "slx_scanprep_fwd": (c_int32, [POINTER(PrepShape)] + [_P] * 11),
     "slx_scanprep_bwd_workspace_bytes": (c_size_t, [POINTER(PrepShape)]),
     "slx_scanprep_bwd": (c_int32, [POINTER(PrepShape)] + [_P] * 15 + [c_size_t, _P]),
+    "slx_set_tensor_path": (c_int32, [c_int32]),
+    "slx_read_tc_status": (c_int32, [POINTER(c_int32)]),
     "slx_umma_selftest": (c_int32, [c_int32] + [_P] * 5),
     "slx_cconv1d_fwd": (c_int32, [POINTER(ConvShape)] + [_P] * 7),
     "slx_cconv1d_bwd_workspace_bytes": (c_size_t, [POINTER(ConvShape)]),
@@ -107,3 +109,17 @@ def check(status: int, what: str) -> None:
             raise TypeError(f"{what}: {msg}")
         raise ValueError(f"{what}: {msg}")
     raise RuntimeError(f"{what}: CUDA error {status}: {msg}")
+
+
+def set_tensor_path(enable: bool) -> bool:
+    """Process-wide switch between the tcgen05 kernels (default, where a shape is
+    eligible) and the fp32-exact CUDA-core kernels.  Returns the previous value."""
+    return bool(lib().slx_set_tensor_path(1 if enable else 0))
+
+
+def read_tc_status() -> int:
+    """Synchronising read-and-clear of the tensor-core kernels' status word
+    (non-zero: a bounded completion wait ran out)."""
+    out = c_int32(0)
+    check(lib().slx_read_tc_status(ctypes.byref(out)), "read_tc_status")
+    return int(out.value)

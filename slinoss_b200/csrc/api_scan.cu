@@ -4,6 +4,7 @@
 #include <cstdio>
 
 #include "scan_simt.cuh"
+#include "scan_tc.cuh"
 #include "state_passing.cuh"
 
 namespace slx {
@@ -116,6 +117,27 @@ static int launch_scan_bwd(const ScanDims &d, const ScanBwdArgs<T> &a, cudaStrea
   return check_launch("chunk_scan_bwd");
 }
 
+// ---- tensor-core path selection ----------------------------------------------------
+static int g_use_tc = 1;  // 0 forces the fp32-exact CUDA-core kernels for every dtype
+
+static bool tc_eligible(const ScanDims &d, int dtype) {
+  return g_use_tc && (dtype == SLX_BF16 || dtype == SLX_F16) && d.L == kTcL && d.P == kTcP && d.D % 64 == 0 &&
+         d.D >= 64 && d.D <= 256;
+}
+
+template <typename T>
+static int launch_scan_fwd_tc(const ScanDims &d, const void *U, const float *M, const float *K, const void *B,
+                              const void *C, const float *starts, const float *Bprev, const float *Uprev, void *Y,
+                              cudaStream_t st) {
+  ScanFwdArgs<T> a{(const T *)U, (const T *)B, (const T *)C, M, K, starts, Bprev, Uprev, (T *)Y, nullptr, d};
+  auto kern = chunk_scan_fwd_tc_kernel<T>;
+  size_t smem = scan_fwd_tc_smem_bytes();
+  int rc = set_smem(kern, smem);
+  if (rc) return rc;
+  kern<<<dim3(d.NC, d.BH), kTcThreads, smem, st>>>(a);
+  return check_launch("chunk_scan_fwd_tc");
+}
+
 static int launch_state_fwd(int BH, int NC, int P, int N, const float *inc, const float *m_chunk, const float *init,
                             float *starts, float *final_state, cudaStream_t st) {
   const int elems = P * 2 * N;
@@ -185,6 +207,21 @@ using namespace slx;
 extern "C" {
 
 int slx_abi_version(void) { return SLX_ABI_VERSION; }
+
+int slx_set_tensor_path(int enable) {
+  int old = g_use_tc;
+  g_use_tc = enable ? 1 : 0;
+  return old;
+}
+
+int slx_read_tc_status(int *host_out) {
+  SLX_REQUIRE(host_out != nullptr, SLX_E_NULL, "read_tc_status: NULL pointer");
+  int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_tc_status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+  if (e != cudaSuccess) return fail((int)e, "read_tc_status: %s", cudaGetErrorString(e));
+  return SLX_OK;
+}
 const char *slx_last_error_string(void) { return g_err; }
 
 int slx_chunk_increment_fwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
@@ -215,6 +252,11 @@ int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M, c
   if (rc) return rc;
   SLX_REQUIRE(U && M && K && B && C && chunk_starts && Y, SLX_E_NULL, "chunk_scan_fwd: NULL tensor");
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
+  if (tc_eligible(d, s->dtype)) {
+    if (s->dtype == SLX_BF16)
+      return launch_scan_fwd_tc<__nv_bfloat16>(d, U, M, K, B, C, chunk_starts, B_prev, U_prev, Y, as_stream(stream));
+    return launch_scan_fwd_tc<__half>(d, U, M, K, B, C, chunk_starts, B_prev, U_prev, Y, as_stream(stream));
+  }
   SLX_DISPATCH_T(s->dtype, SLX_DISPATCH_L(d.L, rc = (launch_scan_fwd<T_, L_>(d, U, M, K, B, C, chunk_starts, B_prev,
                                                                              U_prev, Y, as_stream(stream)))));
   return rc;

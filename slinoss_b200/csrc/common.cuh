@@ -50,10 +50,10 @@ __device__ __forceinline__ float2 cscale(float2 a, float s) { return make_float2
 // ph[t] = normalised prod_{tau<=t} m_tau/|m_tau|.  Tokens >= valid act as m = 1.
 // Executed by warp 0 of the CTA; results land in shared memory (lp, ph of
 // length L) and the caller synchronises.  An exactly-zero |m| sets *bad_flag.
-__device__ __forceinline__ void chunk_prefix_warp0(const float *__restrict__ Mchunk, int L, int valid,
-                                                   float *lp, float2 *ph, float2 *mraw, int *bad_flag) {
+__device__ __forceinline__ void chunk_prefix_warp(int run_warp, const float *__restrict__ Mchunk, int L, int valid,
+                                                  float *lp, float2 *ph, float2 *mraw, int *bad_flag) {
   const int lane = threadIdx.x & 31;
-  if ((threadIdx.x >> 5) != 0) return;
+  if ((int)(threadIdx.x >> 5) != run_warp) return;
   const int per = (L + 31) / 32;
   const int t0 = lane * per;
   float lsum = 0.f;
@@ -106,6 +106,11 @@ __device__ __forceinline__ void chunk_prefix_warp0(const float *__restrict__ Mch
       lp[t] += lex;
     }
   }
+}
+
+__device__ __forceinline__ void chunk_prefix_warp0(const float *__restrict__ Mchunk, int L, int valid, float *lp,
+                                                   float2 *ph, float2 *mraw, int *bad_flag) {
+  chunk_prefix_warp(0, Mchunk, L, valid, lp, ph, mraw, bad_flag);
 }
 
 }  // namespace slx

@@ -1,0 +1,312 @@
+// Tensor-core (tcgen05 / TMEM) chunk kernels of the v2x2ssd scan for half
+// inputs with fp32 state: chunk length 128, head dim 64, state width D = 2N a
+// multiple of 64 up to 256.  One CTA per (chunk, batch*head).
+//
+// Same merged-tap formulation as scan_simt.cuh.  Operands are rotated/weighted on
+// CUDA cores (fp32), rounded to the activation dtype and written into swizzled
+// [rows][64] shared-memory tiles that tcgen05.mma consumes in place; all
+// accumulators live in tensor memory and are read back once per tile.
+#pragma once
+
+#include "scan_simt.cuh"
+#include "umma.cuh"
+
+namespace slx {
+
+__device__ int g_tc_status = 0;  // becomes non-zero when a bounded wait ran out
+
+constexpr int kTcL = 128;
+constexpr int kTcP = 64;
+constexpr int kTcThreads = 256;
+
+// coef * (4 packed complex values) -> 4 packed complex values in T
+template <typename T>
+__device__ __forceinline__ uint4 rotate_chunk(uint4 raw, float2 coef) {
+  const uint32_t *w = reinterpret_cast<const uint32_t *>(&raw);
+  uint4 out;
+  uint32_t *o = reinterpret_cast<uint32_t *>(&out);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 v = umma::unpack2(w[i], T());
+    float2 r = cmul(coef, v);
+    o[i] = umma::pack2(r.x, r.y, T());
+  }
+  return out;
+}
+// acc += sum_i conj(a_i) * b_i over the 4 packed complex values of two chunks
+template <typename T>
+__device__ __forceinline__ void cdot_chunk(uint4 a, uint4 b, float2 &acc) {
+  const uint32_t *wa = reinterpret_cast<const uint32_t *>(&a);
+  const uint32_t *wb = reinterpret_cast<const uint32_t *>(&b);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 x = umma::unpack2(wa[i], T()), y = umma::unpack2(wb[i], T());
+    acc.x = fmaf(x.x, y.x, fmaf(x.y, y.y, acc.x));
+    acc.y = fmaf(x.x, y.y, fmaf(-x.y, y.x, acc.y));
+  }
+}
+__device__ __forceinline__ float2 octet_sum(float2 v) {  // sum over the 8 lanes that share a tile row
+#pragma unroll
+  for (int off = 4; off > 0; off >>= 1) {
+    v.x += __shfl_xor_sync(0xffffffffu, v.x, off);
+    v.y += __shfl_xor_sync(0xffffffffu, v.y, off);
+  }
+  return v;
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float *v) {
+  uint4 out;
+  out.x = umma::pack2(v[0], v[1], T());
+  out.y = umma::pack2(v[2], v[3], T());
+  out.z = umma::pack2(v[4], v[5], T());
+  out.w = umma::pack2(v[6], v[7], T());
+  return out;
+}
+
+constexpr size_t scan_fwd_tc_smem_bytes() { return 1024 + 88 * 1024 + 12 * 1024; }
+
+// Forward chunk scan (replaces reference.py:1059 chunk_scan) on tensor cores.
+//   S  = Qbar kappa^T          (128 x 128, K = D)       tcgen05, fp32 in TMEM
+//   Yo = Qbar Z0^T             (128 x 64,  K = D)
+//   Yd = S' U                  (128 x 64,  K = 128),  S' = masked/decayed S (+ diagonal)
+//   Y  = Yd + exp(lp_t) Yo + sigma_t u_{-1}
+template <typename T>
+__global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFwdArgs<T> a) {
+  constexpr int L = kTcL, P = kTcP;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *base =
+      reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char *tQ = base;               // [128][64]  Qbar slab   (also the Y staging tile)
+  unsigned char *tK = base + 16384;       // [128][64]  kappa slab
+  unsigned char *tU = base + 32768;       // [128][64]  U
+  unsigned char *tS = base + 49152;       // 2 x [128][64]  S'
+  unsigned char *tZ = base + 81920;       // [64][64]   Z0 slab
+  float *lp = reinterpret_cast<float *>(base + 90112);  // 128
+  float2 *ph = reinterpret_cast<float2 *>(lp + L);      // 128 each from here
+  float2 *mraw = ph + L, *kc = mraw + L, *kp = kc + L, *gk = kp + L, *cbv = gk + L, *cbm = cbv + L;
+  float2 *bm1 = cbm + L;                                 // 128 (b_{-1}, all of D)
+  float *um1 = reinterpret_cast<float *>(bm1 + 128);     // 64
+  __shared__ uint64_t mbar;
+  __shared__ uint32_t tmem_slot;
+
+  const ScanDims d = a.d;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, bh = blockIdx.y;
+  const int t0 = c * L;
+  const int valid = min(L, d.T - t0);
+  const size_t tok0 = (size_t)bh * d.T + t0;
+  const int NB = d.D / 64;
+  const uint32_t mbar_s = umma::smem_u32(&mbar);
+
+  if (warp == 0) umma::tmem_alloc(&tmem_slot, 256);
+  if (tid == 32) {
+    umma::mbar_init(mbar_s, 1);
+    umma::fence_mbar_init();
+  }
+  chunk_prefix_warp(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, a.bad);
+  if (tid >= 128) {
+    int t = tid - 128;
+    float2 vp = make_float2(0.f, 0.f), vc = vp;
+    if (t < valid) {
+      float4 k4 = *reinterpret_cast<const float4 *>(a.K + (tok0 + t) * 4);
+      vp = make_float2(k4.x, k4.y);
+      vc = make_float2(k4.z, k4.w);
+    }
+    kp[t] = vp;
+    kc[t] = vc;
+  } else if (tid >= 64) {
+    int p = tid - 64;
+    float v = 0.f;
+    if (t0 > 0) v = to_f(a.U[(tok0 - 1) * P + p]);
+    else if (a.Uprev) v = a.Uprev[(size_t)bh * P + p];
+    um1[p] = v;
+  }
+  if (tid < d.N) {
+    float2 bv = make_float2(0.f, 0.f);
+    if (t0 > 0) bv = load_pair<T>(a.B + (tok0 - 1) * d.D + 2 * tid);
+    else if (a.Bprev) bv = *reinterpret_cast<const float2 *>(a.Bprev + (size_t)bh * d.D + 2 * tid);
+    bm1[tid] = bv;
+  }
+  // U tile: thread owns chunk j of rows r0 + 32 i
+  const int j = tid & 7, r0 = tid >> 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int r = r0 + 32 * i;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < valid) v = *reinterpret_cast<const uint4 *>(a.U + (tok0 + r) * P + 8 * j);
+    *reinterpret_cast<uint4 *>(tU + umma::swz_off(r, j)) = v;
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  if (tid < L) {
+    int t = tid;
+    float2 g = make_float2(0.f, 0.f);
+    if (t + 1 < L) g = cmulc(cadd(cmul(mraw[t + 1], kc[t]), kp[t + 1]), ph[t + 1]);  // gamma_t conj(phi_{t+1})
+    gk[t] = g;
+  }
+  __syncthreads();
+
+  const float *z0 = a.starts + ((size_t)bh * d.NC + c) * P * d.D;
+  const uint32_t sQ = umma::smem_u32(tQ), sK = umma::smem_u32(tK), sU = umma::smem_u32(tU), sS = umma::smem_u32(tS),
+                 sZ = umma::smem_u32(tZ);
+  constexpr int fmt = umma::HalfFmt<T>::value;
+  float2 acc_cb[4], acc_cbm[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc_cb[i] = acc_cbm[i] = make_float2(0.f, 0.f);
+  uint32_t phase = 0;
+  bool ok = true;
+
+  for (int sl = 0; sl < NB; ++sl) {
+    // raw loads of this slab into registers (overlap the previous slab's MMAs)
+    uint4 cr[4], br[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int r = r0 + 32 * i;
+      cr[i] = br[i] = make_uint4(0, 0, 0, 0);
+      if (r < valid) {
+        cr[i] = *reinterpret_cast<const uint4 *>(a.C + (tok0 + r) * d.D + sl * 64 + 8 * j);
+        br[i] = *reinterpret_cast<const uint4 *>(a.B + (tok0 + r) * d.D + sl * 64 + 8 * j);
+      }
+    }
+    float4 zr[2][2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      int q = tid + kTcThreads * k;
+      int p = q >> 3, jj = q & 7;
+      const float4 *src = reinterpret_cast<const float4 *>(z0 + (size_t)p * d.D + sl * 64 + 8 * jj);
+      zr[k][0] = src[0];
+      zr[k][1] = src[1];
+    }
+    if (sl > 0) {
+      ok = umma::mbar_wait(mbar_s, phase) && ok;  // previous slab's products are done: tiles are free
+      phase ^= 1;
+    }
+    // b_{-1} chunk of this slab (for the boundary score)
+    uint4 bm;
+    {
+      float tmp[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 v = bm1[sl * 32 + 4 * j + e];
+        tmp[2 * e] = v.x;
+        tmp[2 * e + 1] = v.y;
+      }
+      bm = pack8<T>(tmp);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int r = r0 + 32 * i;
+      *reinterpret_cast<uint4 *>(tQ + umma::swz_off(r, j)) = rotate_chunk<T>(cr[i], cconj(ph[r]));
+      *reinterpret_cast<uint4 *>(tK + umma::swz_off(r, j)) = rotate_chunk<T>(br[i], gk[r]);
+      cdot_chunk<T>(cr[i], br[i], acc_cb[i]);
+      cdot_chunk<T>(cr[i], bm, acc_cbm[i]);
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      int q = tid + kTcThreads * k;
+      int p = q >> 3, jj = q & 7;
+      float tmp[8] = {zr[k][0].x, zr[k][0].y, zr[k][0].z, zr[k][0].w, zr[k][1].x, zr[k][1].y, zr[k][1].z, zr[k][1].w};
+      *reinterpret_cast<uint4 *>(tZ + umma::swz_off(p, jj)) = pack8<T>(tmp);
+    }
+    umma::fence_smem_to_async();
+    __syncthreads();
+    if (tid == 0) {
+      umma::fence_after_sync();
+      const uint32_t id_s = umma::make_idesc(128, 128, false, false, fmt);
+      const uint32_t id_o = umma::make_idesc(128, 64, false, false, fmt);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        uint64_t da = umma::desc_kmajor(sQ, kk);
+        umma::mma_ss(tmem + 0, da, umma::desc_kmajor(sK, kk), id_s, (sl | kk) != 0);
+        umma::mma_ss(tmem + 128, da, umma::desc_kmajor(sZ, kk), id_o, (sl | kk) != 0);
+      }
+      umma::commit(mbar_s);
+    }
+  }
+  // per-row dots: cb_t = <c_t, b_t>, cbm_t = <c_t, b_{-1}>
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 s1 = octet_sum(acc_cb[i]), s2 = octet_sum(acc_cbm[i]);
+    if (j == 0) {
+      cbv[r0 + 32 * i] = s1;
+      cbm[r0 + 32 * i] = s2;
+    }
+  }
+  ok = umma::mbar_wait(mbar_s, phase) && ok;
+  phase ^= 1;
+  umma::fence_after_sync();
+  __syncthreads();
+
+  // ---- S -> S' (decay, causal mask, diagonal) -> bf16 A operand ----------------------
+  const int q4 = warp & 3, h = warp >> 2;
+  const int t = 32 * q4 + lane;
+  const float lpt = lp[t];
+  {
+    const float dg = kc[t].x * cbv[t].x - kc[t].y * cbv[t].y;  // Re(k^c_t <c_t,b_t>)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int c0 = 64 * h + 32 * half;
+      float v[32];
+      if (c0 <= 32 * q4 + 31) {
+        umma::tmem_ld32(umma::tmem_addr(tmem, 32 * q4, c0), v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          int s = c0 + i;
+          float x = 0.f;
+          if (s < t) x = v[i] * __expf(lpt - lp[s + 1]);
+          else if (s == t) x = dg;
+          v[i] = x;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        *reinterpret_cast<uint4 *>(tS + 16384 * h + umma::swz_off(t, 4 * half + k)) = pack8<T>(v + 8 * k);
+    }
+  }
+  umma::fence_smem_to_async();
+  umma::fence_before_sync();
+  __syncthreads();
+  if (tid == 0) {
+    umma::fence_after_sync();
+    const uint32_t id_y = umma::make_idesc(128, 64, false, true, fmt);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk)
+      umma::mma_ss(tmem + 192, umma::desc_kmajor(sS + 16384u * (kk >> 2), kk & 3), umma::desc_mnmajor(sU, kk, 0), id_y,
+                   kk != 0);
+    umma::commit(mbar_s);
+  }
+  ok = umma::mbar_wait(mbar_s, phase) && ok;
+  phase ^= 1;
+  umma::fence_after_sync();
+
+  // ---- Y = Yd + exp(lp_t) Yo + sigma_t u_{-1} -> staging tile -> global ---------------
+  {
+    float yo[32], yd[32];
+    umma::tmem_ld32(umma::tmem_addr(tmem, 32 * q4, 128 + 32 * h), yo);
+    umma::tmem_ld32(umma::tmem_addr(tmem, 32 * q4, 192 + 32 * h), yd);
+    const float el = __expf(lpt);
+    float2 w = cmul(cmul(cmulc(ph[t], ph[0]), kp[0]), cbm[t]);
+    const float sig = __expf(lpt - lp[0]) * w.x;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) yd[i] = fmaf(sig, um1[32 * h + i], fmaf(el, yo[i], yd[i]));
+#pragma unroll
+    for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4 *>(tQ + umma::swz_off(t, 4 * h + k)) = pack8<T>(yd + 8 * k);
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int r = r0 + 32 * i;
+    if (r < valid)
+      *reinterpret_cast<uint4 *>(a.Y + (tok0 + r) * P + 8 * j) = *reinterpret_cast<const uint4 *>(tQ + umma::swz_off(r, j));
+  }
+  if (!ok && tid == 0) atomicExch(&g_tc_status, 1);
+  if (warp == 0) umma::tmem_dealloc(tmem, 256);
+}
+
+}  // namespace slx

@@ -89,10 +89,12 @@ __device__ __forceinline__ void mbar_init(uint32_t mbar_saddr, uint32_t count) {
 }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
-// Bounded wait: gives up after `max_tries` polls (each poll itself blocks for a
-// hardware-defined short time) and reports failure instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait(uint32_t mbar_saddr, uint32_t parity, int max_tries = 1 << 20) {
-  for (int i = 0; i < max_tries; ++i) {
+// Bounded wait: gives up after about a second of SM clock and reports failure
+// instead of spinning forever (each try_wait poll blocks for a short
+// hardware-defined time by itself).
+__device__ __forceinline__ bool mbar_wait(uint32_t mbar_saddr, uint32_t parity) {
+  const long long t0 = clock64();
+  for (;;) {
     uint32_t done;
     asm volatile(
         "{\n\t"
@@ -104,8 +106,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar_saddr, uint32_t parity, 
         : "r"(mbar_saddr), "r"(parity)
         : "memory");
     if (done) return true;
+    if (clock64() - t0 > 2000000000LL) return false;
   }
-  return false;
 }
 
 // ---- tensor memory ----------------------------------------------------------------

@@ -1,0 +1,57 @@
+"""Tensor-core (tcgen05) scan kernels against the fp32-exact CUDA-core kernels and
+the CPU oracle, stage by stage, at the shapes the tensor path covers
+(chunk 128, P 64, 2N in {64..256}, half inputs)."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from gpu_util import SCAN_GRADS, make_scan_inputs, oracle_fwd_bwd, run_b200_fwd_bwd, to_np
+from util import rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _tensor_path_on():
+    import slinoss_b200 as sb
+
+    sb.set_tensor_path(True)
+    yield
+    sb.set_tensor_path(True)
+    assert sb.read_tc_status() == 0, "a bounded MMA-completion wait ran out"
+
+
+@pytest.mark.parametrize("N,T,dtype,streaming", [
+    (128, 384, torch.bfloat16, True),
+    (128, 300, torch.bfloat16, False),   # ragged last chunk
+    (64, 256, torch.float16, True),
+    (32, 128, torch.bfloat16, True),
+    (96, 200, torch.bfloat16, False),
+])
+def test_chunk_scan_stage_tc_vs_exact(N, T, dtype, streaming):
+    import slinoss_b200 as sb
+
+    inp = make_scan_inputs(2, 2, T, N, 64, dtype, seed=N + T, streaming=streaming, with_init=True, dist="cfg2")
+    kw = dict(B_prev=inp["B_prev"], U_prev=inp["U_prev"], chunk_size=128)
+    inc, mch = sb.chunk_increment_b200(inp["U"], inp["M"], inp["K"], inp["B"], **kw)
+    starts, _ = sb.state_passing_b200(inc, mch, initial_states=inp["initial_states"])
+    y_tc = sb.chunk_scan_b200(inp["U"], inp["M"], inp["K"], inp["B"], inp["C"], starts, **kw)
+    sb.set_tensor_path(False)
+    y_ex = sb.chunk_scan_b200(inp["U"], inp["M"], inp["K"], inp["B"], inp["C"], starts, **kw)
+    sb.set_tensor_path(True)
+    # both round Y to the half dtype; the tensor path also rounds its operands
+    assert rel_err(to_np(y_tc), to_np(y_ex)) < 1e-2
+    Yo, _, _ = oracle_fwd_bwd(inp)
+    assert rel_err(to_np(y_tc), Yo) < 2e-2
+
+
+@pytest.mark.parametrize("N,T,dtype", [(128, 512, torch.bfloat16), (64, 384, torch.float16)])
+def test_full_op_tc_vs_oracle(N, T, dtype):
+    inp = make_scan_inputs(2, 2, T, N, 64, dtype, seed=7, streaming=True, with_init=True, dist="cfg2")
+    Y, fin, grads = run_b200_fwd_bwd(inp, 128)
+    Yo, fino, go = oracle_fwd_bwd(inp)
+    errs = {"Y": rel_err(to_np(Y), Yo), "final": rel_err(to_np(fin), fino)}
+    errs.update({k: rel_err(to_np(grads[k]), go[k]) for k in SCAN_GRADS})
+    assert all(v < 2e-2 for v in errs.values()), errs
