@@ -138,6 +138,18 @@ static int launch_scan_fwd_tc(const ScanDims &d, const void *U, const float *M, 
   return check_launch("chunk_scan_fwd_tc");
 }
 
+template <typename T, int MODE>
+static int launch_outer_tc(const ScanDims &d, const void *A, const void *X, const float *M, const float *K,
+                           const float *Bprev, const float *Uprev, float *out, float *m_chunk, cudaStream_t st) {
+  OuterArgs<T> a{(const T *)A, (const T *)X, M, K, Bprev, Uprev, out, m_chunk, d};
+  auto kern = chunk_outer_tc_kernel<T, MODE>;
+  size_t smem = outer_tc_smem_bytes();
+  int rc = set_smem(kern, smem);
+  if (rc) return rc;
+  kern<<<dim3(d.NC, d.BH), kTcThreads, smem, st>>>(a);
+  return check_launch(MODE == 0 ? "chunk_increment_fwd_tc" : "chunk_scan_bwd_dz0_tc");
+}
+
 static int launch_state_fwd(int BH, int NC, int P, int N, const float *inc, const float *m_chunk, const float *init,
                             float *starts, float *final_state, cudaStream_t st) {
   const int elems = P * 2 * N;
@@ -231,6 +243,11 @@ int slx_chunk_increment_fwd(const slx_scan_shape *s, const void *U, const float 
   if (rc) return rc;
   SLX_REQUIRE(U && M && K && B && inc && m_chunk, SLX_E_NULL, "chunk_increment_fwd: NULL tensor");
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
+  if (tc_eligible(d, s->dtype)) {
+    if (s->dtype == SLX_BF16)
+      return launch_outer_tc<__nv_bfloat16, 0>(d, U, B, M, K, B_prev, U_prev, inc, m_chunk, as_stream(stream));
+    return launch_outer_tc<__half, 0>(d, U, B, M, K, B_prev, U_prev, inc, m_chunk, as_stream(stream));
+  }
   SLX_DISPATCH_T(s->dtype, SLX_DISPATCH_L(d.L, rc = (launch_outer<T_, L_, 0>(d, U, B, M, K, B_prev, U_prev, inc,
                                                                               m_chunk, as_stream(stream)))));
   return rc;
@@ -287,6 +304,12 @@ int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *
   int rc = check_shape(s, &d);
   if (rc) return rc;
   SLX_REQUIRE(M && C && dY && dZ0, SLX_E_NULL, "chunk_scan_bwd_dz0: NULL tensor");
+  if (tc_eligible(d, s->dtype)) {
+    if (s->dtype == SLX_BF16)
+      return launch_outer_tc<__nv_bfloat16, 1>(d, dY, C, M, nullptr, nullptr, nullptr, dZ0, nullptr,
+                                               as_stream(stream));
+    return launch_outer_tc<__half, 1>(d, dY, C, M, nullptr, nullptr, nullptr, dZ0, nullptr, as_stream(stream));
+  }
   SLX_DISPATCH_T(s->dtype, SLX_DISPATCH_L(d.L, rc = (launch_outer<T_, L_, 1>(d, dY, C, M, nullptr, nullptr, nullptr,
                                                                               dZ0, nullptr, as_stream(stream)))));
   return rc;

@@ -309,4 +309,141 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   if (warp == 0) umma::tmem_dealloc(tmem, 256);
 }
 
+// ---------------------------------------------------------------------------
+// out[p, d] = sum_t A[t, p] * (coef_t x_t)[d]  (+ boundary), computed transposed
+// on tensor cores: out^T (d x p) = Xop^T (d x t) * A (t x p), M = 128 state
+// columns per product, N = 64, K = 128 tokens.  MODE as chunk_outer_kernel:
+// 0 = chunk increment (A = U, x = B, writes m_chunk), 1 = dZ0 (A = dY, x = C).
+constexpr size_t outer_tc_smem_bytes() { return 1024 + 80 * 1024 + 8 * 1024; }
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kTcThreads, 2) chunk_outer_tc_kernel(OuterArgs<T> a) {
+  constexpr int L = kTcL, P = kTcP;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *base =
+      reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char *tA = base;            // [128][64]   U or dY
+  unsigned char *tX = base + 16384;    // 4 x [128][64] weighted B or C, one tile per 64 state columns
+  float *lp = reinterpret_cast<float *>(base + 81920);
+  float2 *ph = reinterpret_cast<float2 *>(lp + L);
+  float2 *mraw = ph + L, *coef = mraw + L;
+  float2 *bh1 = coef + L;                               // 128: weighted b_{-1}
+  float *um1 = reinterpret_cast<float *>(bh1 + 128);    // 64
+  __shared__ uint64_t mbar;
+  __shared__ uint32_t tmem_slot;
+
+  const ScanDims d = a.d;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, bh = blockIdx.y;
+  const int t0 = c * L;
+  const int valid = min(L, d.T - t0);
+  const size_t tok0 = (size_t)bh * d.T + t0;
+  const int NB = d.D / 64, NG = (NB + 1) / 2;
+  const uint32_t mbar_s = umma::smem_u32(&mbar);
+
+  if (warp == 0) umma::tmem_alloc(&tmem_slot, 128);
+  if (tid == 32) {
+    umma::mbar_init(mbar_s, 1);
+    umma::fence_mbar_init();
+  }
+  chunk_prefix_warp(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, nullptr);
+  const int j = tid & 7, r0 = tid >> 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int r = r0 + 32 * i;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < valid) v = *reinterpret_cast<const uint4 *>(a.A + (tok0 + r) * P + 8 * j);
+    *reinterpret_cast<uint4 *>(tA + umma::swz_off(r, j)) = v;
+  }
+  if (MODE == 0 && tid >= 192) {
+    int p = tid - 192;
+    float v = 0.f;
+    if (t0 > 0) v = to_f(a.A[(tok0 - 1) * P + p]);
+    else if (a.Uprev) v = a.Uprev[(size_t)bh * P + p];
+    um1[p] = v;
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  if (tid < L) {
+    const int t = tid;
+    float2 cf;
+    if (MODE == 0) {
+      float2 kcv = make_float2(0.f, 0.f), kpn = kcv;
+      if (t < valid) kcv = *reinterpret_cast<const float2 *>(a.K + (tok0 + t) * 4 + 2);
+      if (t + 1 < valid) kpn = *reinterpret_cast<const float2 *>(a.K + (tok0 + t + 1) * 4);
+      if (t + 1 < L) {
+        float2 gam = cadd(cmul(mraw[t + 1], kcv), kpn);
+        cf = cmul(cscale(cmulc(ph[L - 1], ph[t + 1]), __expf(lp[L - 1] - lp[t + 1])), gam);
+      } else {
+        cf = kcv;
+      }
+    } else {
+      cf = cscale(cconj(ph[t]), __expf(lp[t]));
+    }
+    coef[t] = cf;
+  } else if (MODE == 0 && tid - L < d.N) {
+    const int n = tid - L;
+    float2 k0p = make_float2(0.f, 0.f);
+    if (valid > 0) k0p = *reinterpret_cast<const float2 *>(a.K + tok0 * 4);
+    k0p = cmul(cscale(cmulc(ph[L - 1], ph[0]), __expf(lp[L - 1] - lp[0])), k0p);
+    float2 bv = make_float2(0.f, 0.f);
+    if (t0 > 0) bv = load_pair<T>(a.X + (tok0 - 1) * d.D + 2 * n);
+    else if (a.Bprev) bv = *reinterpret_cast<const float2 *>(a.Bprev + (size_t)bh * d.D + 2 * n);
+    bh1[n] = cmul(k0p, bv);
+  }
+  if (MODE == 0 && tid == 255) {
+    float2 acc = make_float2(1.f, 0.f);
+    for (int t = 0; t < L; ++t) acc = cmul(acc, mraw[t]);
+    *reinterpret_cast<float2 *>(a.m_chunk + ((size_t)bh * d.NC + c) * 2) = acc;
+  }
+  __syncthreads();
+  for (int sl = 0; sl < NB; ++sl) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int r = r0 + 32 * i;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < valid) v = *reinterpret_cast<const uint4 *>(a.X + (tok0 + r) * d.D + sl * 64 + 8 * j);
+      *reinterpret_cast<uint4 *>(tX + 16384 * sl + umma::swz_off(r, j)) = rotate_chunk<T>(v, coef[r]);
+    }
+  }
+  umma::fence_smem_to_async();
+  __syncthreads();
+  if (tid == 0) {
+    umma::fence_after_sync();
+    const uint32_t id = umma::make_idesc(128, 64, true, true, umma::HalfFmt<T>::value);
+    const uint32_t sA = umma::smem_u32(tA), sX = umma::smem_u32(tX);
+    for (int g = 0; g < NG; ++g)
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        umma::mma_ss(tmem + 64 * g, umma::desc_mnmajor(sX + 32768u * g, kk, 16384u), umma::desc_mnmajor(sA, kk, 0), id,
+                     kk != 0);
+    umma::commit(mbar_s);
+  }
+  const bool ok = umma::mbar_wait(mbar_s, 0);
+  umma::fence_after_sync();
+  const int q4 = warp & 3;
+  float *outc = a.out + ((size_t)bh * d.NC + c) * P * d.D;
+  for (int g = warp >> 2; g < NG; g += 2) {
+    const int dd = 128 * g + 32 * q4 + lane;
+    float v0[32], v1[32];
+    umma::tmem_ld32(umma::tmem_addr(tmem, 32 * q4, 64 * g), v0);
+    umma::tmem_ld32(umma::tmem_addr(tmem, 32 * q4, 64 * g + 32), v1);
+    if (dd < d.D) {
+      float bw = 0.f;
+      if (MODE == 0) bw = (dd & 1) ? bh1[dd >> 1].y : bh1[dd >> 1].x;
+#pragma unroll
+      for (int p = 0; p < 32; ++p) {
+        outc[(size_t)p * d.D + dd] = (MODE == 0) ? fmaf(um1[p], bw, v0[p]) : v0[p];
+        outc[(size_t)(p + 32) * d.D + dd] = (MODE == 0) ? fmaf(um1[p + 32], bw, v1[p]) : v1[p];
+      }
+    }
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  if (!ok && tid == 0) atomicExch(&g_tc_status, 1);
+  if (warp == 0) umma::tmem_dealloc(tmem, 128);
+}
+
 }  // namespace slx

@@ -55,3 +55,17 @@ def test_full_op_tc_vs_oracle(N, T, dtype):
     errs = {"Y": rel_err(to_np(Y), Yo), "final": rel_err(to_np(fin), fino)}
     errs.update({k: rel_err(to_np(grads[k]), go[k]) for k in SCAN_GRADS})
     assert all(v < 2e-2 for v in errs.values()), errs
+
+
+@pytest.mark.parametrize("N,T,dtype", [(128, 300, torch.bfloat16), (32, 256, torch.float16), (96, 128, torch.bfloat16)])
+def test_increment_stage_tc_vs_exact(N, T, dtype):
+    import slinoss_b200 as sb
+
+    inp = make_scan_inputs(2, 2, T, N, 64, dtype, seed=N, streaming=True, with_init=False, dist="cfg2")
+    kw = dict(B_prev=inp["B_prev"], U_prev=inp["U_prev"], chunk_size=128)
+    inc_tc, m_tc = sb.chunk_increment_b200(inp["U"], inp["M"], inp["K"], inp["B"], **kw)
+    sb.set_tensor_path(False)
+    inc_ex, m_ex = sb.chunk_increment_b200(inp["U"], inp["M"], inp["K"], inp["B"], **kw)
+    sb.set_tensor_path(True)
+    assert rel_err(to_np(m_tc), to_np(m_ex)) < 1e-6
+    assert rel_err(to_np(inc_tc), to_np(inc_ex)) < 5e-3
