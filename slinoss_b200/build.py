@@ -32,7 +32,7 @@ def _nvcc() -> str:
 
 
 def _newest_source_mtime() -> float:
-    files = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "slinoss_b200.h"]
+    files = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.inc")) + [PKG.parent / "include" / "slinoss_b200.h"]
     return max(f.stat().st_mtime for f in files)
 
 

@@ -2,9 +2,11 @@
 // no synchronisation).
 #include <cstdarg>
 #include <cstdio>
+#include <type_traits>
 
 #include "scan_simt.cuh"
 #include "scan_tc.cuh"
+#include "scan_tc_bwd.cuh"
 #include "state_passing.cuh"
 
 namespace slx {
@@ -148,6 +150,16 @@ static int launch_outer_tc(const ScanDims &d, const void *A, const void *X, cons
   if (rc) return rc;
   kern<<<dim3(d.NC, d.BH), kTcThreads, smem, st>>>(a);
   return check_launch(MODE == 0 ? "chunk_increment_fwd_tc" : "chunk_scan_bwd_dz0_tc");
+}
+
+template <typename T>
+static int launch_scan_bwd_tc(const ScanDims &d, const ScanBwdArgs<T> &a, cudaStream_t st) {
+  auto kern = chunk_scan_bwd_tc_kernel<T>;
+  size_t smem = scan_bwd_tc_smem_bytes();
+  int rc = set_smem(kern, smem);
+  if (rc) return rc;
+  kern<<<dim3(d.NC, d.BH), kTcThreads, smem, st>>>(a);
+  return check_launch("chunk_scan_bwd_tc");
 }
 
 static int launch_state_fwd(int BH, int NC, int P, int N, const float *inc, const float *m_chunk, const float *init,
@@ -337,9 +349,13 @@ int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M, c
                   carryU,
               SLX_E_NULL, "chunk_scan_bwd: NULL tensor");
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
+  const bool tc = tc_eligible(d, s->dtype);
   SLX_DISPATCH_T(s->dtype, {
     ScanBwdArgs<T_> a{(const T_ *)U, (const T_ *)B, (const T_ *)C, (const T_ *)dY, M, K, chunk_starts, d_inc, zdot,
                       B_prev, U_prev, (T_ *)dU, (T_ *)dB, (T_ *)dC, dM, dK, carryB, carryU, d};
+    if constexpr (!std::is_same<T_, float>::value) {
+      if (tc) return launch_scan_bwd_tc<T_>(d, a, as_stream(stream));
+    }
     SLX_DISPATCH_L(d.L, rc = (launch_scan_bwd<T_, L_>(d, a, as_stream(stream))));
   });
   return rc;

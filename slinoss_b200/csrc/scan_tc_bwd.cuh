@@ -1,0 +1,210 @@
+// Tensor-core per-chunk backward of the v2x2ssd scan (chunk 128, P 64, half
+// inputs, fp32 state).  Same mathematics as chunk_scan_bwd_kernel in
+// scan_simt.cuh; every contraction runs on tcgen05 with fp32 accumulators in
+// tensor memory.  One CTA (256 threads) per (chunk, batch*head), one CTA per SM.
+//
+// Tensor-memory map (fp32 columns):
+//   [  0,128)  G = dY U^T, then S = Qbar kappa^T (accumulated over state slabs)
+//   [128,192)  dU, increment path:  Bhat Lambda^T
+//   [192,256)  dq  (slab)   = dS' kappa + (e^lp dY) Z0
+//   [256,320)  X   (slab)   = dS'^T Qbar
+//   [320,384)  UL  (slab)   = U Lambda
+//   [384,448)  dU, score path:      S'^T dY
+//
+// The source token in front of the chunk (b_{-1}, u_{-1}) borrows key slot 127,
+// whose own merged-tap column is empty (no query follows the last token):
+//   dS'[t][127] = exp(lp_t - lp_0) dY_t.u_{-1},   kappa[127] = k^p_0 b_{-1} conj(phi_0)
+// so that row 127 of X is the column sum the carry gradient needs, the boundary
+// term of dq comes out of the same product, column 127 of S is the boundary
+// score and row 127 of S'^T dY is the dU carried to the previous token.
+#pragma once
+
+#include "scan_tc.cuh"
+
+namespace slx {
+
+constexpr size_t scan_bwd_tc_smem_bytes() { return 1024 + 144 * 1024 + 24 * 1024; }
+
+template <typename T>
+__global__ void __launch_bounds__(kTcThreads, 1) chunk_scan_bwd_tc_kernel(ScanBwdArgs<T> a) {
+  constexpr int L = kTcL, P = kTcP;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *base =
+      reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char *tdY = base;                // [t][p]
+  unsigned char *tdYe = base + 16384;       // [t][p]  exp(lp_t) dY
+  unsigned char *tU = base + 32768;         // [s][p]
+  unsigned char *tdS = base + 49152;        // 2 x [t][64 s]   dS', later S'
+  unsigned char *tQ = base + 81920;         // [t][d]  Qbar slab
+  unsigned char *tK = base + 98304;         // [s][d]  kappa slab
+  unsigned char *tBh = base + 114688;       // [s][d]  w_s b_s slab
+  unsigned char *tZ = base + 131072;        // [p][d]  Z0 slab        (8 KB)
+  unsigned char *tLm = base + 139264;       // [p][d]  Lambda slab    (8 KB)
+  float *lp = reinterpret_cast<float *>(base + 147456);
+  float *gd = lp + L;                        // G[t][t]
+  float *gm1 = gd + L;                       // dY_t . u_{-1}
+  float *um1 = gm1 + L;                      // 64
+  float *duc = um1 + 64;                     // 64  increment path of the carried dU
+  float2 *ph = reinterpret_cast<float2 *>(duc + 64);
+  float2 *mraw = ph + L, *kc = mraw + L, *kp = kc + L, *gam = kp + L, *gk = gam + L, *wco = gk + L, *sg1 = wco + L;
+  float2 *bc = sg1 + L, *bX = bc + L, *gA = bX + L, *gsum = gA + L;
+  float2 *bm1 = gsum + L;                    // 128  b_{-1}
+  float2 *ul1 = bm1 + 128;                   // 128  (u_{-1} . Lambda)[n]
+  float2 *misc = ul1 + 128;                  // [0] bLam(last row) [1] dk^p_0 [2] w_{-1} [3] p_{L-1}/p_0
+  float2 *half2sum = misc + 4;               // 3 x 128: partial dots of the second column half
+  __shared__ uint64_t mbar;
+  __shared__ uint32_t tmem_slot;
+
+  const ScanDims d = a.d;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, bh = blockIdx.y;
+  const int t0 = c * L;
+  const int valid = min(L, d.T - t0);
+  const size_t tok0 = (size_t)bh * d.T + t0;
+  const int NB = d.D / 64;
+  const uint32_t mbar_s = umma::smem_u32(&mbar);
+  constexpr int fmt = umma::HalfFmt<T>::value;
+
+  if (warp == 0) umma::tmem_alloc(&tmem_slot, 512);
+  if (tid == 32) {
+    umma::mbar_init(mbar_s, 1);
+    umma::fence_mbar_init();
+  }
+  chunk_prefix_warp(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, nullptr);
+  if (tid >= 128) {
+    int t = tid - 128;
+    float2 vp = make_float2(0.f, 0.f), vc = vp;
+    if (t < valid) {
+      float4 k4 = *reinterpret_cast<const float4 *>(a.K + (tok0 + t) * 4);
+      vp = make_float2(k4.x, k4.y);
+      vc = make_float2(k4.z, k4.w);
+    }
+    kp[t] = vp;
+    kc[t] = vc;
+    bX[t] = gA[t] = make_float2(0.f, 0.f);
+  } else if (tid >= 64) {
+    int p = tid - 64;
+    float v = 0.f;
+    if (t0 > 0) v = to_f(a.U[(tok0 - 1) * P + p]);
+    else if (a.Uprev) v = a.Uprev[(size_t)bh * P + p];
+    um1[p] = v;
+    duc[p] = 0.f;
+  } else if (tid < 4) {
+    misc[tid] = make_float2(0.f, 0.f);
+  }
+  if (tid < d.N) {
+    float2 bv = make_float2(0.f, 0.f);
+    if (t0 > 0) bv = load_pair<T>(a.B + (tok0 - 1) * d.D + 2 * tid);
+    else if (a.Bprev) bv = *reinterpret_cast<const float2 *>(a.Bprev + (size_t)bh * d.D + 2 * tid);
+    bm1[tid] = bv;
+  }
+  const int j = tid & 7, r0 = tid >> 3;
+  // raw dY, U tiles (dYe needs lp: second pass below)
+  uint4 dyr[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int r = r0 + 32 * i;
+    uint4 u = make_uint4(0, 0, 0, 0);
+    dyr[i] = u;
+    if (r < valid) {
+      u = *reinterpret_cast<const uint4 *>(a.U + (tok0 + r) * P + 8 * j);
+      dyr[i] = *reinterpret_cast<const uint4 *>(a.dY + (tok0 + r) * P + 8 * j);
+    }
+    *reinterpret_cast<uint4 *>(tU + umma::swz_off(r, j)) = u;
+    *reinterpret_cast<uint4 *>(tdY + umma::swz_off(r, j)) = dyr[i];
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  // exp(lp_t) dY and g_{-1}[t] = dY_t . u_{-1}
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int r = r0 + 32 * i;
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(&dyr[i]);
+    const float el = __expf(lp[r]);
+    float tmp[8], dot = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 v = umma::unpack2(w[e], T());
+      dot = fmaf(v.x, um1[8 * j + 2 * e], fmaf(v.y, um1[8 * j + 2 * e + 1], dot));
+      tmp[2 * e] = el * v.x;
+      tmp[2 * e + 1] = el * v.y;
+    }
+    *reinterpret_cast<uint4 *>(tdYe + umma::swz_off(r, j)) = pack8<T>(tmp);
+#pragma unroll
+    for (int off = 4; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+    if (j == 0) gm1[r] = dot;
+  }
+  if (tid < L) {
+    const int t = tid;
+    float2 g = make_float2(0.f, 0.f), w, s1 = g, gkv = g;
+    if (t + 1 < L) {
+      g = cadd(cmul(mraw[t + 1], kc[t]), kp[t + 1]);
+      gkv = cmulc(g, ph[t + 1]);
+      s1 = cscale(cmulc(ph[L - 1], ph[t + 1]), __expf(lp[L - 1] - lp[t + 1]));  // p_{L-1}/p_{t+1}
+      w = cmul(s1, g);
+    } else {
+      w = kc[t];
+      gkv = cmulc(kp[0], ph[0]);  // boundary slot: kappa[127] = k^p_0 b_{-1} conj(phi_0)
+    }
+    gam[t] = g;
+    gk[t] = gkv;
+    sg1[t] = s1;
+    wco[t] = w;
+  }
+  if (tid == 255) {
+    float2 s0 = cscale(cmulc(ph[L - 1], ph[0]), __expf(lp[L - 1] - lp[0]));  // p_{L-1}/p_0
+    misc[3] = s0;
+    misc[2] = cmul(s0, kp[0]);
+  }
+  umma::fence_smem_to_async();
+  __syncthreads();
+
+  const uint32_t sdY = umma::smem_u32(tdY), sdYe = umma::smem_u32(tdYe), sU = umma::smem_u32(tU),
+                 sdS = umma::smem_u32(tdS), sQ = umma::smem_u32(tQ), sK = umma::smem_u32(tK),
+                 sBh = umma::smem_u32(tBh), sZ = umma::smem_u32(tZ), sLm = umma::smem_u32(tLm);
+  uint32_t phase = 0;
+  bool ok = true;
+  const int q4 = warp & 3, h = warp >> 2;
+  const int row = 32 * q4 + lane;
+
+  // ---- G = dY U^T -> dS' ---------------------------------------------------------
+  if (tid == 0) {
+    umma::fence_after_sync();
+    const uint32_t id = umma::make_idesc(128, 128, false, false, fmt);
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk)
+      umma::mma_ss(tmem, umma::desc_kmajor(sdY, kk), umma::desc_kmajor(sU, kk), id, kk != 0);
+    umma::commit(mbar_s);
+  }
+  ok = umma::mbar_wait(mbar_s, phase) && ok;
+  phase ^= 1;
+  umma::fence_after_sync();
+  {
+    const float lpt = lp[row];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int c0 = 64 * h + 32 * half;
+      float v[32];
+      umma::tmem_ld32(umma::tmem_addr(tmem, 32 * q4, c0), v);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int s = c0 + i;
+        if (s == row) gd[row] = v[i];
+        float x = 0.f;
+        if (s < row) x = v[i] * __expf(lpt - lp[s + 1]);
+        if (s == L - 1) x = __expf(lpt - lp[0]) * gm1[row];  // boundary slot
+        v[i] = x;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        *reinterpret_cast<uint4 *>(tdS + 16384 * h + umma::swz_off(row, 4 * half + k)) = pack8<T>(v + 8 * k);
+    }
+  }
+  umma::fence_before_sync();
+  // (the slab loop's first barrier orders these stores and TMEM reads before the next products)
+#include "scan_tc_bwd_body.inc"
+}
+
+}  // namespace slx

@@ -69,3 +69,30 @@ def test_increment_stage_tc_vs_exact(N, T, dtype):
     sb.set_tensor_path(True)
     assert rel_err(to_np(m_tc), to_np(m_ex)) < 1e-6
     assert rel_err(to_np(inc_tc), to_np(inc_ex)) < 5e-3
+
+
+@pytest.mark.parametrize("N,T,dtype,streaming", [
+    (128, 384, torch.bfloat16, True),
+    (128, 200, torch.bfloat16, False),   # ragged last chunk
+    (32, 256, torch.float16, True),
+    (96, 128, torch.bfloat16, True),
+])
+def test_backward_tc_vs_exact_and_oracle(N, T, dtype, streaming):
+    """Tensor-core backward against the fp32-exact kernels (same half inputs) and the oracle."""
+    import slinoss_b200 as sb
+
+    inp = make_scan_inputs(2, 2, T, N, 64, dtype, seed=3 * N + T, streaming=streaming, with_init=True,
+                           dist="cfg2")
+    Y, fin, g_tc = run_b200_fwd_bwd(inp, 128)
+    sb.set_tensor_path(False)
+    Y2, fin2, g_ex = run_b200_fwd_bwd(inp, 128)
+    sb.set_tensor_path(True)
+    Yo, fino, go = oracle_fwd_bwd(inp)
+    errs_ex, errs_or = {}, {}
+    for k in SCAN_GRADS:
+        if g_tc[k] is None:
+            continue
+        errs_ex[k] = rel_err(to_np(g_tc[k]), to_np(g_ex[k]))
+        errs_or[k] = rel_err(to_np(g_tc[k]), go[k])
+    assert all(v < 2e-2 for v in errs_or.values()), ("oracle", errs_or, "exact", errs_ex)
+    assert all(v < 2e-2 for v in errs_ex.values()), ("exact", errs_ex)
