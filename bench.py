@@ -206,7 +206,7 @@ def main() -> int:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--chunk", type=int, default=64)
+    ap.add_argument("--chunk", type=int, default=128)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--T", type=int, default=HEADLINE["T"])
     ap.add_argument("--batch", type=int, default=HEADLINE["batch"])
@@ -358,7 +358,7 @@ def main() -> int:
         k_ms = e0.elapsed_time(e1) / reps
     flops = dense_flops_bwd_chunk(L, P, D) * BH * NC
     achieved = flops / (k_ms * 1e-3) / 1e12
-    roofline = dict(kernel="chunk_scan_bwd_kernel", bound="tensor", achieved=achieved, peak=peaks["tflops"],
+    roofline = dict(kernel="chunk_scan_bwd_tc_kernel" if L == 128 else "chunk_scan_bwd_kernel", bound="tensor", achieved=achieved, peak=peaks["tflops"],
                     unit="TFLOP/s", frac=achieved / peaks["tflops"], traffic=None, ms_per_launch=k_ms,
                     flops_per_launch=flops, peak_source=peaks["source"] + " (bf16 sustained)")
     alg_bytes = algorithmic_bytes_per_head_token(P, D) * BH * T
