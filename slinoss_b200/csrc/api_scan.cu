@@ -158,7 +158,7 @@ static int launch_scan_bwd_tc(const ScanDims &d, const ScanBwdArgs<T> &a, cudaSt
   size_t smem = scan_bwd_tc_smem_bytes();
   int rc = set_smem(kern, smem);
   if (rc) return rc;
-  kern<<<dim3(d.NC, d.BH), kTcThreads, smem, st>>>(a);
+  kern<<<dim3(d.NC, d.BH), kTcBwdThreads, smem, st>>>(a);
   return check_launch("chunk_scan_bwd_tc");
 }
 

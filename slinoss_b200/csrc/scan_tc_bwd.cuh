@@ -1,7 +1,7 @@
 // Tensor-core per-chunk backward of the v2x2ssd scan (chunk 128, P 64, half
 // inputs, fp32 state).  Same mathematics as chunk_scan_bwd_kernel in
 // scan_simt.cuh; every contraction runs on tcgen05 with fp32 accumulators in
-// tensor memory.  One CTA (256 threads) per (chunk, batch*head), one CTA per SM.
+// tensor memory.  One CTA of 512 threads per (chunk, batch*head), one CTA per SM.
 //
 // Tensor-memory map (fp32 columns):
 //   [  0,128)  G = dY U^T, then S = Qbar kappa^T (accumulated over state slabs)
@@ -17,16 +17,22 @@
 // so that row 127 of X is the column sum the carry gradient needs, the boundary
 // term of dq comes out of the same product, column 127 of S is the boundary
 // score and row 127 of S'^T dY is the dU carried to the previous token.
+//
+// Thread roles: for staging, thread = (16-byte chunk j = tid%8, rows tid/8 and
+// tid/8+64); for tensor-memory epilogues, thread = (row 32*(warp%4)+lane,
+// column quarter warp/4).  Global loads a phase needs are issued before the
+// wait on the preceding products, so that their latency overlaps the tensor work.
 #pragma once
 
 #include "scan_tc.cuh"
 
 namespace slx {
 
-constexpr size_t scan_bwd_tc_smem_bytes() { return 1024 + 144 * 1024 + 24 * 1024; }
+constexpr int kTcBwdThreads = 512;
+constexpr size_t scan_bwd_tc_smem_bytes() { return 1024 + 144 * 1024 + 28 * 1024 + 32 * 1024; }
 
 template <typename T>
-__global__ void __launch_bounds__(kTcThreads, 1) chunk_scan_bwd_tc_kernel(ScanBwdArgs<T> a) {
+__global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(ScanBwdArgs<T> a) {
   constexpr int L = kTcL, P = kTcP;
   extern __shared__ unsigned char smem_raw[];
   unsigned char *base =
@@ -50,8 +56,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) chunk_scan_bwd_tc_kernel(ScanBw
   float2 *bc = sg1 + L, *bX = bc + L, *gA = bX + L, *gsum = gA + L;
   float2 *bm1 = gsum + L;                    // 128  b_{-1}
   float2 *ul1 = bm1 + 128;                   // 128  (u_{-1} . Lambda)[n]
-  float2 *misc = ul1 + 128;                  // [0] bLam(last row) [1] dk^p_0 [2] w_{-1} [3] p_{L-1}/p_0
-  float2 *half2sum = misc + 4;               // 3 x 128: partial dots of the second column half
+  float2 *bh1 = ul1 + 128;                   // 128  w_{-1} b_{-1}
+  float2 *misc = bh1 + 128;                  // [0] bLam(last row) [1] dk^p_0 [2] w_{-1} [3] p_{L-1}/p_0
+  float *ulw = reinterpret_cast<float *>(misc + 4);  // [16][64] per-warp partials of u_{-1}.Lambda
   __shared__ uint64_t mbar;
   __shared__ uint32_t tmem_slot;
 
@@ -71,7 +78,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) chunk_scan_bwd_tc_kernel(ScanBw
     umma::fence_mbar_init();
   }
   chunk_prefix_warp(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, nullptr);
-  if (tid >= 128) {
+  if (tid >= 128 && tid < 256) {
     int t = tid - 128;
     float2 vp = make_float2(0.f, 0.f), vc = vp;
     if (t < valid) {
@@ -81,29 +88,25 @@ __global__ void __launch_bounds__(kTcThreads, 1) chunk_scan_bwd_tc_kernel(ScanBw
     }
     kp[t] = vp;
     kc[t] = vc;
-    bX[t] = gA[t] = make_float2(0.f, 0.f);
-  } else if (tid >= 64) {
-    int p = tid - 64;
+  } else if (tid >= 256 && tid < 320) {
+    int p = tid - 256;
     float v = 0.f;
     if (t0 > 0) v = to_f(a.U[(tok0 - 1) * P + p]);
     else if (a.Uprev) v = a.Uprev[(size_t)bh * P + p];
     um1[p] = v;
     duc[p] = 0.f;
-  } else if (tid < 4) {
-    misc[tid] = make_float2(0.f, 0.f);
-  }
-  if (tid < d.N) {
+  } else if (tid >= 320 && tid < 320 + d.N) {
+    int n = tid - 320;
     float2 bv = make_float2(0.f, 0.f);
-    if (t0 > 0) bv = load_pair<T>(a.B + (tok0 - 1) * d.D + 2 * tid);
-    else if (a.Bprev) bv = *reinterpret_cast<const float2 *>(a.Bprev + (size_t)bh * d.D + 2 * tid);
-    bm1[tid] = bv;
+    if (t0 > 0) bv = load_pair<T>(a.B + (tok0 - 1) * d.D + 2 * n);
+    else if (a.Bprev) bv = *reinterpret_cast<const float2 *>(a.Bprev + (size_t)bh * d.D + 2 * n);
+    bm1[n] = bv;
   }
-  const int j = tid & 7, r0 = tid >> 3;
-  // raw dY, U tiles (dYe needs lp: second pass below)
-  uint4 dyr[4];
+  const int j = tid & 7, r0 = tid >> 3;  // r0 in [0,64)
+  uint4 dyr[2];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    int r = r0 + 32 * i;
+  for (int i = 0; i < 2; ++i) {
+    int r = r0 + 64 * i;
     uint4 u = make_uint4(0, 0, 0, 0);
     dyr[i] = u;
     if (r < valid) {
@@ -119,8 +122,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) chunk_scan_bwd_tc_kernel(ScanBw
   const uint32_t tmem = tmem_slot;
   // exp(lp_t) dY and g_{-1}[t] = dY_t . u_{-1}
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    int r = r0 + 32 * i;
+  for (int i = 0; i < 2; ++i) {
+    int r = r0 + 64 * i;
     const uint32_t *w = reinterpret_cast<const uint32_t *>(&dyr[i]);
     const float el = __expf(lp[r]);
     float tmp[8], dot = 0.f;
@@ -152,11 +155,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) chunk_scan_bwd_tc_kernel(ScanBw
     gk[t] = gkv;
     sg1[t] = s1;
     wco[t] = w;
-  }
-  if (tid == 255) {
-    float2 s0 = cscale(cmulc(ph[L - 1], ph[0]), __expf(lp[L - 1] - lp[0]));  // p_{L-1}/p_0
-    misc[3] = s0;
-    misc[2] = cmul(s0, kp[0]);
+  } else if (tid >= 256 && tid < 256 + d.N) {
+    const int n = tid - 256;
+    const float2 s0 = cscale(cmulc(ph[L - 1], ph[0]), __expf(lp[L - 1] - lp[0]));  // p_{L-1}/p_0
+    const float2 w1 = cmul(s0, kp[0]);
+    bh1[n] = cmul(w1, bm1[n]);
+    if (n == 0) {
+      misc[0] = misc[1] = make_float2(0.f, 0.f);
+      misc[2] = w1;
+      misc[3] = s0;
+    }
   }
   umma::fence_smem_to_async();
   __syncthreads();
@@ -166,7 +174,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) chunk_scan_bwd_tc_kernel(ScanBw
                  sBh = umma::smem_u32(tBh), sZ = umma::smem_u32(tZ), sLm = umma::smem_u32(tLm);
   uint32_t phase = 0;
   bool ok = true;
-  const int q4 = warp & 3, h = warp >> 2;
+  const int q4 = warp & 3, qc = warp >> 2;  // lane quarter of tensor memory, column quarter
   const int row = 32 * q4 + lane;
 
   // ---- G = dY U^T -> dS' ---------------------------------------------------------
@@ -178,32 +186,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) chunk_scan_bwd_tc_kernel(ScanBw
       umma::mma_ss(tmem, umma::desc_kmajor(sdY, kk), umma::desc_kmajor(sU, kk), id, kk != 0);
     umma::commit(mbar_s);
   }
-  ok = umma::mbar_wait(mbar_s, phase) && ok;
-  phase ^= 1;
-  umma::fence_after_sync();
-  {
-    const float lpt = lp[row];
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int c0 = 64 * h + 32 * half;
-      float v[32];
-      umma::tmem_ld32(umma::tmem_addr(tmem, 32 * q4, c0), v);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int s = c0 + i;
-        if (s == row) gd[row] = v[i];
-        float x = 0.f;
-        if (s < row) x = v[i] * __expf(lpt - lp[s + 1]);
-        if (s == L - 1) x = __expf(lpt - lp[0]) * gm1[row];  // boundary slot
-        v[i] = x;
-      }
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        *reinterpret_cast<uint4 *>(tdS + 16384 * h + umma::swz_off(row, 4 * half + k)) = pack8<T>(v + 8 * k);
-    }
-  }
-  umma::fence_before_sync();
-  // (the slab loop's first barrier orders these stores and TMEM reads before the next products)
 #include "scan_tc_bwd_body.inc"
 }
 
