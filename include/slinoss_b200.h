@@ -220,6 +220,10 @@ int slx_set_tensor_path(int enable);
  * out and the affected launch produced undefined values. */
 int slx_read_tc_status(int *host_out);
 
+/* Diagnostic (synchronising): 64 clock64() stamps written by CTA (0,0) of the
+ * last tensor-core backward launch at its phase boundaries. */
+int slx_read_phase_clock(long long *host_out64);
+
 /* Self-test of the tcgen05 tile engine (no counterpart in the reference): one
  * CTA computes a small bf16 product with fp32 accumulation in tensor memory.
  * mode 0: C[128x128] = A[128x64] B[128x64]^T;  mode 1: C[128x64] = A[128x128]

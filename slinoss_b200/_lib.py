@@ -58,6 +58,7 @@ SIGNATURES = {
     "slx_scanprep_bwd": (c_int32, [POINTER(PrepShape)] + [_P] * 15 + [c_size_t, _P]),
     "slx_set_tensor_path": (c_int32, [c_int32]),
     "slx_read_tc_status": (c_int32, [POINTER(c_int32)]),
+    "slx_read_phase_clock": (c_int32, [POINTER(c_int64)]),
     "slx_umma_selftest": (c_int32, [c_int32] + [_P] * 5),
     "slx_cconv1d_fwd": (c_int32, [POINTER(ConvShape)] + [_P] * 7),
     "slx_cconv1d_bwd_workspace_bytes": (c_size_t, [POINTER(ConvShape)]),

@@ -238,6 +238,13 @@ int slx_set_tensor_path(int enable) {
   return old;
 }
 
+int slx_read_phase_clock(long long *host_out64) {
+  SLX_REQUIRE(host_out64 != nullptr, SLX_E_NULL, "read_phase_clock: NULL pointer");
+  cudaError_t e = cudaMemcpyFromSymbol(host_out64, g_phase_clock, sizeof(long long) * 64);
+  if (e != cudaSuccess) return fail((int)e, "read_phase_clock: %s", cudaGetErrorString(e));
+  return SLX_OK;
+}
+
 int slx_read_tc_status(int *host_out) {
   SLX_REQUIRE(host_out != nullptr, SLX_E_NULL, "read_tc_status: NULL pointer");
   int zero = 0;

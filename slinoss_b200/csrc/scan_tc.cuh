@@ -14,12 +14,15 @@
 namespace slx {
 
 __device__ int g_tc_status = 0;  // becomes non-zero when a bounded wait ran out
+__device__ long long g_phase_clock[64];  // clock64() stamps of CTA (0,0) of the last backward launch (diagnostic)
 
 constexpr int kTcL = 128;
 constexpr int kTcP = 64;
 constexpr int kTcThreads = 256;
 
-// coef * (4 packed complex values) -> 4 packed complex values in T
+// coef * (4 packed complex values) -> 4 packed complex values in T.
+// fp32 rotation, one rounding to T: used wherever the gradient identities rely on
+// consistently rounded operands (the packed variant above costs ~1e-2 on dM)
 template <typename T>
 __device__ __forceinline__ uint4 rotate_chunk(uint4 raw, float2 coef) {
   const uint32_t *w = reinterpret_cast<const uint32_t *>(&raw);

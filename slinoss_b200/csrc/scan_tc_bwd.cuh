@@ -72,6 +72,9 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
   const uint32_t mbar_s = umma::smem_u32(&mbar);
   constexpr int fmt = umma::HalfFmt<T>::value;
 
+  const bool stamp_on = (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0);
+#define SLX_STAMP(i) do { if (stamp_on) g_phase_clock[i] = clock64(); } while (0)
+  SLX_STAMP(0);
   if (warp == 0) umma::tmem_alloc(&tmem_slot, 512);
   if (tid == 32) {
     umma::mbar_init(mbar_s, 1);
@@ -177,6 +180,7 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
   const int q4 = warp & 3, qc = warp >> 2;  // lane quarter of tensor memory, column quarter
   const int row = 32 * q4 + lane;
 
+  SLX_STAMP(1);
   // ---- G = dY U^T -> dS' ---------------------------------------------------------
   if (tid == 0) {
     umma::fence_after_sync();
@@ -187,6 +191,7 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
     umma::commit(mbar_s);
   }
 #include "scan_tc_bwd_body.inc"
+#undef SLX_STAMP
 }
 
 }  // namespace slx
