@@ -240,7 +240,7 @@ int slx_set_tensor_path(int enable) {
 
 int slx_read_phase_clock(long long *host_out64) {
   SLX_REQUIRE(host_out64 != nullptr, SLX_E_NULL, "read_phase_clock: NULL pointer");
-  cudaError_t e = cudaMemcpyFromSymbol(host_out64, g_phase_clock, sizeof(long long) * 64);
+  cudaError_t e = cudaMemcpyFromSymbol(host_out64, g_phase_clock, sizeof(long long) * 128);
   if (e != cudaSuccess) return fail((int)e, "read_phase_clock: %s", cudaGetErrorString(e));
   return SLX_OK;
 }

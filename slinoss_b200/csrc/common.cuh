@@ -50,6 +50,7 @@ __device__ __forceinline__ float2 cscale(float2 a, float s) { return make_float2
 // ph[t] = normalised prod_{tau<=t} m_tau/|m_tau|.  Tokens >= valid act as m = 1.
 // Executed by warp 0 of the CTA; results land in shared memory (lp, ph of
 // length L) and the caller synchronises.  An exactly-zero |m| sets *bad_flag.
+template <bool FAST = false>
 __device__ __forceinline__ void chunk_prefix_warp(int run_warp, const float *__restrict__ Mchunk, int L, int valid,
                                                   float *lp, float2 *ph, float2 *mraw, int *bad_flag) {
   const int lane = threadIdx.x & 31;
@@ -63,15 +64,28 @@ __device__ __forceinline__ void chunk_prefix_warp(int run_warp, const float *__r
     if (t < L) {
       float2 m = make_float2(1.f, 0.f);
       if (t < valid) m = *reinterpret_cast<const float2 *>(Mchunk + 2 * (size_t)t);
-      float mag = hypotf(m.x, m.y);
-      if (mag == 0.f) {
-        if (bad_flag) atomicExch(bad_flag, 1);
-        mag = 1.f;
-        m = make_float2(1.f, 0.f);
+      float mag, inv, lg;
+      if (FAST) {  // half-input kernels: fast intrinsics are far inside their error budget
+        float m2 = fmaf(m.x, m.x, m.y * m.y);
+        if (m2 == 0.f) {
+          if (bad_flag) atomicExch(bad_flag, 1);
+          m2 = 1.f;
+          m = make_float2(1.f, 0.f);
+        }
+        inv = rsqrtf(m2);
+        lg = 0.5f * __logf(m2);
+      } else {
+        mag = hypotf(m.x, m.y);
+        if (mag == 0.f) {
+          if (bad_flag) atomicExch(bad_flag, 1);
+          mag = 1.f;
+          m = make_float2(1.f, 0.f);
+        }
+        inv = 1.f / mag;
+        lg = logf(mag);
       }
       mraw[t] = m;
-      lsum += logf(mag);
-      float inv = 1.f / mag;
+      lsum += lg;
       psum = cmul(psum, make_float2(m.x * inv, m.y * inv));
       lp[t] = lsum;
       ph[t] = psum;
@@ -110,7 +124,7 @@ __device__ __forceinline__ void chunk_prefix_warp(int run_warp, const float *__r
 
 __device__ __forceinline__ void chunk_prefix_warp0(const float *__restrict__ Mchunk, int L, int valid, float *lp,
                                                    float2 *ph, float2 *mraw, int *bad_flag) {
-  chunk_prefix_warp(0, Mchunk, L, valid, lp, ph, mraw, bad_flag);
+  chunk_prefix_warp<false>(0, Mchunk, L, valid, lp, ph, mraw, bad_flag);
 }
 
 }  // namespace slx

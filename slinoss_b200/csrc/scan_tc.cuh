@@ -14,7 +14,7 @@
 namespace slx {
 
 __device__ int g_tc_status = 0;  // becomes non-zero when a bounded wait ran out
-__device__ long long g_phase_clock[64];  // clock64() stamps of CTA (0,0) of the last backward launch (diagnostic)
+__device__ long long g_phase_clock[128];  // clock64() stamps of CTA (0,0) of the last backward launch (diagnostic)
 
 constexpr int kTcL = 128;
 constexpr int kTcP = 64;
@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
     umma::mbar_init(mbar_s, 1);
     umma::fence_mbar_init();
   }
-  chunk_prefix_warp(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, a.bad);
+  chunk_prefix_warp<true>(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, a.bad);
   if (tid >= 128) {
     int t = tid - 128;
     float2 vp = make_float2(0.f, 0.f), vc = vp;
@@ -349,7 +349,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_outer_tc_kernel(OuterArgs
     umma::mbar_init(mbar_s, 1);
     umma::fence_mbar_init();
   }
-  chunk_prefix_warp(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, nullptr);
+  chunk_prefix_warp<true>(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, nullptr);
   const int j = tid & 7, r0 = tid >> 3;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {

@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
     umma::mbar_init(mbar_s, 1);
     umma::fence_mbar_init();
   }
-  chunk_prefix_warp(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, nullptr);
+  chunk_prefix_warp<true>(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, nullptr);
   if (tid >= 128 && tid < 256) {
     int t = tid - 128;
     float2 vp = make_float2(0.f, 0.f), vc = vp;

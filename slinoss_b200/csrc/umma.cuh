@@ -42,6 +42,12 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_saddr, int kk, ui
   return make_desc(tile_saddr + 2048u * kk, block_stride_bytes, 1024u);
 }
 
+// Descriptor of the same tile view advanced by `bytes` (a multiple of 16): only the
+// 14-bit start-address field changes, so this is one 64-bit add.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
+constexpr uint32_t kStepK = 32;     // K-major: next K-step of 16 halfs inside a 64-column tile
+constexpr uint32_t kStepMN = 2048;  // MN-major: next K-step = 16 rows of 128 bytes
+
 // 32-bit instruction descriptor for kind::f16 with fp32 accumulation.
 // fmt: 0 = fp16 operands, 1 = bf16 operands.
 __host__ __device__ constexpr uint32_t make_idesc(int M, int N, bool a_mn_major, bool b_mn_major, int fmt) {
