@@ -1,0 +1,224 @@
+"""Stage-level timings of the scan path on one GPU, with achieved bandwidth /
+tensor throughput per kernel against the measured peaks.
+
+    python -m slinoss_b200.bench_stages [--batch 4 --heads 32 --T 8192 --N 128 --chunk 128] [--prep] [--conv]
+
+Prints one JSON line per stage: name, ms (CUDA events, median of reps after
+warm-up), algorithmic bytes and dense flops per launch, GB/s, TFLOP/s and the
+fraction of the measured HBM / bf16 peaks (MEASURED_PEAKS.json beside the
+package root, else the pool's fallback figures).  Inputs are seeded synthetic
+tensors larger than L2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+from ctypes import byref
+from pathlib import Path
+
+import torch
+
+from . import _lib
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), float(d["bf16_tflops_sustained"]), "measured"
+    return 6650.0, 1400.0, "fallback"
+
+
+def _time(fn, reps=10, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def _emit(name, ms, nbytes, flops, hbm, tfl, src, extra=None):
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    tf = flops / (ms * 1e-3) / 1e12
+    line = dict(stage=name, ms=round(ms, 4), bytes=int(nbytes), flops=int(flops), gbs=round(gbs, 1),
+                tflops=round(tf, 2), frac_hbm=round(gbs / hbm, 4), frac_tensor=round(tf / tfl, 4), peaks=src)
+    if extra:
+        line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+def scan_stages(b, h, T, P, N, L, dtype):
+    dev = torch.device("cuda")
+    hbm, tfl, src = _peaks()
+    g = torch.Generator().manual_seed(0)
+    D, BH, NC = 2 * N, b * h, (T + L - 1) // L
+    es = torch.empty((), dtype=dtype).element_size()
+    radius = torch.sigmoid(2.0 + torch.randn((b, h, T), generator=g))
+    angle = torch.tanh(torch.randn((b, h, T), generator=g)) * (math.pi / 4)
+    M = torch.view_as_real(torch.polar(radius, angle)).float().contiguous().to(dev)
+    K = (torch.randn((b, h, T, 2, 2), generator=g) * 0.1).float().to(dev)
+    U = torch.randn((b, h, T, P), generator=g).to(dtype).to(dev)
+    B = (torch.randn((b, h, T, D), generator=g) / math.sqrt(N)).to(dtype).to(dev)
+    C = (torch.randn((b, h, T, D), generator=g) / math.sqrt(N)).to(dtype).to(dev)
+    dY = torch.randn((b, h, T, P), generator=g).to(dtype).to(dev)
+    lib, st = _lib.lib(), _lib.stream_ptr(dev)
+    s = _lib.ScanShape(BH, T, P, N, L, _lib.dtype_code(dtype))
+    f32 = dict(device=dev, dtype=torch.float32)
+    inc = torch.empty((b, h, NC, P, D), **f32)
+    starts = torch.empty_like(inc)
+    mch = torch.empty((b, h, NC, 2), **f32)
+    final = torch.empty((b, h, P, D), **f32)
+    Y = torch.empty_like(U)
+    dz0 = torch.empty_like(inc)
+    d_inc = torch.empty_like(inc)
+    zdot = torch.empty((b, h, NC, 2), **f32)
+    part = torch.empty((BH * NC * 2 * 64,), **f32)
+    dU, dB, dC = torch.empty_like(U), torch.empty_like(B), torch.empty_like(C)
+    dM, dK = torch.empty_like(M), torch.empty_like(K)
+    cB, cU = torch.empty((b, h, NC, D), **f32), torch.empty((b, h, NC, P), **f32)
+    ck = _lib.check
+    ht = BH * T
+    state_bytes = BH * NC * P * D * 4
+
+    def inc_fn():
+        ck(lib.slx_chunk_increment_fwd(byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), None, None,
+                                       inc.data_ptr(), mch.data_ptr(), st), "inc")
+
+    _emit("chunk_increment_fwd", _time(inc_fn), ht * (es * (P + D) + 24) + state_bytes, 2 * ht * P * D, hbm, tfl, src)
+
+    def sp_fn():
+        ck(lib.slx_state_passing_fwd(BH, NC, P, N, inc.data_ptr(), mch.data_ptr(), None, starts.data_ptr(),
+                                     final.data_ptr(), st), "sp")
+
+    _emit("state_passing_fwd", _time(sp_fn), 2 * state_bytes, 0, hbm, tfl, src)
+
+    def scan_fn():
+        ck(lib.slx_chunk_scan_fwd(byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
+                                  starts.data_ptr(), None, None, Y.data_ptr(), st), "scan")
+
+    _emit("chunk_scan_fwd", _time(scan_fn), ht * (es * (2 * P + 2 * D) + 24) + state_bytes,
+          ht * (2 * L * (D + P) + 2 * P * D), hbm, tfl, src)
+
+    def dz0_fn():
+        ck(lib.slx_chunk_scan_bwd_dz0(byref(s), M.data_ptr(), C.data_ptr(), dY.data_ptr(), dz0.data_ptr(), st), "dz0")
+
+    _emit("chunk_scan_bwd_dz0", _time(dz0_fn), ht * (es * (P + D) + 8) + state_bytes, 2 * ht * P * D, hbm, tfl, src)
+
+    def spb_fn():
+        ck(lib.slx_state_passing_bwd(BH, NC, P, N, dz0.data_ptr(), mch.data_ptr(), starts.data_ptr(),
+                                     final.data_ptr(), None, d_inc.data_ptr(), None, zdot.data_ptr(),
+                                     part.data_ptr(), st), "spb")
+
+    _emit("state_passing_bwd", _time(spb_fn), 3 * state_bytes, 0, hbm, tfl, src)
+
+    def bwd_fn():
+        ck(lib.slx_chunk_scan_bwd(byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(), None,
+                                  None, starts.data_ptr(), d_inc.data_ptr(), zdot.data_ptr(), dY.data_ptr(),
+                                  dU.data_ptr(), dM.data_ptr(), dK.data_ptr(), dB.data_ptr(), dC.data_ptr(),
+                                  cB.data_ptr(), cU.data_ptr(), st), "bwd")
+
+    _emit("chunk_scan_bwd", _time(bwd_fn), ht * (es * (3 * P + 4 * D) + 48) + 2 * state_bytes,
+          ht * 2 * (2 * L * P + 3 * L * D + 3 * P * D), hbm, tfl, src)
+
+
+def prep_stage(b, T, H, P, N, dtype):
+    import slinoss_b200 as sb
+
+    dev = torch.device("cuda")
+    hbm, tfl, src = _peaks()
+    g = torch.Generator().manual_seed(1)
+    es = torch.empty((), dtype=dtype).element_size()
+    value = torch.randn(b, T, H * P, generator=g).to(dtype).to(dev).requires_grad_(True)
+    params = torch.randn(b, T, H * 13, generator=g).to(dtype).to(dev).requires_grad_(True)
+    bc = torch.randn(b, T, H, 4, N, generator=g).to(dtype).to(dev).requires_grad_(True)
+    names = ("dt_bias", "gamma_bias", "omega_bias", "mix_r_bias", "mix_theta_bias", "mix_k_prev_bias",
+             "mix_k_curr_bias")
+    pars = {n: torch.zeros(H, device=dev, requires_grad=True) for n in names}
+    bs = torch.ones(H, 2, N, device=dev, requires_grad=True)
+    cs = torch.ones(H, 2, N, device=dev, requires_grad=True)
+    hp = dict(dt_min=1e-4, dt_max=1e-1, r_min=0.9, r_max=1.0, theta_bound=math.pi, k_max=0.5, eps=1e-8)
+
+    def fwd():
+        return sb.scanprep_b200(value, params, bc, n_heads=H, d_state=N, d_head=P, normalize_bc=True, **hp, **pars,
+                                b_scale=bs, c_scale=cs)
+
+    with torch.no_grad():
+        ms = _time(fwd)
+    rows = b * T * H
+    per_row = es * (P + 13 + 4 * N) + es * (P + 4 * N) + 24
+    _emit("scanprep_fwd", ms, rows * per_row, 0, hbm, tfl, src)
+    si = fwd()
+    outs = [si.U, si.M, si.K, si.B, si.C]
+    gouts = [torch.randn_like(o) for o in outs]
+    leaves = [value, params, bc, bs, cs] + list(pars.values())
+
+    def bwd():
+        torch.autograd.grad(outs, leaves, gouts, retain_graph=True)
+
+    ms = _time(bwd)
+    _emit("scanprep_bwd", ms, rows * (per_row + es * (13 + 4 * N)), 0, hbm, tfl, src,
+          dict(note="reads params, bc and all five gradients; writes d_value, d_params, d_bc"))
+
+
+def conv_stage(b, T, Cn, dtype):
+    import slinoss_b200 as sb
+
+    dev = torch.device("cuda")
+    hbm, tfl, src = _peaks()
+    g = torch.Generator().manual_seed(2)
+    es = torch.empty((), dtype=dtype).element_size()
+    x = torch.randn(b, T, Cn, generator=g).to(dtype).to(dev).requires_grad_(True)
+    w = torch.randn(Cn, 4, generator=g).to(dtype).to(dev).requires_grad_(True)
+    bias = torch.randn(Cn, generator=g).to(dtype).to(dev).requires_grad_(True)
+
+    def fwd():
+        return sb.cconv1d_b200(x, w, bias, None)
+
+    with torch.no_grad():
+        ms = _time(fwd)
+    _emit("cconv1d_fwd", ms, b * T * Cn * 2 * es, 0, hbm, tfl, src)
+    y, _ = fwd()
+    gy = torch.randn_like(y)
+
+    def bwd():
+        torch.autograd.grad(y, [x, w, bias], gy, retain_graph=True)
+
+    _emit("cconv1d_bwd", _time(bwd), b * T * Cn * 3 * es, 0, hbm, tfl, src)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=4)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--T", type=int, default=8192)
+    ap.add_argument("--P", type=int, default=64)
+    ap.add_argument("--N", type=int, default=128)
+    ap.add_argument("--chunk", type=int, default=128)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16", "f32"])
+    ap.add_argument("--no-scan", action="store_true")
+    ap.add_argument("--prep", action="store_true")
+    ap.add_argument("--conv", action="store_true")
+    a = ap.parse_args()
+    dt = dict(bf16=torch.bfloat16, f16=torch.float16, f32=torch.float32)[a.dtype]
+    if not a.no_scan:
+        scan_stages(a.batch, a.heads, a.T, a.P, a.N, a.chunk, dt)
+    if a.prep:
+        prep_stage(a.batch, a.T, a.heads, a.P, a.N, dt)
+    if a.conv:
+        conv_stage(a.batch, a.T, a.heads * a.P, dt)
+
+
+if __name__ == "__main__":
+    main()
