@@ -207,6 +207,27 @@ int slx_cconv1d_bwd(const slx_conv_shape *s, const void *x, const void *weight,
                     float *dbias, float *dstate, void *workspace,
                     size_t workspace_bytes, void *stream);
 
+/* Same computation and results as slx_cconv1d_bwd, for callers that cannot hand
+ * over a workspace because they cannot allocate device memory at call time: a
+ * serving process whose own allocator was given all device memory at start-up, a
+ * plugin host that forbids driver allocations once it is running, or any place
+ * where a cudaMalloc would stall the device.  (No counterpart in the reference.)
+ * The partial sums go to a buffer that is part of the library image: 4 MiB per GPU
+ * that loads the library, kept until the process exits.  Limit:
+ * batch * ceil(T/128) * channels * 5 floats <= 1,048,576, otherwise SLX_E_UNSUPPORTED
+ * with a message naming the sizes.  The entry point allocates nothing and frees
+ * nothing.  Its first call on each device looks up the buffer's device address (with
+ * that device current); make that first call outside any stream capture.  All calls
+ * on one GPU share the buffer: two calls whose kernels can overlap on the GPU
+ * (different streams, no ordering) race on it and must be serialised by the caller.
+ * Nothing in the buffer needs clearing between calls: every slot that is read was
+ * written earlier in the same call. */
+int slx_cconv1d_bwd_noalloc(const slx_conv_shape *s, const void *x,
+                            const void *weight, const void *bias, const void *state,
+                            const void *dy, const void *d_next_state, void *dx,
+                            float *dweight, float *dbias, float *dstate,
+                            void *stream);
+
 /* ---- diagnostics ----------------------------------------------------------- */
 
 /* Half inputs with chunk 128, P 64 and 2N in {64,128,192,256} run on the

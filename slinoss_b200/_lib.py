@@ -56,6 +56,7 @@ SIGNATURES = {
     "slx_scanprep_fwd": (c_int32, [POINTER(PrepShape)] + [_P] * 11),
     "slx_scanprep_bwd_workspace_bytes": (c_size_t, [POINTER(PrepShape)]),
     "slx_scanprep_bwd": (c_int32, [POINTER(PrepShape)] + [_P] * 15 + [c_size_t, _P]),
+    "slx_cconv1d_bwd_noalloc": (c_int32, [POINTER(ConvShape)] + [_P] * 11),
     "slx_set_tensor_path": (c_int32, [c_int32]),
     "slx_read_tc_status": (c_int32, [POINTER(c_int32)]),
     "slx_read_phase_clock": (c_int32, [POINTER(c_int64)]),

@@ -11,6 +11,7 @@
 // load and one vector store per channel-vector-token, i.e. the algorithmic
 // 4 bytes per channel-token forward and 6 backward for half types.
 #include <initializer_list>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -378,3 +379,54 @@ int slx_cconv1d_bwd(const slx_conv_shape *s, const void *x, const void *weight, 
 }
 
 }  // extern "C"
+
+// ---- backward without caller-provided scratch ------------------------------------------------
+// Scratch for the weight/bias partial sums lives in the library image itself: kNoAllocFloats
+// floats (4 MiB) per GPU that loads the library, held until the process exits.
+namespace slx {
+constexpr size_t kNoAllocFloats = 1u << 20;
+static __device__ __align__(256) float g_conv_noalloc_scratch[kNoAllocFloats];
+
+// In host code the array's name is only a stand-in for the symbol; the device address has to be
+// asked for, once per device, with that device current.
+static float *noalloc_scratch_for_current_device(int *status) {
+  static std::mutex mu;
+  static float *cache[64] = {};
+  *status = SLX_OK;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    *status = fail(e != cudaSuccess ? (int)e : SLX_E_UNSUPPORTED, "cconv1d_bwd_noalloc: cannot identify the device");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache[dev] == nullptr) {
+    void *p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_conv_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      *status = fail((int)e, "cconv1d_bwd_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    cache[dev] = static_cast<float *>(p);
+  }
+  return cache[dev];
+}
+}  // namespace slx
+
+extern "C" int slx_cconv1d_bwd_noalloc(const slx_conv_shape *s, const void *x, const void *weight, const void *bias,
+                                       const void *state, const void *dy, const void *d_next_state, void *dx,
+                                       float *dweight, float *dbias, float *dstate, void *stream) {
+  using namespace slx;
+  const size_t need = slx_cconv1d_bwd_workspace_bytes(s);
+  SLX_REQUIRE(need != 0, SLX_E_SHAPE, "cconv1d_bwd_noalloc: bad shape");
+  SLX_REQUIRE(need <= kNoAllocFloats * sizeof(float), SLX_E_UNSUPPORTED,
+              "cconv1d_bwd_noalloc: this shape needs %zu bytes of scratch, the built-in buffer holds %zu "
+              "(batch * ceil(T/128) * channels * 5 floats must not exceed %zu); use slx_cconv1d_bwd with a "
+              "caller-provided workspace",
+              need, kNoAllocFloats * sizeof(float), kNoAllocFloats);
+  int rc = SLX_OK;
+  float *scratch = noalloc_scratch_for_current_device(&rc);
+  if (rc) return rc;
+  return slx_cconv1d_bwd(s, x, weight, bias, state, dy, d_next_state, dx, dweight, dbias, dstate, scratch,
+                         kNoAllocFloats * sizeof(float), stream);
+}
