@@ -153,7 +153,10 @@ __device__ __forceinline__ void coef_backward(const CoefCtx &c, const PrepHyper 
 // ---- vector access ------------------------------------------------------------
 template <typename T, int VEC>
 __device__ __forceinline__ void load_vec(const T *p, float (&v)[VEC]) {
-  if constexpr (VEC * sizeof(T) == 16) {
+  if constexpr (VEC * sizeof(T) == 32 && sizeof(T) == 4) {
+    const float4 a = reinterpret_cast<const float4 *>(p)[0], b = reinterpret_cast<const float4 *>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else if constexpr (VEC * sizeof(T) == 16) {
     uint4 raw = *reinterpret_cast<const uint4 *>(p);
     const T *e = reinterpret_cast<const T *>(&raw);
 #pragma unroll
@@ -200,83 +203,139 @@ __global__ void __launch_bounds__(256) scanprep_fwd_kernel(const T *__restrict__
                                                            float *__restrict__ M, float *__restrict__ K,
                                                            T *__restrict__ Bo, T *__restrict__ Co, PrepDims d,
                                                            PrepHyper hp) {
-  constexpr int GPB = 256 / G;  // rows per CTA pass
+  // A CTA pass covers 256 consecutive rows.  Phase 1: one row per THREAD for the
+  // coefficient map (its ~500 scalar instructions then cost one issue slot per 32 rows
+  // instead of one per row).  Phase 2: one row per lane group for the wide copies.
+  constexpr int GPB = 256 / G;   // lane groups per CTA
+  constexpr int RPG = 256 / GPB; // rows each group walks through per pass (= G)
   const int q = threadIdx.x % G;
   const int grp = threadIdx.x / G;
   const long long n_rows = (long long)d.batch * d.H * d.T;
   const int D = 2 * d.N;
-  for (long long row0 = (long long)blockIdx.x * GPB; row0 < n_rows; row0 += (long long)gridDim.x * GPB) {
-    const long long row = row0 + grp;
-    const bool live = row < n_rows;
-    const long long rr = live ? row : 0;
-    const int t = (int)(rr % d.T);
-    const int h = (int)((rr / d.T) % d.H);
-    const int b = (int)(rr / ((long long)d.T * d.H));
-    const long long in_row = (long long)b * d.T + t;
-    // ---- U: copy P values ----
-    if (live) {
-      const T *src = value + in_row * d.vs + (long long)h * d.P;
-      T *dst = U + rr * d.P;
-      for (int p0 = q * VEC; p0 < d.P; p0 += G * VEC) {
-        float v[VEC];
-        load_vec<T, VEC>(src + p0, v);
-        store_vec<T, VEC>(dst + p0, v);
+  for (long long row0 = (long long)blockIdx.x * 256; row0 < n_rows; row0 += (long long)gridDim.x * 256) {
+    {
+      const long long row = row0 + threadIdx.x;
+      if (row < n_rows) {
+        const int t = (int)(row % d.T);
+        const int h = (int)((row / d.T) % d.H);
+        const int b = (int)(row / ((long long)d.T * d.H));
+        float p[13];
+        const T *pr = params + ((long long)b * d.T + t) * d.ps + (long long)h * 13;
+#pragma unroll
+        for (int i = 0; i < 13; ++i) p[i] = to_f(pr[i]) + bias[h * 13 + i];
+        CoefOut o = coef_forward(p, hp, nullptr);
+        *reinterpret_cast<float2 *>(M + row * 2) = o.rho;
+        *reinterpret_cast<float4 *>(K + row * 4) = make_float4(o.kp.x, o.kp.y, o.kc.x, o.kc.y);
       }
     }
-    // ---- B, C ----
-    const T *bcr = bc + in_row * d.bs + (long long)h * 4 * d.N;
-    float ss[4] = {0.f, 0.f, 0.f, 0.f};
-    if (d.normalize) {
+    for (int k = 0; k < RPG; ++k) {
+      const long long row = row0 + (long long)grp * RPG + k;
+      const bool live = row < n_rows;
+      const long long rr = live ? row : 0;
+      const int t = (int)(rr % d.T);
+      const int h = (int)((rr / d.T) % d.H);
+      const int b = (int)(rr / ((long long)d.T * d.H));
+      const long long in_row = (long long)b * d.T + t;
+      // ---- U: copy P values ----
       if (live) {
-        for (int n0 = q * VEC; n0 < d.N; n0 += G * VEC) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float v[VEC];
-            load_vec<T, VEC>(bcr + j * d.N + n0, v);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) ss[j] = fmaf(v[i], v[i], ss[j]);
-          }
+        const T *src = value + in_row * d.vs + (long long)h * d.P;
+        T *dst = U + rr * d.P;
+        for (int p0 = q * VEC; p0 < d.P; p0 += G * VEC) {
+          float v[VEC];
+          load_vec<T, VEC>(src + p0, v);
+          store_vec<T, VEC>(dst + p0, v);
         }
       }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) ss[j] = rsqrtf(group_sum_f<G>(ss[j]) / (float)d.N + 1e-5f);
-    }
-    if (live) {
-      for (int n0 = q * VEC; n0 < d.N; n0 += G * VEC) {
+      // ---- B, C ----
+      const T *bcr = bc + in_row * d.bs + (long long)h * 4 * d.N;
+      if (d.N <= G * VEC) {
+        // one sweep: every lane keeps its four row slices in registers
+        const int n0 = q * VEC;
+        const bool mine = live && n0 < d.N;
         float y[4][VEC];
+        float ss[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          load_vec<T, VEC>(bcr + j * d.N + n0, y[j]);
-          if (d.normalize) {
-            const float *sc = scale + ((long long)h * 4 + j) * d.N + n0;
+          if (mine) load_vec<T, VEC>(bcr + j * d.N + n0, y[j]);
+          else {
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) y[j][i] = (y[j][i] * ss[j]) * sc[i];
+            for (int i = 0; i < VEC; ++i) y[j][i] = 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) ss[j] = fmaf(y[j][i], y[j][i], ss[j]);
+        }
+        if (d.normalize) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            ss[j] = rsqrtf(group_sum_f<G>(ss[j]) / (float)d.N + 1e-5f);
+            if (mine) {
+              float sc[VEC];
+              load_vec<float, VEC>(scale + ((long long)h * 4 + j) * d.N + n0, sc);
+#pragma unroll
+              for (int i = 0; i < VEC; ++i) y[j][i] = (y[j][i] * ss[j]) * sc[i];
+            }
           }
         }
-        float ob[2][VEC], oc[2][VEC];
+        if (mine) {
+          float ob[2][VEC], oc[2][VEC];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-          int o = 2 * i;
-          ob[o / VEC][o % VEC] = y[0][i];
-          ob[(o + 1) / VEC][(o + 1) % VEC] = y[1][i];
-          oc[o / VEC][o % VEC] = y[2][i];
-          oc[(o + 1) / VEC][(o + 1) % VEC] = y[3][i];
+          for (int i = 0; i < VEC; ++i) {
+            int o = 2 * i;
+            ob[o / VEC][o % VEC] = y[0][i];
+            ob[(o + 1) / VEC][(o + 1) % VEC] = y[1][i];
+            oc[o / VEC][o % VEC] = y[2][i];
+            oc[(o + 1) / VEC][(o + 1) % VEC] = y[3][i];
+          }
+          store_vec<T, VEC>(Bo + rr * D + 2 * n0, ob[0]);
+          store_vec<T, VEC>(Bo + rr * D + 2 * n0 + VEC, ob[1]);
+          store_vec<T, VEC>(Co + rr * D + 2 * n0, oc[0]);
+          store_vec<T, VEC>(Co + rr * D + 2 * n0 + VEC, oc[1]);
         }
-        store_vec<T, VEC>(Bo + rr * D + 2 * n0, ob[0]);
-        store_vec<T, VEC>(Bo + rr * D + 2 * n0 + VEC, ob[1]);
-        store_vec<T, VEC>(Co + rr * D + 2 * n0, oc[0]);
-        store_vec<T, VEC>(Co + rr * D + 2 * n0 + VEC, oc[1]);
-      }
-    }
-    // ---- M, K ----
-    if (live && q == 0) {
-      float p[13];
-      const T *pr = params + in_row * d.ps + (long long)h * 13;
+      } else {
+        float ss[4] = {0.f, 0.f, 0.f, 0.f};
+        if (d.normalize) {
+          if (live) {
+            for (int n0 = q * VEC; n0 < d.N; n0 += G * VEC) {
 #pragma unroll
-      for (int i = 0; i < 13; ++i) p[i] = to_f(pr[i]) + bias[h * 13 + i];
-      CoefOut o = coef_forward(p, hp, nullptr);
-      *reinterpret_cast<float2 *>(M + rr * 2) = o.rho;
-      *reinterpret_cast<float4 *>(K + rr * 4) = make_float4(o.kp.x, o.kp.y, o.kc.x, o.kc.y);
+              for (int j = 0; j < 4; ++j) {
+                float v[VEC];
+                load_vec<T, VEC>(bcr + j * d.N + n0, v);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) ss[j] = fmaf(v[i], v[i], ss[j]);
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) ss[j] = rsqrtf(group_sum_f<G>(ss[j]) / (float)d.N + 1e-5f);
+        }
+        if (live) {
+          for (int n0 = q * VEC; n0 < d.N; n0 += G * VEC) {
+            float y[4][VEC];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              load_vec<T, VEC>(bcr + j * d.N + n0, y[j]);
+              if (d.normalize) {
+                const float *sc = scale + ((long long)h * 4 + j) * d.N + n0;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) y[j][i] = (y[j][i] * ss[j]) * sc[i];
+              }
+            }
+            float ob[2][VEC], oc[2][VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+              int o = 2 * i;
+              ob[o / VEC][o % VEC] = y[0][i];
+              ob[(o + 1) / VEC][(o + 1) % VEC] = y[1][i];
+              oc[o / VEC][o % VEC] = y[2][i];
+              oc[(o + 1) / VEC][(o + 1) % VEC] = y[3][i];
+            }
+            store_vec<T, VEC>(Bo + rr * D + 2 * n0, ob[0]);
+            store_vec<T, VEC>(Bo + rr * D + 2 * n0 + VEC, ob[1]);
+            store_vec<T, VEC>(Co + rr * D + 2 * n0, oc[0]);
+            store_vec<T, VEC>(Co + rr * D + 2 * n0 + VEC, oc[1]);
+          }
+        }
+      }
     }
   }
 }
@@ -514,8 +573,8 @@ static int launch_prep_fwd(const slx_prep_shape *s, const PrepDims &d, const voi
   PrepHyper hp = make_hyper(s);
   constexpr int G = prep_group<VEC>();
   long long n_rows = (long long)d.batch * d.H * d.T;
-  long long blocks = (n_rows + (256 / G) - 1) / (256 / G);
-  if (blocks > 148LL * 64) blocks = 148LL * 64;
+  long long blocks = (n_rows + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
   scanprep_fwd_kernel<T, VEC, G><<<(unsigned)blocks, 256, 0, st>>>(
       (const T *)value, (const T *)params, (const T *)bc, bias, scale, (T *)U, M, K, (T *)B, (T *)C, d, hp);
   return check_launch("scanprep_fwd");
