@@ -369,9 +369,39 @@ __global__ void __launch_bounds__(256) scanprep_bwd_kernel(const T *__restrict__
     for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int i = 0; i < VEC; ++i) dsc[k][j][i] = 0.f;
-  float dbias[13];
+  // ---- coefficient-map VJP: one row per THREAD (rows_per_tile == blockDim.x) -------------
+  __shared__ float sbias[8][13];
+  {
+    float dbias[13];
 #pragma unroll
-  for (int i = 0; i < 13; ++i) dbias[i] = 0.f;
+    for (int i = 0; i < 13; ++i) dbias[i] = 0.f;
+    for (int t = t_lo + (int)threadIdx.x; t < t_hi; t += 256) {
+      const long long in_row = (long long)b * d.T + t;
+      const long long orow = ((long long)bh) * d.T + t;
+      float p[13], dp[13];
+      const T *pr = params + in_row * d.ps + (long long)h * 13;
+#pragma unroll
+      for (int i = 0; i < 13; ++i) p[i] = to_f(pr[i]) + bias[h * 13 + i];
+      CoefCtx ctx;
+      coef_forward(p, hp, &ctx);
+      float2 dm = *reinterpret_cast<const float2 *>(dM + orow * 2);
+      float4 dk = *reinterpret_cast<const float4 *>(dK + orow * 4);
+      coef_backward(ctx, hp, dm, make_float2(dk.x, dk.y), make_float2(dk.z, dk.w), dp);
+      T *dpr = d_params + in_row * ((long long)d.H * 13) + (long long)h * 13;
+#pragma unroll
+      for (int i = 0; i < 13; ++i) {
+        dpr[i] = from_f<T>(dp[i]);
+        dbias[i] += dp[i];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 13; ++i) {
+      float v = dbias[i];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+      if ((threadIdx.x & 31) == 0) sbias[threadIdx.x >> 5][i] = v;
+    }
+  }
 
   for (int tb = t_lo; tb < t_hi; tb += GPB) {
     const int t = tb + grp;
@@ -459,24 +489,6 @@ __global__ void __launch_bounds__(256) scanprep_bwd_kernel(const T *__restrict__
         }
       }
     }
-    // coefficient map VJP (one lane per row)
-    if (live && q == 0) {
-      float p[13], dp[13];
-      const T *pr = params + in_row * d.ps + (long long)h * 13;
-#pragma unroll
-      for (int i = 0; i < 13; ++i) p[i] = to_f(pr[i]) + bias[h * 13 + i];
-      CoefCtx ctx;
-      coef_forward(p, hp, &ctx);
-      float2 dm = *reinterpret_cast<const float2 *>(dM + orow * 2);
-      float4 dk = *reinterpret_cast<const float4 *>(dK + orow * 4);
-      coef_backward(ctx, hp, dm, make_float2(dk.x, dk.y), make_float2(dk.z, dk.w), dp);
-      T *dpr = d_params + in_row * ((long long)d.H * 13) + (long long)h * 13;
-#pragma unroll
-      for (int i = 0; i < 13; ++i) {
-        dpr[i] = from_f<T>(dp[i]);
-        dbias[i] += dp[i];
-      }
-    }
   }
   // ---- CTA-level reduction in a fixed order ----
   {
@@ -489,9 +501,6 @@ __global__ void __launch_bounds__(256) scanprep_bwd_kernel(const T *__restrict__
 #pragma unroll
           for (int i = 0; i < VEC; ++i) mine[j * d.N + n0 + i] = dsc[k][j][i];
     }
-    if (q == 0)
-#pragma unroll
-      for (int i = 0; i < 13; ++i) mine[4 * d.N + i] = dbias[i];
   }
   __syncthreads();
   float *outp = part + ((size_t)bh * gridDim.x + blockIdx.x) * W;
@@ -501,7 +510,11 @@ __global__ void __launch_bounds__(256) scanprep_bwd_kernel(const T *__restrict__
       continue;
     }
     float acc = 0.f;
-    for (int g = 0; g < GPB; ++g) acc += red[(size_t)g * W + e];
+    if (e < 4 * d.N) {
+      for (int g = 0; g < GPB; ++g) acc += red[(size_t)g * W + e];
+    } else {
+      for (int w = 0; w < 8; ++w) acc += sbias[w][e - 4 * d.N];
+    }
     outp[e] = acc;
   }
 }
