@@ -201,6 +201,73 @@ def run_reference_arm(args, cfg):
     return 0
 
 
+def run_context_parallel(args) -> int:
+    """BASELINE config 4: batch 1, heads 32, P 64, N 128, T 262144, bf16 / fp32 state, the
+    sequence split over the ranks; only chunk-final states and one-token halos cross ranks
+    (NCCL send/recv over NVLink).  Strong scaling: total work fixed."""
+    import torch
+    import torch.distributed as dist
+
+    from slinoss_b200.context_parallel import v2x2ssd_context_parallel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world == 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    else:
+        dist.init_process_group("nccl", device_id=dev)
+    T, L = args.cp_T, args.chunk
+    T_loc = T // world
+    cfg = dict(batch=1, heads=32, T=T_loc, P=64, N=128)
+    inp = make_inputs(cfg, dev, seed=77 + rank, dtype=torch.bfloat16)
+    leaves = [inp[k].requires_grad_(True) for k in ("U", "M", "K", "B", "C")]
+
+    def step():
+        Y, _ = v2x2ssd_context_parallel(*leaves, chunk_size=L)
+        torch.autograd.grad(Y, leaves, inp["dY"])
+
+    W, K = max(args.warmup, 3), args.steps
+    for _ in range(W):
+        step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        step()
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = float(t.item()) / K
+    peaks = _peaks()
+    alg = algorithmic_bytes_per_head_token(64, 256) * 32 * T
+    if rank == 0:
+        per_gpu_gbs = alg / world / (ms_step * 1e-3) / 1e9
+        print(json.dumps(dict(
+            metric="v2x2ssd fwd+bwd tokens/sec, context-parallel (b1 H32 P64 N128, bf16 in / fp32 state)",
+            value=T / (ms_step * 1e-3), unit="tokens/s", n_gpus=world, steps=K, warmup=W, ms_per_step=ms_step,
+            higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
+            config=dict(workload=f"context-parallel v2x2ssd fwd+bwd b1 H32 P64 N128 T{T} chunk {L}, "
+                                 f"{T_loc} tokens per rank", exchange="chunk-final state + 1-token halo per hop, "
+                                 "NCCL send/recv", l2="inputs larger than L2"),
+            clocks=clocks, gpu_launches=(8 + 3) * K,
+            roofline_whole_op=dict(bound="hbm", achieved=per_gpu_gbs, peak=peaks["hbm_gbs"], unit="GB/s per GPU",
+                                   frac=per_gpu_gbs / peaks["hbm_gbs"], peak_source=peaks["source"]))))
+    dist.destroy_process_group()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -212,10 +279,16 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=HEADLINE["batch"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--mode", default="batch", choices=["batch", "cp"],
+                    help="batch: every rank runs its own (batch x heads) shard (headline, weak scaling); "
+                         "cp: one b1 H32 T262144 sequence split over the ranks along time (strong scaling)")
+    ap.add_argument("--cp-T", type=int, default=262144)
     args = ap.parse_args()
     cfg = dict(HEADLINE, T=args.T, batch=args.batch)
     if args.impl == "reference":
         return run_reference_arm(args, cfg)
+    if args.mode == "cp":
+        return run_context_parallel(args)
 
     import torch
     import torch.distributed as dist
