@@ -81,9 +81,11 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
       reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char *tQ = base;               // [128][64]  Qbar slab   (also the Y staging tile)
   unsigned char *tK = base + 16384;       // [128][64]  kappa slab
+  unsigned char *tS = base;               // 2 x [128][64]  S' (over the Qbar and kappa tiles, idle by then)
   unsigned char *tU = base + 32768;       // [128][64]  U
-  unsigned char *tS = base + 49152;       // 2 x [128][64]  S'
-  unsigned char *tZ = base + 81920;       // [64][64]   Z0 slab
+  unsigned char *tZ = base + 49152;       // [64][64]   Z0 slab
+  unsigned char *sC = base + 57344;       // raw C slab, filled by cp.async one slab ahead
+  unsigned char *sB = base + 73728;       // raw B slab
   float *lp = reinterpret_cast<float *>(base + 90112);  // 128
   float2 *ph = reinterpret_cast<float2 *>(lp + L);      // 128 each from here
   float2 *mraw = ph + L, *kc = mraw + L, *kp = kc + L, *gk = kp + L, *cbv = gk + L, *cbm = cbv + L;
@@ -100,7 +102,51 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   const size_t tok0 = (size_t)bh * d.T + t0;
   const int NB = d.D / 64;
   const uint32_t mbar_s = umma::smem_u32(&mbar);
+  const int j = tid & 7, r0 = tid >> 3;  // staging: 16-byte chunk j of rows r0 + 32 i
+  const float *z0 = a.starts + ((size_t)bh * d.NC + c) * P * d.D;
+  auto prefetch_cb = [&](int sl) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = r0 + 32 * i;
+      const int rr = r < valid ? r : 0;
+      const uint32_t nbytes = r < valid ? 16u : 0u;
+      const size_t g = (tok0 + rr) * d.D + sl * 64 + 8 * j;
+      const uint32_t off = umma::swz_off(r, j);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(umma::smem_u32(sC + off)), "l"(a.C + g),
+                   "r"(nbytes)
+                   : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(umma::smem_u32(sB + off)), "l"(a.B + g),
+                   "r"(nbytes)
+                   : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float4 zr[2][2];
+  auto prefetch_z = [&](int sl) {
+#pragma unroll
+    for (int k2 = 0; k2 < 2; ++k2) {
+      const int q = tid + kTcThreads * k2;
+      const float4 *src = reinterpret_cast<const float4 *>(z0 + (size_t)(q >> 3) * d.D + sl * 64 + 8 * (q & 7));
+      zr[k2][0] = src[0];
+      zr[k2][1] = src[1];
+    }
+  };
+  // U tile straight into its operand tile (no transform needed), same commit group as slab 0
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = r0 + 32 * i;
+    const int rr = r < valid ? r : 0;
+    const uint32_t nbytes = r < valid ? 16u : 0u;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(umma::smem_u32(tU + umma::swz_off(r, j))),
+                 "l"(a.U + (tok0 + rr) * P + 8 * j), "r"(nbytes)
+                 : "memory");
+  }
+  prefetch_cb(0);
+  prefetch_z(0);
 
+  const bool stamp_on = (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0);
+#define SLX_FSTAMP(i) do { if (stamp_on) g_phase_clock[64 + (i)] = clock64(); } while (0)
+  SLX_FSTAMP(0);
   if (warp == 0) umma::tmem_alloc(&tmem_slot, 256);
   if (tid == 32) {
     umma::mbar_init(mbar_s, 1);
@@ -130,15 +176,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
     else if (a.Bprev) bv = *reinterpret_cast<const float2 *>(a.Bprev + (size_t)bh * d.D + 2 * tid);
     bm1[tid] = bv;
   }
-  // U tile: thread owns chunk j of rows r0 + 32 i
-  const int j = tid & 7, r0 = tid >> 3;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    int r = r0 + 32 * i;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < valid) v = *reinterpret_cast<const uint4 *>(a.U + (tok0 + r) * P + 8 * j);
-    *reinterpret_cast<uint4 *>(tU + umma::swz_off(r, j)) = v;
-  }
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
@@ -151,7 +188,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   }
   __syncthreads();
 
-  const float *z0 = a.starts + ((size_t)bh * d.NC + c) * P * d.D;
   const uint32_t sQ = umma::smem_u32(tQ), sK = umma::smem_u32(tK), sU = umma::smem_u32(tU), sS = umma::smem_u32(tS),
                  sZ = umma::smem_u32(tZ);
   constexpr int fmt = umma::HalfFmt<T>::value;
@@ -161,31 +197,23 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   uint32_t phase = 0;
   bool ok = true;
 
+  SLX_FSTAMP(1);
   for (int sl = 0; sl < NB; ++sl) {
-    // raw loads of this slab into registers (overlap the previous slab's MMAs)
-    uint4 cr[4], br[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      int r = r0 + 32 * i;
-      cr[i] = br[i] = make_uint4(0, 0, 0, 0);
-      if (r < valid) {
-        cr[i] = *reinterpret_cast<const uint4 *>(a.C + (tok0 + r) * d.D + sl * 64 + 8 * j);
-        br[i] = *reinterpret_cast<const uint4 *>(a.B + (tok0 + r) * d.D + sl * 64 + 8 * j);
-      }
-    }
-    float4 zr[2][2];
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      int q = tid + kTcThreads * k;
-      int p = q >> 3, jj = q & 7;
-      const float4 *src = reinterpret_cast<const float4 *>(z0 + (size_t)p * d.D + sl * 64 + 8 * jj);
-      zr[k][0] = src[0];
-      zr[k][1] = src[1];
-    }
+    SLX_FSTAMP(8 + 4 * sl);
+    // this slab's raw C, B arrived through cp.async (issued one slab ahead)
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (sl > 0) {
       ok = umma::mbar_wait(mbar_s, phase) && ok;  // previous slab's products are done: tiles are free
       phase ^= 1;
     }
+    uint4 cr[4], br[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t off = umma::swz_off(r0 + 32 * i, j);
+      cr[i] = *reinterpret_cast<const uint4 *>(sC + off);
+      br[i] = *reinterpret_cast<const uint4 *>(sB + off);
+    }
+    SLX_FSTAMP(9 + 4 * sl);
     // b_{-1} chunk of this slab (for the boundary score)
     uint4 bm;
     {
@@ -214,7 +242,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
       *reinterpret_cast<uint4 *>(tZ + umma::swz_off(p, jj)) = pack8<T>(tmp);
     }
     umma::fence_smem_to_async();
+    SLX_FSTAMP(10 + 4 * sl);
     __syncthreads();
+    SLX_FSTAMP(11 + 4 * sl);
     if (tid == 0) {
       umma::fence_after_sync();
       const uint32_t id_s = umma::make_idesc(128, 128, false, false, fmt);
@@ -227,7 +257,12 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
       }
       umma::commit(mbar_s);
     }
+    if (sl + 1 < NB) {  // staging tiles were consumed before the barrier: refill them
+      prefetch_cb(sl + 1);
+      prefetch_z(sl + 1);
+    }
   }
+  SLX_FSTAMP(2);
   // per-row dots: cb_t = <c_t, b_t>, cbm_t = <c_t, b_{-1}>
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -242,6 +277,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   umma::fence_after_sync();
   __syncthreads();
 
+  SLX_FSTAMP(3);
   // ---- S -> S' (decay, causal mask, diagonal) -> bf16 A operand ----------------------
   const int q4 = warp & 3, h = warp >> 2;
   const int t = 32 * q4 + lane;
@@ -273,6 +309,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   }
   umma::fence_smem_to_async();
   umma::fence_before_sync();
+  SLX_FSTAMP(4);
   __syncthreads();
   if (tid == 0) {
     umma::fence_after_sync();
@@ -287,6 +324,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   phase ^= 1;
   umma::fence_after_sync();
 
+  SLX_FSTAMP(5);
   // ---- Y = Yd + exp(lp_t) Yo + sigma_t u_{-1} -> staging tile -> global ---------------
   {
     float yo[32], yd[32];
@@ -308,8 +346,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
     if (r < valid)
       *reinterpret_cast<uint4 *>(a.Y + (tok0 + r) * P + 8 * j) = *reinterpret_cast<const uint4 *>(tQ + umma::swz_off(r, j));
   }
+  SLX_FSTAMP(6);
   if (!ok && tid == 0) atomicExch(&g_tc_status, 1);
   if (warp == 0) umma::tmem_dealloc(tmem, 256);
+#undef SLX_FSTAMP
 }
 
 // ---------------------------------------------------------------------------
