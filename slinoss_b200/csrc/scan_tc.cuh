@@ -389,14 +389,49 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_outer_tc_kernel(OuterArgs
     umma::mbar_init(mbar_s, 1);
     umma::fence_mbar_init();
   }
-  chunk_prefix_warp<true>(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, nullptr);
+  // Every operand byte of the chunk is requested before any arithmetic: the A tile lands in
+  // place, the X slabs land raw in their operand tiles and are weighted in place by the
+  // thread that requested them once the chunk's coefficients exist.
   const int j = tid & 7, r0 = tid >> 3;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    int r = r0 + 32 * i;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < valid) v = *reinterpret_cast<const uint4 *>(a.A + (tok0 + r) * P + 8 * j);
-    *reinterpret_cast<uint4 *>(tA + umma::swz_off(r, j)) = v;
+    const int r = r0 + 32 * i;
+    const int rr = r < valid ? r : 0;
+    const uint32_t nbytes = r < valid ? 16u : 0u;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(umma::smem_u32(tA + umma::swz_off(r, j))),
+                 "l"(a.A + (tok0 + rr) * P + 8 * j), "r"(nbytes)
+                 : "memory");
+    for (int sl = 0; sl < NB; ++sl)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                       umma::smem_u32(tX + 16384 * sl + umma::swz_off(r, j))),
+                   "l"(a.X + (tok0 + rr) * d.D + sl * 64 + 8 * j), "r"(nbytes)
+                   : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  // scalar inputs of the coefficient phase, requested before the prefix so that they are in
+  // registers by the time it ends
+  float2 kcv = make_float2(0.f, 0.f), kpn = kcv, bv = kcv;
+  if (MODE == 0) {
+    if (tid < L) {
+      if (tid < valid) kcv = *reinterpret_cast<const float2 *>(a.K + (tok0 + tid) * 4 + 2);
+      if (tid + 1 < valid) kpn = *reinterpret_cast<const float2 *>(a.K + (tok0 + tid + 1) * 4);
+    } else if (tid - L < d.N) {
+      const int n = tid - L;
+      if (valid > 0) kpn = *reinterpret_cast<const float2 *>(a.K + tok0 * 4);
+      if (t0 > 0) bv = load_pair<T>(a.X + (tok0 - 1) * d.D + 2 * n);
+      else if (a.Bprev) bv = *reinterpret_cast<const float2 *>(a.Bprev + (size_t)bh * d.D + 2 * n);
+    }
+  }
+  chunk_prefix_warp<true>(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, nullptr);
+  if (MODE == 0 && warp == 2) {
+    // chunk transition = product of the raw multipliers: four per lane, then a butterfly
+    float2 acc = cmul(cmul(mraw[4 * lane], mraw[4 * lane + 1]), cmul(mraw[4 * lane + 2], mraw[4 * lane + 3]));
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const float ox = __shfl_xor_sync(0xffffffffu, acc.x, off), oy = __shfl_xor_sync(0xffffffffu, acc.y, off);
+      acc = cmul(acc, make_float2(ox, oy));
+    }
+    if (lane == 0) *reinterpret_cast<float2 *>(a.m_chunk + ((size_t)bh * d.NC + c) * 2) = acc;
   }
   if (MODE == 0 && tid >= 192) {
     int p = tid - 192;
@@ -413,9 +448,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_outer_tc_kernel(OuterArgs
     const int t = tid;
     float2 cf;
     if (MODE == 0) {
-      float2 kcv = make_float2(0.f, 0.f), kpn = kcv;
-      if (t < valid) kcv = *reinterpret_cast<const float2 *>(a.K + (tok0 + t) * 4 + 2);
-      if (t + 1 < valid) kpn = *reinterpret_cast<const float2 *>(a.K + (tok0 + t + 1) * 4);
       if (t + 1 < L) {
         float2 gam = cadd(cmul(mraw[t + 1], kcv), kpn);
         cf = cmul(cscale(cmulc(ph[L - 1], ph[t + 1]), __expf(lp[L - 1] - lp[t + 1])), gam);
@@ -428,27 +460,17 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_outer_tc_kernel(OuterArgs
     coef[t] = cf;
   } else if (MODE == 0 && tid - L < d.N) {
     const int n = tid - L;
-    float2 k0p = make_float2(0.f, 0.f);
-    if (valid > 0) k0p = *reinterpret_cast<const float2 *>(a.K + tok0 * 4);
-    k0p = cmul(cscale(cmulc(ph[L - 1], ph[0]), __expf(lp[L - 1] - lp[0])), k0p);
-    float2 bv = make_float2(0.f, 0.f);
-    if (t0 > 0) bv = load_pair<T>(a.X + (tok0 - 1) * d.D + 2 * n);
-    else if (a.Bprev) bv = *reinterpret_cast<const float2 *>(a.Bprev + (size_t)bh * d.D + 2 * n);
+    const float2 k0p = cmul(cscale(cmulc(ph[L - 1], ph[0]), __expf(lp[L - 1] - lp[0])), kpn);
     bh1[n] = cmul(k0p, bv);
   }
-  if (MODE == 0 && tid == 255) {
-    float2 acc = make_float2(1.f, 0.f);
-    for (int t = 0; t < L; ++t) acc = cmul(acc, mraw[t]);
-    *reinterpret_cast<float2 *>(a.m_chunk + ((size_t)bh * d.NC + c) * 2) = acc;
-  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
   for (int sl = 0; sl < NB; ++sl) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      int r = r0 + 32 * i;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (r < valid) v = *reinterpret_cast<const uint4 *>(a.X + (tok0 + r) * d.D + sl * 64 + 8 * j);
-      *reinterpret_cast<uint4 *>(tX + 16384 * sl + umma::swz_off(r, j)) = rotate_chunk<T>(v, coef[r]);
+      const int r = r0 + 32 * i;
+      uint4 *slot = reinterpret_cast<uint4 *>(tX + 16384 * sl + umma::swz_off(r, j));
+      *slot = rotate_chunk<T>(*slot, coef[r]);
     }
   }
   umma::fence_smem_to_async();
