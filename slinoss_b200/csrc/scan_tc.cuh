@@ -66,6 +66,32 @@ __device__ __forceinline__ uint4 pack8(const float *v) {
   return out;
 }
 
+// Decay, causal mask and diagonal of one 32-column block of a score tile:
+//   v[i] <- v[i] exp(lp_row - lp_{s+1})  for s = c0 + i < row,   diag  for s == row,   0 above.
+// FAST factors the exponential as exp(lp_row - lp_{c0+1}) * e2[s] with the per-chunk table
+//   e2[s] = exp(lp_{b+1} - lp_{s+1}),  b = 32 (s / 32),
+// one exponential per thread instead of one per element.  The table cannot overflow while
+// every per-token log-magnitude lies in [-1.9, 0.5] (31 * 1.9 < 88); chunks outside that
+// range take the per-element path (decay_table_ok is evaluated once per chunk).
+__device__ __forceinline__ bool decay_step_out_of_range(const float *lp, int t) {
+  const float lg = lp[t] - (t > 0 ? lp[t - 1] : 0.f);
+  return lg < -1.9f || lg > 0.5f;
+}
+__device__ __forceinline__ float decay_table_entry(const float *lp, int s, int L) {
+  return (s + 1 < L) ? __expf(lp[32 * (s >> 5) + 1] - lp[s + 1]) : 0.f;
+}
+template <bool FAST>
+__device__ __forceinline__ void decay_mask32(float (&v)[32], int c0, int row, float lp_row, const float *lp,
+                                             const float *e2, float diag) {
+  const float rf = FAST ? __expf(lp_row - lp[c0 + 1]) : 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int s = c0 + i;
+    const float f = FAST ? rf * e2[s] : __expf(lp_row - lp[min(s + 1, kTcL - 1)]);
+    v[i] = (s < row) ? v[i] * f : (s == row ? diag : 0.f);
+  }
+}
+
 constexpr size_t scan_fwd_tc_smem_bytes() { return 1024 + 88 * 1024 + 12 * 1024; }
 
 // Forward chunk scan (replaces reference.py:1059 chunk_scan) on tensor cores.
@@ -91,6 +117,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   float2 *mraw = ph + L, *kc = mraw + L, *kp = kc + L, *gk = kp + L, *cbv = gk + L, *cbm = cbv + L;
   float2 *bm1 = cbm + L;                                 // 128 (b_{-1}, all of D)
   float *um1 = reinterpret_cast<float *>(bm1 + 128);     // 64
+  float *e2 = um1 + 64;                                  // 128: decay table (decay_mask32)
   __shared__ uint64_t mbar;
   __shared__ uint32_t tmem_slot;
 
@@ -185,8 +212,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
     float2 g = make_float2(0.f, 0.f);
     if (t + 1 < L) g = cmulc(cadd(cmul(mraw[t + 1], kc[t]), kp[t + 1]), ph[t + 1]);  // gamma_t conj(phi_{t+1})
     gk[t] = g;
+    e2[t] = decay_table_entry(lp, t, L);
   }
-  __syncthreads();
+  const bool fast_decay = !__syncthreads_or(tid < L && decay_step_out_of_range(lp, tid));
 
   const uint32_t sQ = umma::smem_u32(tQ), sK = umma::smem_u32(tK), sU = umma::smem_u32(tU), sS = umma::smem_u32(tS),
                  sZ = umma::smem_u32(tZ);
@@ -290,14 +318,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
       float v[32];
       if (c0 <= 32 * q4 + 31) {
         umma::tmem_ld32(umma::tmem_addr(tmem, 32 * q4, c0), v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          int s = c0 + i;
-          float x = 0.f;
-          if (s < t) x = v[i] * __expf(lpt - lp[s + 1]);
-          else if (s == t) x = dg;
-          v[i] = x;
-        }
+        if (fast_decay) decay_mask32<true>(v, c0, t, lpt, lp, e2, dg);
+        else decay_mask32<false>(v, c0, t, lpt, lp, e2, dg);
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0.f;

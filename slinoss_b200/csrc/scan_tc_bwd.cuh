@@ -59,6 +59,11 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
   float2 *bh1 = ul1 + 128;                   // 128  w_{-1} b_{-1}
   float2 *misc = bh1 + 128;                  // [0] bLam(last row) [1] dk^p_0 [2] w_{-1} [3] p_{L-1}/p_0
   float *ulw = reinterpret_cast<float *>(misc + 4);  // [16][64] per-warp partials of u_{-1}.Lambda
+  float *e2 = ulw + 16 * 64;                          // 128: decay table (decay_mask32)
+  float *xb = e2 + L;                                 // 256: row 127 of X (boundary column sums), all slabs
+  float *ulf = xb + 256;                              // 256: u_{-1} . Lambda, all slabs
+  unsigned char *sC = base + 147456 + 28672;          // raw C slab (swizzled tile), filled by cp.async
+  unsigned char *sB = sC + 16384;                     // raw B slab
   __shared__ uint64_t mbar;
   __shared__ uint32_t tmem_slot;
 
@@ -75,6 +80,58 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
   const bool stamp_on = (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0);
 #define SLX_STAMP(i) do { if (stamp_on) g_phase_clock[i] = clock64(); } while (0)
   SLX_STAMP(0);
+  const int j = tid & 7, r0 = tid >> 3;  // r0 in [0,64)
+  const float *z0 = a.starts + ((size_t)bh * d.NC + c) * P * d.D;
+  const float *lam = a.d_inc + ((size_t)bh * d.NC + c) * P * d.D;
+  // U and dY land in their operand tiles by asynchronous copy (rows past the chunk end are
+  // zero-filled); the first raw (C, B) slab follows as a second group
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = r0 + 64 * i;
+    const int rr = r < valid ? r : 0;
+    const uint32_t nbytes = r < valid ? 16u : 0u;
+    const uint32_t off = umma::swz_off(r, j);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(umma::smem_u32(tU + off)),
+                 "l"(a.U + (tok0 + rr) * P + 8 * j), "r"(nbytes)
+                 : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(umma::smem_u32(tdY + off)),
+                 "l"(a.dY + (tok0 + rr) * P + 8 * j), "r"(nbytes)
+                 : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  // asynchronous copy of one raw (C, B) slab into the staging tiles: every thread copies the
+  // chunks it will itself transform
+  auto prefetch_cb = [&](int sl) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = r0 + 64 * i;
+      const int rr = r < valid ? r : 0;
+      const uint32_t nbytes = r < valid ? 16u : 0u;
+      const size_t g = (tok0 + rr) * d.D + sl * 64 + 8 * j;
+      const uint32_t off = umma::swz_off(r, j);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(umma::smem_u32(sC + off)), "l"(a.C + g),
+                   "r"(nbytes)
+                   : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(umma::smem_u32(sB + off)), "l"(a.B + g),
+                   "r"(nbytes)
+                   : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  prefetch_cb(0);
+  // Z0 / Lambda slab (fp32): one 8-float item per thread, prefetched into registers
+  const int zp = tid >> 3, zj = tid & 7;
+  float4 zr0, zr1, lr0, lr1;
+  auto prefetch_zl = [&](int sl) {
+    const float4 *zs = reinterpret_cast<const float4 *>(z0 + (size_t)zp * d.D + sl * 64 + 8 * zj);
+    const float4 *ls = reinterpret_cast<const float4 *>(lam + (size_t)zp * d.D + sl * 64 + 8 * zj);
+    zr0 = zs[0];
+    zr1 = zs[1];
+    lr0 = ls[0];
+    lr1 = ls[1];
+  };
+  prefetch_zl(0);
+
   if (warp == 0) umma::tmem_alloc(&tmem_slot, 512);
   if (tid == 32) {
     umma::mbar_init(mbar_s, 1);
@@ -105,29 +162,30 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
     else if (a.Bprev) bv = *reinterpret_cast<const float2 *>(a.Bprev + (size_t)bh * d.D + 2 * n);
     bm1[n] = bv;
   }
-  const int j = tid & 7, r0 = tid >> 3;  // r0 in [0,64)
-  uint4 dyr[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    int r = r0 + 64 * i;
-    uint4 u = make_uint4(0, 0, 0, 0);
-    dyr[i] = u;
-    if (r < valid) {
-      u = *reinterpret_cast<const uint4 *>(a.U + (tok0 + r) * P + 8 * j);
-      dyr[i] = *reinterpret_cast<const uint4 *>(a.dY + (tok0 + r) * P + 8 * j);
-    }
-    *reinterpret_cast<uint4 *>(tU + umma::swz_off(r, j)) = u;
-    *reinterpret_cast<uint4 *>(tdY + umma::swz_off(r, j)) = dyr[i];
-  }
+  asm volatile("cp.async.wait_group 1;" ::: "memory");  // U, dY tiles (the slab group may still be in flight)
+  umma::fence_smem_to_async();
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
   const uint32_t tmem = tmem_slot;
+  const uint32_t sdY = umma::smem_u32(tdY), sdYe = umma::smem_u32(tdYe), sU = umma::smem_u32(tU),
+                 sdS = umma::smem_u32(tdS), sQ = umma::smem_u32(tQ), sK = umma::smem_u32(tK),
+                 sBh = umma::smem_u32(tBh), sZ = umma::smem_u32(tZ), sLm = umma::smem_u32(tLm);
+  SLX_STAMP(1);
+  // ---- G = dY U^T (runs while the per-token coefficients are computed) -----------------------
+  if (tid == 0) {
+    const uint32_t id = umma::make_idesc(128, 128, false, false, fmt);
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk)
+      umma::mma_ss(tmem, umma::desc_kmajor(sdY, kk), umma::desc_kmajor(sU, kk), id, kk != 0);
+    umma::commit(mbar_s);
+  }
   // exp(lp_t) dY and g_{-1}[t] = dY_t . u_{-1}
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     int r = r0 + 64 * i;
-    const uint32_t *w = reinterpret_cast<const uint32_t *>(&dyr[i]);
+    const uint4 dyr = *reinterpret_cast<const uint4 *>(tdY + umma::swz_off(r, j));
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(&dyr);
     const float el = __expf(lp[r]);
     float tmp[8], dot = 0.f;
 #pragma unroll
@@ -158,6 +216,7 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
     gk[t] = gkv;
     sg1[t] = s1;
     wco[t] = w;
+    e2[t] = decay_table_entry(lp, t, L);
   } else if (tid >= 256 && tid < 256 + d.N) {
     const int n = tid - 256;
     const float2 s0 = cscale(cmulc(ph[L - 1], ph[0]), __expf(lp[L - 1] - lp[0]));  // p_{L-1}/p_0
@@ -170,26 +229,12 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
     }
   }
   umma::fence_smem_to_async();
-  __syncthreads();
+  const bool fast_decay = !__syncthreads_or(tid < L && decay_step_out_of_range(lp, tid));
 
-  const uint32_t sdY = umma::smem_u32(tdY), sdYe = umma::smem_u32(tdYe), sU = umma::smem_u32(tU),
-                 sdS = umma::smem_u32(tdS), sQ = umma::smem_u32(tQ), sK = umma::smem_u32(tK),
-                 sBh = umma::smem_u32(tBh), sZ = umma::smem_u32(tZ), sLm = umma::smem_u32(tLm);
   uint32_t phase = 0;
   bool ok = true;
   const int q4 = warp & 3, qc = warp >> 2;  // lane quarter of tensor memory, column quarter
   const int row = 32 * q4 + lane;
-
-  SLX_STAMP(1);
-  // ---- G = dY U^T -> dS' ---------------------------------------------------------
-  if (tid == 0) {
-    umma::fence_after_sync();
-    const uint32_t id = umma::make_idesc(128, 128, false, false, fmt);
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk)
-      umma::mma_ss(tmem, umma::desc_kmajor(sdY, kk), umma::desc_kmajor(sU, kk), id, kk != 0);
-    umma::commit(mbar_s);
-  }
 #include "scan_tc_bwd_body.inc"
 #undef SLX_STAMP
 }

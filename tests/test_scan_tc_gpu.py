@@ -96,3 +96,22 @@ def test_backward_tc_vs_exact_and_oracle(N, T, dtype, streaming):
         errs_or[k] = rel_err(to_np(g_tc[k]), go[k])
     assert all(v < 2e-2 for v in errs_or.values()), ("oracle", errs_or, "exact", errs_ex)
     assert all(v < 2e-2 for v in errs_ex.values()), ("exact", errs_ex)
+
+
+def test_strong_decay_takes_per_element_path():
+    """Multipliers of magnitude < exp(-1.9) switch a chunk from the factored decay table to one
+    exponential per score; both paths must agree with the oracle."""
+    inp = make_scan_inputs(1, 2, 384, 64, 64, torch.bfloat16, seed=91, streaming=True, with_init=True,
+                           dist="tests")
+    M = inp["M"].clone()
+    M[:, 0, ::7] *= 0.2          # head 0: every 7th token has |m| in [0.12, 0.19]; head 1 stays on the table path
+    inp["M"] = M.contiguous()
+    Y, fin, grads = run_b200_fwd_bwd(inp, 128)
+    Yo, fino, go = oracle_fwd_bwd(inp)
+    errs = {"Y": rel_err(to_np(Y), Yo), "final": rel_err(to_np(fin), fino)}
+    errs.update({k: rel_err(to_np(grads[k]), go[k]) for k in SCAN_GRADS if grads[k] is not None})
+    # dM is the accumulated sum divided by conj(m): small |m| amplifies the half-precision
+    # rounding of that sum, so dM alone gets a wider band here
+    tol = {k: 2e-2 for k in errs}
+    tol["dM"] = 4e-2
+    assert all(errs[k] < tol[k] for k in errs), errs
