@@ -33,7 +33,12 @@ def _peaks():
     return 6650.0, 1400.0, "fallback"
 
 
-def _time(fn, reps=10, warm=3):
+REPS, WARM = 10, 3   # overridden by --reps / --warm (a profiler capture wants few launches)
+
+
+def _time(fn, reps=None, warm=None):
+    reps = REPS if reps is None else reps
+    warm = WARM if warm is None else warm
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
@@ -210,7 +215,11 @@ def main():
     ap.add_argument("--no-scan", action="store_true")
     ap.add_argument("--prep", action="store_true")
     ap.add_argument("--conv", action="store_true")
+    ap.add_argument("--reps", type=int, default=10, help="timed launches per stage")
+    ap.add_argument("--warm", type=int, default=3, help="untimed launches per stage")
     a = ap.parse_args()
+    global REPS, WARM
+    REPS, WARM = max(a.reps, 1), max(a.warm, 0)
     dt = dict(bf16=torch.bfloat16, f16=torch.float16, f32=torch.float32)[a.dtype]
     if not a.no_scan:
         scan_stages(a.batch, a.heads, a.T, a.P, a.N, a.chunk, dt)

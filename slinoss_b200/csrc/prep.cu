@@ -345,7 +345,7 @@ __global__ void __launch_bounds__(256) scanprep_fwd_kernel(const T *__restrict__
 // shared memory in a fixed order) and then across CTAs in a second kernel.
 // Partial layout: part[(bh * n_tiles + tile)][4*N + 13].
 template <typename T, int VEC, int G, int KMAX>
-__global__ void __launch_bounds__(256) scanprep_bwd_kernel(const T *__restrict__ params, const T *__restrict__ bc,
+__global__ void __launch_bounds__(256, KMAX == 1 ? 2 : 1) scanprep_bwd_kernel(const T *__restrict__ params, const T *__restrict__ bc,
                                                            const float *__restrict__ bias,
                                                            const float *__restrict__ scale, const T *__restrict__ dU,
                                                            const float *__restrict__ dM, const float *__restrict__ dK,
@@ -403,6 +403,100 @@ __global__ void __launch_bounds__(256) scanprep_bwd_kernel(const T *__restrict__
     }
   }
 
+  // Single-sweep path (one 16-byte vector per lane covers N): the row's raw bc and dB/dC stay
+  // packed in registers (8 x 16 bytes) and are expanded twice, once for the row sums and once
+  // for the output, instead of holding expanded fp32 copies; the head's scale sits in shared memory.
+  constexpr bool kPacked = (KMAX == 1) && (VEC > 1) && (VEC * sizeof(T) == 16);
+  float *sscale = red + (size_t)GPB * W;
+  if (kPacked && d.normalize) {
+    for (int e = threadIdx.x; e < 4 * d.N; e += 256) sscale[e] = scale[(long long)h * 4 * d.N + e];
+    __syncthreads();
+  }
+  if constexpr (kPacked) {
+    const int n0 = q * VEC;
+    const bool lane_on = n0 < d.N;
+    for (int tb = t_lo; tb < t_hi; tb += GPB) {
+      const int t = tb + grp;
+      const bool live = (t < t_hi);
+      const int tt = live ? t : t_lo;
+      const long long in_row = (long long)b * d.T + tt;
+      const long long orow = ((long long)bh) * d.T + tt;
+      const T *bcr = bc + in_row * d.bs + (long long)h * 4 * d.N;
+      T *dbcr = d_bc + in_row * ((long long)d.H * 4 * d.N) + (long long)h * 4 * d.N;
+      uint4 xr[4], gr[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) xr[j] = gr[j] = make_uint4(0, 0, 0, 0);
+      if (live && lane_on) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) xr[j] = *reinterpret_cast<const uint4 *>(bcr + j * d.N + n0);
+        gr[0] = *reinterpret_cast<const uint4 *>(dB + orow * D + 2 * n0);
+        gr[1] = *reinterpret_cast<const uint4 *>(dB + orow * D + 2 * n0 + VEC);
+        gr[2] = *reinterpret_cast<const uint4 *>(dC + orow * D + 2 * n0);
+        gr[3] = *reinterpret_cast<const uint4 *>(dC + orow * D + 2 * n0 + VEC);
+      }
+      if (live) {
+        const T *src = dU + orow * d.P;
+        T *dst = d_value + in_row * ((long long)d.H * d.P) + (long long)h * d.P;
+        for (int p0 = q * VEC; p0 < d.P; p0 += G * VEC)
+          *reinterpret_cast<uint4 *>(dst + p0) = *reinterpret_cast<const uint4 *>(src + p0);
+      }
+      auto elem = [](const uint4 &raw, int i) { return to_f(reinterpret_cast<const T *>(&raw)[i]); };
+      // dy of (plane j, lane i): de-interleave (re, im) pairs of dB (j < 2) or dC
+      auto dy_of = [&](int j, int i) {
+        const int o = 2 * i + (j & 1);
+        return elem(gr[(j < 2 ? 0 : 2) + o / VEC], o % VEC);
+      };
+      if (d.normalize) {
+        float ss[4], gx[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float a = 0.f;
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) {
+            const float v = elem(xr[j], i);
+            a = fmaf(v, v, a);
+          }
+          ss[j] = rsqrtf(group_sum_f<G>(a) / (float)d.N + 1e-5f);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float a = 0.f;
+          const float4 s0 = *reinterpret_cast<const float4 *>(sscale + j * d.N + (lane_on ? n0 : 0));
+          const float4 s1 = *reinterpret_cast<const float4 *>(sscale + j * d.N + (lane_on ? n0 : 0) + 4);
+          const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) {
+            const float xv = elem(xr[j], i) * ss[j];
+            const float dy = dy_of(j, i);
+            dsc[0][j][i] = fmaf(dy, xv, dsc[0][j][i]);
+            a = fmaf(dy * sc[i], xv, a);
+          }
+          gx[j] = group_sum_f<G>(a) / (float)d.N;
+        }
+        if (live && lane_on) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 s0 = *reinterpret_cast<const float4 *>(sscale + j * d.N + n0);
+            const float4 s1 = *reinterpret_cast<const float4 *>(sscale + j * d.N + n0 + 4);
+            const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            float o[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i)
+              o[i] = ss[j] * (dy_of(j, i) * sc[i] - elem(xr[j], i) * ss[j] * gx[j]);
+            store_vec<T, VEC>(dbcr + j * d.N + n0, o);
+          }
+        }
+      } else if (live && lane_on) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float o[VEC];
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) o[i] = dy_of(j, i);
+          store_vec<T, VEC>(dbcr + j * d.N + n0, o);
+        }
+      }
+    }
+  } else
   for (int tb = t_lo; tb < t_hi; tb += GPB) {
     const int t = tb + grp;
     const bool live = t < t_hi;
@@ -605,7 +699,7 @@ static PrepBwdPlan prep_bwd_plan(const slx_prep_shape *s, int VEC) {
   p.rows_per_tile = 256;
   p.n_tiles = (s->T + p.rows_per_tile - 1) / p.rows_per_tile;
   int W = 4 * s->N + 13;
-  p.smem = sizeof(float) * (size_t)(256 / p.G) * W;
+  p.smem = sizeof(float) * ((size_t)(256 / p.G) * W + 4 * (size_t)s->N);  // group partials + the head's scale
   p.ws_bytes = sizeof(float) * (size_t)s->batch * s->heads * p.n_tiles * W;
   return p;
 }
