@@ -139,66 +139,82 @@ def scan_stages(b, h, T, P, N, L, dtype):
 
 
 def prep_stage(b, T, H, P, N, dtype):
-    import slinoss_b200 as sb
-
+    """scanprep forward / backward through the C ABI with preallocated buffers (kernel time only)."""
     dev = torch.device("cuda")
     hbm, tfl, src = _peaks()
     g = torch.Generator().manual_seed(1)
     es = torch.empty((), dtype=dtype).element_size()
-    value = torch.randn(b, T, H * P, generator=g).to(dtype).to(dev).requires_grad_(True)
-    params = torch.randn(b, T, H * 13, generator=g).to(dtype).to(dev).requires_grad_(True)
-    bc = torch.randn(b, T, H, 4, N, generator=g).to(dtype).to(dev).requires_grad_(True)
-    names = ("dt_bias", "gamma_bias", "omega_bias", "mix_r_bias", "mix_theta_bias", "mix_k_prev_bias",
-             "mix_k_curr_bias")
-    pars = {n: torch.zeros(H, device=dev, requires_grad=True) for n in names}
-    bs = torch.ones(H, 2, N, device=dev, requires_grad=True)
-    cs = torch.ones(H, 2, N, device=dev, requires_grad=True)
-    hp = dict(dt_min=1e-4, dt_max=1e-1, r_min=0.9, r_max=1.0, theta_bound=math.pi, k_max=0.5, eps=1e-8)
+    value = torch.randn(b, T, H * P, generator=g).to(dtype).to(dev)
+    params = torch.randn(b, T, H * 13, generator=g).to(dtype).to(dev)
+    bc = torch.randn(b, T, H * 4 * N, generator=g).to(dtype).to(dev)
+    bias = torch.zeros(H, 13, device=dev, dtype=torch.float32)
+    scale = torch.ones(H, 4, N, device=dev, dtype=torch.float32)
+    f32 = dict(device=dev, dtype=torch.float32)
+    U = torch.empty((b, H, T, P), device=dev, dtype=dtype)
+    Bo = torch.empty((b, H, T, 2 * N), device=dev, dtype=dtype)
+    Co = torch.empty_like(Bo)
+    M = torch.empty((b, H, T, 2), **f32)
+    K = torch.empty((b, H, T, 2, 2), **f32)
+    s = _lib.PrepShape(b, T, H, P, N, _lib.dtype_code(dtype), 1, 1e-4, 1e-1, 0.9, 1.0, math.pi, 0.5, 1e-8,
+                       H * P, H * 13, H * 4 * N)
+    lib, st, ck = _lib.lib(), _lib.stream_ptr(dev), _lib.check
 
     def fwd():
-        return sb.scanprep_b200(value, params, bc, n_heads=H, d_state=N, d_head=P, normalize_bc=True, **hp, **pars,
-                                b_scale=bs, c_scale=cs)
+        ck(lib.slx_scanprep_fwd(byref(s), value.data_ptr(), params.data_ptr(), bc.data_ptr(), bias.data_ptr(),
+                                scale.data_ptr(), U.data_ptr(), M.data_ptr(), K.data_ptr(), Bo.data_ptr(),
+                                Co.data_ptr(), st), "scanprep fwd")
 
-    with torch.no_grad():
-        ms = _time(fwd)
     rows = b * T * H
     per_row = es * (P + 13 + 4 * N) + es * (P + 4 * N) + 24
-    _emit("scanprep_fwd", ms, rows * per_row, 0, hbm, tfl, src)
-    si = fwd()
-    outs = [si.U, si.M, si.K, si.B, si.C]
-    gouts = [torch.randn_like(o) for o in outs]
-    leaves = [value, params, bc, bs, cs] + list(pars.values())
+    _emit("scanprep_fwd", _time(fwd), rows * per_row, 0, hbm, tfl, src)
+    dU, dB, dC = torch.randn_like(U), torch.randn_like(Bo), torch.randn_like(Co)
+    dM, dK = torch.randn_like(M), torch.randn_like(K)
+    d_value, d_params, d_bc = torch.empty_like(value), torch.empty_like(params), torch.empty_like(bc)
+    d_bias, d_scale = torch.empty_like(bias), torch.empty_like(scale)
+    nbytes = int(lib.slx_scanprep_bwd_workspace_bytes(byref(s)))
+    ws = torch.empty((max(nbytes, 16),), device=dev, dtype=torch.uint8)
 
     def bwd():
-        torch.autograd.grad(outs, leaves, gouts, retain_graph=True)
+        ck(lib.slx_scanprep_bwd(byref(s), params.data_ptr(), bc.data_ptr(), bias.data_ptr(), scale.data_ptr(),
+                                dU.data_ptr(), dM.data_ptr(), dK.data_ptr(), dB.data_ptr(), dC.data_ptr(),
+                                d_value.data_ptr(), d_params.data_ptr(), d_bc.data_ptr(), d_bias.data_ptr(),
+                                d_scale.data_ptr(), ws.data_ptr(), nbytes, st), "scanprep bwd")
 
-    ms = _time(bwd)
-    _emit("scanprep_bwd", ms, rows * (per_row + es * (13 + 4 * N)), 0, hbm, tfl, src,
+    _emit("scanprep_bwd", _time(bwd), rows * (per_row + es * (13 + 4 * N)), 0, hbm, tfl, src,
           dict(note="reads params, bc and all five gradients; writes d_value, d_params, d_bc"))
 
 
 def conv_stage(b, T, Cn, dtype):
-    import slinoss_b200 as sb
-
+    """Depthwise causal conv (width 4, bias, no activation) through the C ABI, kernel time only."""
     dev = torch.device("cuda")
     hbm, tfl, src = _peaks()
     g = torch.Generator().manual_seed(2)
     es = torch.empty((), dtype=dtype).element_size()
-    x = torch.randn(b, T, Cn, generator=g).to(dtype).to(dev).requires_grad_(True)
-    w = torch.randn(Cn, 4, generator=g).to(dtype).to(dev).requires_grad_(True)
-    bias = torch.randn(Cn, generator=g).to(dtype).to(dev).requires_grad_(True)
+    W = 4
+    x = torch.randn(b, T, Cn, generator=g).to(dtype).to(dev)
+    w = torch.randn(Cn, W, generator=g).to(dtype).to(dev)
+    bias = torch.randn(Cn, generator=g).to(dtype).to(dev)
+    y = torch.empty_like(x)
+    nxt = torch.empty((b, Cn, W - 1), device=dev, dtype=dtype)
+    s = _lib.ConvShape(b, T, Cn, W, _lib.dtype_code(dtype), 0, Cn, T * Cn)
+    lib, st, ck = _lib.lib(), _lib.stream_ptr(dev), _lib.check
 
     def fwd():
-        return sb.cconv1d_b200(x, w, bias, None)
+        ck(lib.slx_cconv1d_fwd(byref(s), x.data_ptr(), w.data_ptr(), bias.data_ptr(), None, y.data_ptr(),
+                               nxt.data_ptr(), st), "conv fwd")
 
-    with torch.no_grad():
-        ms = _time(fwd)
-    _emit("cconv1d_fwd", ms, b * T * Cn * 2 * es, 0, hbm, tfl, src)
-    y, _ = fwd()
-    gy = torch.randn_like(y)
+    _emit("cconv1d_fwd", _time(fwd), b * T * Cn * 2 * es, 0, hbm, tfl, src)
+    dy = torch.randn_like(y)
+    dx = torch.empty_like(x)
+    dw = torch.empty((Cn, W), device=dev, dtype=torch.float32)
+    db = torch.empty((Cn,), device=dev, dtype=torch.float32)
+    nbytes = int(lib.slx_cconv1d_bwd_workspace_bytes(byref(s)))
+    ws = torch.empty((max(nbytes, 16),), device=dev, dtype=torch.uint8)
 
     def bwd():
-        torch.autograd.grad(y, [x, w, bias], gy, retain_graph=True)
+        ck(lib.slx_cconv1d_bwd(byref(s), x.data_ptr(), w.data_ptr(), bias.data_ptr(), None, dy.data_ptr(), None,
+                               dx.data_ptr(), dw.data_ptr(), db.data_ptr(), None, ws.data_ptr(), nbytes, st),
+           "conv bwd")
 
     _emit("cconv1d_bwd", _time(bwd), b * T * Cn * 3 * es, 0, hbm, tfl, src)
 

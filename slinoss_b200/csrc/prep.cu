@@ -228,14 +228,103 @@ __global__ void __launch_bounds__(256) scanprep_fwd_kernel(const T *__restrict__
         *reinterpret_cast<float4 *>(K + row * 4) = make_float4(o.kp.x, o.kp.y, o.kc.x, o.kc.y);
       }
     }
+    // (b, h, t) of the group's first row by division once per pass, then by increment
+    const long long grow0 = row0 + (long long)grp * RPG;
+    int gt, gh, gb;
+    {
+      const long long r = grow0 < n_rows ? grow0 : 0;
+      gt = (int)(r % d.T);
+      gh = (int)((r / d.T) % d.H);
+      gb = (int)(r / ((long long)d.T * d.H));
+    }
+    constexpr bool kPacked = (VEC > 1) && (VEC * sizeof(T) == 16);
+    const bool one_sweep = d.N <= G * VEC;
+    // raw 16-byte slices of the next row (value + four bc planes), requested one row ahead
+    uint4 nx[5];
+    auto fetch_row = [&](long long row, int b, int h, int t) {
+      if constexpr (kPacked) {
+#pragma unroll
+        for (int j = 0; j < 5; ++j) nx[j] = make_uint4(0, 0, 0, 0);
+        if (row < n_rows) {
+          const long long in_row = (long long)b * d.T + t;
+          const int n0 = q * VEC;
+          if (n0 < d.P) nx[4] = *reinterpret_cast<const uint4 *>(value + in_row * d.vs + (long long)h * d.P + n0);
+          if (n0 < d.N) {
+            const T *bcr = bc + in_row * d.bs + (long long)h * 4 * d.N;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) nx[j] = *reinterpret_cast<const uint4 *>(bcr + j * d.N + n0);
+          }
+        }
+      }
+    };
+    const bool packed_path = kPacked && one_sweep && d.P <= G * VEC;
+    if (packed_path) fetch_row(grow0, gb, gh, gt);
     for (int k = 0; k < RPG; ++k) {
-      const long long row = row0 + (long long)grp * RPG + k;
+      const long long row = grow0 + k;
       const bool live = row < n_rows;
       const long long rr = live ? row : 0;
-      const int t = (int)(rr % d.T);
-      const int h = (int)((rr / d.T) % d.H);
-      const int b = (int)(rr / ((long long)d.T * d.H));
+      const int t = live ? gt : 0, h = live ? gh : 0, b = live ? gb : 0;
+      // advance (b, h, t) to the next row
+      if (++gt == d.T) {
+        gt = 0;
+        if (++gh == d.H) {
+          gh = 0;
+          ++gb;
+        }
+      }
       const long long in_row = (long long)b * d.T + t;
+      if constexpr (kPacked) {
+        if (packed_path) {
+          uint4 cur[5];
+#pragma unroll
+          for (int j = 0; j < 5; ++j) cur[j] = nx[j];
+          if (k + 1 < RPG) fetch_row(row + 1, gb, gh, gt);
+          const int n0 = q * VEC;
+          if (live && n0 < d.P) *reinterpret_cast<uint4 *>(U + rr * d.P + n0) = cur[4];
+          const bool mine = live && n0 < d.N;
+          float y[4][VEC];
+          float ss[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const T *e = reinterpret_cast<const T *>(&cur[j]);
+            float a = 0.f;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+              y[j][i] = to_f(e[i]);
+              a = fmaf(y[j][i], y[j][i], a);
+            }
+            ss[j] = a;
+          }
+          if (d.normalize) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              ss[j] = rsqrtf(group_sum_f<G>(ss[j]) / (float)d.N + 1e-5f);
+              if (mine) {
+                float sc[VEC];
+                load_vec<float, VEC>(scale + ((long long)h * 4 + j) * d.N + n0, sc);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) y[j][i] = (y[j][i] * ss[j]) * sc[i];
+              }
+            }
+          }
+          if (mine) {
+            float ob[2][VEC], oc[2][VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+              int o = 2 * i;
+              ob[o / VEC][o % VEC] = y[0][i];
+              ob[(o + 1) / VEC][(o + 1) % VEC] = y[1][i];
+              oc[o / VEC][o % VEC] = y[2][i];
+              oc[(o + 1) / VEC][(o + 1) % VEC] = y[3][i];
+            }
+            store_vec<T, VEC>(Bo + rr * D + 2 * n0, ob[0]);
+            store_vec<T, VEC>(Bo + rr * D + 2 * n0 + VEC, ob[1]);
+            store_vec<T, VEC>(Co + rr * D + 2 * n0, oc[0]);
+            store_vec<T, VEC>(Co + rr * D + 2 * n0 + VEC, oc[1]);
+          }
+          continue;
+        }
+      }
       // ---- U: copy P values ----
       if (live) {
         const T *src = value + in_row * d.vs + (long long)h * d.P;
@@ -248,7 +337,7 @@ __global__ void __launch_bounds__(256) scanprep_fwd_kernel(const T *__restrict__
       }
       // ---- B, C ----
       const T *bcr = bc + in_row * d.bs + (long long)h * 4 * d.N;
-      if (d.N <= G * VEC) {
+      if (one_sweep) {
         // one sweep: every lane keeps its four row slices in registers
         const int n0 = q * VEC;
         const bool mine = live && n0 < d.N;
@@ -369,40 +458,6 @@ __global__ void __launch_bounds__(256, KMAX == 1 ? 2 : 1) scanprep_bwd_kernel(co
     for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int i = 0; i < VEC; ++i) dsc[k][j][i] = 0.f;
-  // ---- coefficient-map VJP: one row per THREAD (rows_per_tile == blockDim.x) -------------
-  __shared__ float sbias[8][13];
-  {
-    float dbias[13];
-#pragma unroll
-    for (int i = 0; i < 13; ++i) dbias[i] = 0.f;
-    for (int t = t_lo + (int)threadIdx.x; t < t_hi; t += 256) {
-      const long long in_row = (long long)b * d.T + t;
-      const long long orow = ((long long)bh) * d.T + t;
-      float p[13], dp[13];
-      const T *pr = params + in_row * d.ps + (long long)h * 13;
-#pragma unroll
-      for (int i = 0; i < 13; ++i) p[i] = to_f(pr[i]) + bias[h * 13 + i];
-      CoefCtx ctx;
-      coef_forward(p, hp, &ctx);
-      float2 dm = *reinterpret_cast<const float2 *>(dM + orow * 2);
-      float4 dk = *reinterpret_cast<const float4 *>(dK + orow * 4);
-      coef_backward(ctx, hp, dm, make_float2(dk.x, dk.y), make_float2(dk.z, dk.w), dp);
-      T *dpr = d_params + in_row * ((long long)d.H * 13) + (long long)h * 13;
-#pragma unroll
-      for (int i = 0; i < 13; ++i) {
-        dpr[i] = from_f<T>(dp[i]);
-        dbias[i] += dp[i];
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 13; ++i) {
-      float v = dbias[i];
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-      if ((threadIdx.x & 31) == 0) sbias[threadIdx.x >> 5][i] = v;
-    }
-  }
-
   // Single-sweep path (one 16-byte vector per lane covers N): the row's raw bc and dB/dC stay
   // packed in registers (8 x 16 bytes) and are expanded twice, once for the row sums and once
   // for the output, instead of holding expanded fp32 copies; the head's scale sits in shared memory.
@@ -458,6 +513,11 @@ __global__ void __launch_bounds__(256, KMAX == 1 ? 2 : 1) scanprep_bwd_kernel(co
           }
           ss[j] = rsqrtf(group_sum_f<G>(a) / (float)d.N + 1e-5f);
         }
+        // keep the packed words opaque between the passes: expanding them again costs a few
+        // shifts, holding 64 expanded values across the group sums costs the occupancy
+#define SLX_OPAQUE4(u) asm volatile("" : "+r"((u).x), "+r"((u).y), "+r"((u).z), "+r"((u).w))
+#pragma unroll
+        for (int j = 0; j < 4; ++j) SLX_OPAQUE4(xr[j]);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float a = 0.f;
@@ -473,6 +533,12 @@ __global__ void __launch_bounds__(256, KMAX == 1 ? 2 : 1) scanprep_bwd_kernel(co
           }
           gx[j] = group_sum_f<G>(a) / (float)d.N;
         }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          SLX_OPAQUE4(xr[j]);
+          SLX_OPAQUE4(gr[j]);
+        }
+#undef SLX_OPAQUE4
         if (live && lane_on) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -603,13 +669,66 @@ __global__ void __launch_bounds__(256, KMAX == 1 ? 2 : 1) scanprep_bwd_kernel(co
       outp[e] = 0.f;
       continue;
     }
+    if (e >= 4 * d.N) continue;  // the 13 bias slots belong to scanprep_bwd_coef_kernel
     float acc = 0.f;
-    if (e < 4 * d.N) {
-      for (int g = 0; g < GPB; ++g) acc += red[(size_t)g * W + e];
-    } else {
-      for (int w = 0; w < 8; ++w) acc += sbias[w][e - 4 * d.N];
-    }
+    for (int g = 0; g < GPB; ++g) acc += red[(size_t)g * W + e];
     outp[e] = acc;
+  }
+}
+
+// Coefficient-map VJP of the backward: one row per thread (rows_per_tile == blockDim.x),
+// d_params rows and the per-tile partial sums of the 13 bias gradients
+// (part[(bh * n_tiles + tile)][4N .. 4N+13)).  Little traffic, long scalar chains: kept apart
+// from the streaming kernel above so that neither limits the other's occupancy.
+template <typename T>
+__global__ void __launch_bounds__(256) scanprep_bwd_coef_kernel(const T *__restrict__ params,
+                                                                const float *__restrict__ bias,
+                                                                const float *__restrict__ dM,
+                                                                const float *__restrict__ dK, T *__restrict__ d_params,
+                                                                float *__restrict__ part, PrepDims d, PrepHyper hp,
+                                                                int rows_per_tile) {
+  const int bh = blockIdx.y, b = bh / d.H, h = bh % d.H;
+  const int W = 4 * d.N + 13;
+  const int t_lo = blockIdx.x * rows_per_tile;
+  const int t_hi = min(d.T, t_lo + rows_per_tile);
+  __shared__ float sbias[8][13];
+  {
+    float dbias[13];
+#pragma unroll
+    for (int i = 0; i < 13; ++i) dbias[i] = 0.f;
+    for (int t = t_lo + (int)threadIdx.x; t < t_hi; t += 256) {
+      const long long in_row = (long long)b * d.T + t;
+      const long long orow = ((long long)bh) * d.T + t;
+      float p[13], dp[13];
+      const T *pr = params + in_row * d.ps + (long long)h * 13;
+#pragma unroll
+      for (int i = 0; i < 13; ++i) p[i] = to_f(pr[i]) + bias[h * 13 + i];
+      CoefCtx ctx;
+      coef_forward(p, hp, &ctx);
+      float2 dm = *reinterpret_cast<const float2 *>(dM + orow * 2);
+      float4 dk = *reinterpret_cast<const float4 *>(dK + orow * 4);
+      coef_backward(ctx, hp, dm, make_float2(dk.x, dk.y), make_float2(dk.z, dk.w), dp);
+      T *dpr = d_params + in_row * ((long long)d.H * 13) + (long long)h * 13;
+#pragma unroll
+      for (int i = 0; i < 13; ++i) {
+        dpr[i] = from_f<T>(dp[i]);
+        dbias[i] += dp[i];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 13; ++i) {
+      float v = dbias[i];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+      if ((threadIdx.x & 31) == 0) sbias[threadIdx.x >> 5][i] = v;
+    }
+  }
+
+  __syncthreads();
+  if (threadIdx.x < 13) {
+    float acc = 0.f;
+    for (int w = 0; w < 8; ++w) acc += sbias[w][threadIdx.x];
+    part[((size_t)bh * gridDim.x + blockIdx.x) * W + 4 * d.N + threadIdx.x] = acc;
   }
 }
 
@@ -728,6 +847,10 @@ static int launch_prep_bwd(const slx_prep_shape *s, const PrepDims &d, const voi
   else SLX_PREP_BWD(4)
 #undef SLX_PREP_BWD
   int rc = check_launch("scanprep_bwd");
+  if (rc) return rc;
+  scanprep_bwd_coef_kernel<T><<<dim3(pl.n_tiles, d.batch * d.H), 256, 0, st>>>(
+      (const T *)params, bias, dM, dK, (T *)d_params, part, d, hp, pl.rows_per_tile);
+  rc = check_launch("scanprep_bwd_coef");
   if (rc) return rc;
   int W = 4 * d.N + 13;
   scanprep_reduce_kernel<<<dim3((W + 127) / 128, d.H), 128, 0, st>>>(part, d_bias, d_scale, d.batch, d.H, pl.n_tiles,
