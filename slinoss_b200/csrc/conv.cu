@@ -18,11 +18,18 @@
 namespace slx {
 
 constexpr int kConvThreads = 128;
+constexpr int kConvAhead = 8;  // rows each thread requests ahead of its walk
+constexpr int kConvVec = 4;    // channels per thread: 8-byte vectors of half types, 16-byte of fp32
 
 template <typename T, int VEC>
 __device__ __forceinline__ void ldv(const T *p, float (&v)[VEC]) {
   if constexpr (VEC * sizeof(T) == 16) {
     uint4 raw = *reinterpret_cast<const uint4 *>(p);
+    const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] = to_f(e[i]);
+  } else if constexpr (VEC * sizeof(T) == 8) {
+    uint2 raw = *reinterpret_cast<const uint2 *>(p);
     const T *e = reinterpret_cast<const T *>(&raw);
 #pragma unroll
     for (int i = 0; i < VEC; ++i) v[i] = to_f(e[i]);
@@ -39,9 +46,32 @@ __device__ __forceinline__ void stv(T *p, const float (&v)[VEC]) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) e[i] = from_f<T>(v[i]);
     *reinterpret_cast<uint4 *>(p) = raw;
+  } else if constexpr (VEC * sizeof(T) == 8) {
+    uint2 raw;
+    T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) e[i] = from_f<T>(v[i]);
+    *reinterpret_cast<uint2 *>(p) = raw;
   } else {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) p[i] = from_f<T>(v[i]);
+  }
+}
+
+// One thread's slice of a row as it lies in memory (kept packed while it waits in registers)
+template <typename T, int VEC>
+struct alignas(VEC * sizeof(T) >= 16 ? 16 : 8) RowSlice {
+  T v[VEC];
+};
+template <typename T, int VEC>
+__device__ __forceinline__ void ld_raw(const T *p, RowSlice<T, VEC> &r) {
+  if constexpr (VEC * sizeof(T) == 16) {
+    *reinterpret_cast<uint4 *>(r.v) = *reinterpret_cast<const uint4 *>(p);
+  } else if constexpr (VEC * sizeof(T) == 8) {
+    *reinterpret_cast<uint2 *>(r.v) = *reinterpret_cast<const uint2 *>(p);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) r.v[i] = p[i];
   }
 }
 
@@ -95,23 +125,34 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_fwd_kernel(const T *__re
   load_cat<T, VEC>(x, state, d, b, t_lo - 3, c0, x0);
   load_cat<T, VEC>(x, state, d, b, t_lo - 2, c0, x1);
   load_cat<T, VEC>(x, state, d, b, t_lo - 1, c0, x2);
-  for (int t = t_lo; t < t_hi; ++t) {
-    ldv<T, VEC>(x + (long long)b * d.xbs + (long long)t * d.xs + c0, x3);
-    float o[VEC];
+  // kConvAhead rows are requested before any of them is used, so that each thread keeps
+  // several independent loads in flight along its otherwise sequential walk
+  for (int tb = t_lo; tb < t_hi; tb += kConvAhead) {
+    RowSlice<T, VEC> xr[kConvAhead];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      float acc = bv[e];
-      acc = fmaf(w4[0][e], x0[e], acc);
-      acc = fmaf(w4[1][e], x1[e], acc);
-      acc = fmaf(w4[2][e], x2[e], acc);
-      acc = fmaf(w4[3][e], x3[e], acc);
-      if (d.silu) acc = acc / (1.f + expf(-acc));
-      o[e] = acc;
-      x0[e] = x1[e];
-      x1[e] = x2[e];
-      x2[e] = x3[e];
+    for (int u = 0; u < kConvAhead; ++u)
+      if (tb + u < t_hi) ld_raw<T, VEC>(x + (long long)b * d.xbs + (long long)(tb + u) * d.xs + c0, xr[u]);
+#pragma unroll
+    for (int u = 0; u < kConvAhead; ++u) {
+      const int t = tb + u;
+      if (t >= t_hi) break;
+      float o[VEC];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        x3[e] = to_f(xr[u].v[e]);
+        float acc = bv[e];
+        acc = fmaf(w4[0][e], x0[e], acc);
+        acc = fmaf(w4[1][e], x1[e], acc);
+        acc = fmaf(w4[2][e], x2[e], acc);
+        acc = fmaf(w4[3][e], x3[e], acc);
+        if (d.silu) acc = acc / (1.f + expf(-acc));
+        o[e] = acc;
+        x0[e] = x1[e];
+        x1[e] = x2[e];
+        x2[e] = x3[e];
+      }
+      stv<T, VEC>(y + ((long long)b * d.T + t) * d.C + c0, o);
     }
-    stv<T, VEC>(y + ((long long)b * d.T + t) * d.C + c0, o);
   }
   if (next_state && t_hi == d.T) {
     for (int i = 0; i < d.W - 1; ++i) {
@@ -136,6 +177,32 @@ __device__ __forceinline__ void load_dyact(const T *dy, const ConvDims &d, int b
     return;
   }
   ldv<T, VEC>(dy + ((long long)b * d.T + t) * d.C + c0, g);
+  if (d.silu) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      float pre = bv[e];
+      pre = fmaf(w4[0][e], xa[e], pre);
+      pre = fmaf(w4[1][e], xb[e], pre);
+      pre = fmaf(w4[2][e], xc[e], pre);
+      pre = fmaf(w4[3][e], xd[e], pre);
+      float s = 1.f / (1.f + expf(-pre));
+      g[e] *= s * (1.f + pre * (1.f - s));
+    }
+  }
+}
+
+// same with dy already loaded (raw): g = dy * act'(pre), zero past the end of the sequence
+template <typename T, int VEC>
+__device__ __forceinline__ void apply_dyact(const ConvDims &d, int t, const float (&w4)[4][VEC], const float (&bv)[VEC],
+                                            const float (&xa)[VEC], const float (&xb)[VEC], const float (&xc)[VEC],
+                                            const float (&xd)[VEC], const RowSlice<T, VEC> &raw, float (&g)[VEC]) {
+  if (t >= d.T) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) g[e] = 0.f;
+    return;
+  }
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) g[e] = to_f(raw.v[e]);
   if (d.silu) {
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
@@ -176,9 +243,25 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_kernel(
     for (int k = 0; k < 4; ++k) dw[k][e] = 0.f;
   }
   const int t_end = min(d.T + 3, t_hi + 3);
-  for (int t = t_lo; t < t_end; ++t) {
-    if (t < d.T) ldv<T, VEC>(x + (long long)b * d.xbs + (long long)t * d.xs + c0, x3);
-    load_dyact<T, VEC>(dy, d, b, t, c0, w4, bv, x0, x1, x2, x3, g3);
+  for (int tb = t_lo; tb < t_end; tb += kConvAhead) {
+    RowSlice<T, VEC> xr[kConvAhead], gr[kConvAhead];
+#pragma unroll
+    for (int u = 0; u < kConvAhead; ++u) {
+      const int t = tb + u;
+      if (t < t_end && t < d.T) {
+        ld_raw<T, VEC>(x + (long long)b * d.xbs + (long long)t * d.xs + c0, xr[u]);
+        ld_raw<T, VEC>(dy + ((long long)b * d.T + t) * d.C + c0, gr[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kConvAhead; ++u) {
+    const int t = tb + u;
+    if (t >= t_end) break;
+    if (t < d.T) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) x3[e] = to_f(xr[u].v[e]);
+    }
+    apply_dyact<T, VEC>(d, t, w4, bv, x0, x1, x2, x3, gr[u], g3);
     if (t < t_hi) {
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
@@ -215,6 +298,7 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_kernel(
       g0[e] = g1[e];
       g1[e] = g2[e];
       g2[e] = g3[e];
+    }
     }
   }
   float *pp = part + (((long long)b * gridDim.y + blockIdx.y) * d.C + c0) * 5;
@@ -321,7 +405,7 @@ int slx_cconv1d_fwd(const slx_conv_shape *s, const void *x, const void *weight, 
   const int tile = conv_tile(d.T, false);
   const int n_tiles = (d.T + tile - 1) / tile;
   SLX_CONV_T(s->dtype, {
-    constexpr int VFULL = 16 / (int)sizeof(T_);
+    constexpr int VFULL = kConvVec;
     if (conv_vec_ok<T_>(s, {x, y})) {
       int nvec = d.C / VFULL;
       cconv1d_fwd_kernel<T_, VFULL><<<dim3((nvec + kConvThreads - 1) / kConvThreads, n_tiles, d.batch), kConvThreads, 0,
@@ -359,7 +443,7 @@ int slx_cconv1d_bwd(const slx_conv_shape *s, const void *x, const void *weight, 
   const int n_tiles = (d.T + tile - 1) / tile;
   float *part = static_cast<float *>(workspace);
   SLX_CONV_T(s->dtype, {
-    constexpr int VFULL = 16 / (int)sizeof(T_);
+    constexpr int VFULL = kConvVec;
     if (conv_vec_ok<T_>(s, {x, dy, dx})) {
       int nvec = d.C / VFULL;
       cconv1d_bwd_kernel<T_, VFULL><<<dim3((nvec + kConvThreads - 1) / kConvThreads, n_tiles, d.batch), kConvThreads, 0,
