@@ -399,7 +399,7 @@ def main() -> int:
         mch = torch.empty((b, h, NC, 2), **f32)
         _lib.check(lib.slx_v2x2ssd_fwd(byref(shape), U.data_ptr(), M.data_ptr(), Kt.data_ptr(), B.data_ptr(),
                                        C.data_ptr(), None, None, None, Y.data_ptr(), final.data_ptr(),
-                                       starts.data_ptr(), mch.data_ptr(), st), "fwd")
+                                       starts.data_ptr(), mch.data_ptr(), None, st), "fwd")
         d_inc = torch.empty_like(starts)
         zdot = torch.empty((b, h, NC, 2), **f32)
         part = torch.empty((BH * NC * 2 * 64,), **f32)

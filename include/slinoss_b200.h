@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define SLX_ABI_VERSION 1
+#define SLX_ABI_VERSION 2
 
 typedef enum { SLX_F32 = 0, SLX_BF16 = 1, SLX_F16 = 2 } slx_dtype;
 
@@ -82,13 +82,16 @@ int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M,
 
 /* Replaces reference.py:1195 v2x2ssd / cute/kernels/fwd/__init__.py:1691
  * v2x2ssd_fwd_cute: the three stages back to back on one stream.
- * chunk_starts doubles as the increment buffer. */
+ * increments: scratch of the size of chunk_starts for the chunk increments.
+ * NULL makes chunk_starts double as the increment buffer: no extra memory, but
+ * the state pass then overwrites each line it has just read, which runs at
+ * well under half the speed of the two-buffer pass on B200. */
 int slx_v2x2ssd_fwd(const slx_scan_shape *s, const void *U, const float *M,
                     const float *K, const void *B, const void *C,
                     const float *initial_states /*[opt]*/,
                     const float *B_prev /*[opt]*/, const float *U_prev /*[opt]*/,
                     void *Y, float *final_state, float *chunk_starts,
-                    float *m_chunk, void *stream);
+                    float *m_chunk, float *increments /*[opt]*/, void *stream);
 
 /* ---- backward ----------------------------------------------------------- */
 

@@ -47,7 +47,7 @@ SIGNATURES = {
     "slx_chunk_increment_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 9),
     "slx_state_passing_fwd": (c_int32, [c_int32] * 4 + [_P] * 6),
     "slx_chunk_scan_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 10),
-    "slx_v2x2ssd_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 13),
+    "slx_v2x2ssd_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 14),
     "slx_v2x2ssd_bwd_workspace_bytes": (c_size_t, [POINTER(ScanShape)]),
     "slx_chunk_scan_bwd_dz0": (c_int32, [POINTER(ScanShape)] + [_P] * 5),
     "slx_state_passing_bwd": (c_int32, [c_int32] * 4 + [_P] * 10),

@@ -300,12 +300,13 @@ int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M, c
 
 int slx_v2x2ssd_fwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
                     const void *C, const float *initial_states, const float *B_prev, const float *U_prev, void *Y,
-                    float *final_state, float *chunk_starts, float *m_chunk, void *stream) {
-  int rc = slx_chunk_increment_fwd(s, U, M, K, B, B_prev, U_prev, chunk_starts, m_chunk, stream);
+                    float *final_state, float *chunk_starts, float *m_chunk, float *increments, void *stream) {
+  float *inc = increments ? increments : chunk_starts;
+  int rc = slx_chunk_increment_fwd(s, U, M, K, B, B_prev, U_prev, inc, m_chunk, stream);
   if (rc) return rc;
   SLX_REQUIRE(final_state != nullptr, SLX_E_NULL, "v2x2ssd_fwd: final_state is NULL");
   const int NC = (s->T + s->chunk - 1) / s->chunk;
-  rc = slx_state_passing_fwd(s->batch_heads, NC, s->P, s->N, chunk_starts, m_chunk, initial_states, chunk_starts,
+  rc = slx_state_passing_fwd(s->batch_heads, NC, s->P, s->N, inc, m_chunk, initial_states, chunk_starts,
                              final_state, stream);
   if (rc) return rc;
   return slx_chunk_scan_fwd(s, U, M, K, B, C, chunk_starts, B_prev, U_prev, Y, stream);
