@@ -180,6 +180,33 @@ int slx_scanprep_bwd(const slx_prep_shape *s, const void *params, const void *bc
                      float *d_bias, float *d_scale, void *workspace,
                      size_t workspace_bytes, void *stream);
 
+/* ---- one-token decode step ------------------------------------------------- */
+
+typedef struct {
+  int32_t batch, heads, P, N; /* N even */
+  int32_t dtype;              /* slx_dtype of value, params, bc, gate, skip, b_prev, u_prev, out */
+  int32_t normalize_bc;
+  float dt_min, dt_max, r_min, r_max, theta_bound, k_max, eps;
+} slx_decode_shape;
+
+/* Replaces SLinOSSMixer._decode_step_reference (layers/mixer.py:714-748) and the contract
+ * of mixer_decode_step_cute (ops/v2x2ssd/cute/decode.py:117-149; that kernel is limited to
+ * P = 64, N = 64, batch in {1,2,4,8,16}): scan prep of one token, one recurrence step on
+ * the carried state, skip and gate.
+ *   value, gate (batch, heads, P); params (batch, heads, 13); bc (batch, heads, 4, N);
+ *   skip (heads, P); bias (heads, 13) fp32; scale (heads, 4, N) fp32 [needed iff normalize_bc];
+ *   state_in (batch, heads, P, 2N) fp32 [NULL = zero state]; b_prev (batch, heads, 2N) and
+ *   u_prev (batch, heads, P) in dtype [both NULL = no previous token];
+ *   out (batch, heads*P); state_out like state_in; b_last, u_last like b_prev, u_prev [opt].
+ * state_out may be state_in, b_last may be b_prev, u_last may be u_prev (in-place update of
+ * a ScanState, as the reference's final_state_out / b_last_out / u_last_out do). */
+int slx_decode_step(const slx_decode_shape *s, const void *value, const void *params,
+                    const void *bc, const void *gate, const void *skip, const float *bias,
+                    const float *scale /*[opt]*/, const float *state_in /*[opt]*/,
+                    const void *b_prev /*[opt]*/, const void *u_prev /*[opt]*/, void *out,
+                    float *state_out, void *b_last /*[opt]*/, void *u_last /*[opt]*/,
+                    void *stream);
+
 /* ---- depthwise causal conv1d --------------------------------------------- */
 
 typedef struct {

@@ -33,6 +33,13 @@ class PrepShape(Structure):
                 ("value_stride", c_int64), ("params_stride", c_int64), ("bc_stride", c_int64)]
 
 
+class DecodeShape(Structure):
+    _fields_ = [("batch", c_int32), ("heads", c_int32), ("P", c_int32), ("N", c_int32),
+                ("dtype", c_int32), ("normalize_bc", c_int32),
+                ("dt_min", c_float), ("dt_max", c_float), ("r_min", c_float), ("r_max", c_float),
+                ("theta_bound", c_float), ("k_max", c_float), ("eps", c_float)]
+
+
 class ConvShape(Structure):
     _fields_ = [("batch", c_int32), ("T", c_int32), ("channels", c_int32), ("width", c_int32),
                 ("dtype", c_int32), ("silu", c_int32), ("x_stride", c_int64),
@@ -61,6 +68,7 @@ SIGNATURES = {
     "slx_read_tc_status": (c_int32, [POINTER(c_int32)]),
     "slx_read_phase_clock": (c_int32, [POINTER(c_int64)]),
     "slx_umma_selftest": (c_int32, [c_int32] + [_P] * 5),
+    "slx_decode_step": (c_int32, [POINTER(DecodeShape)] + [_P] * 15),
     "slx_cconv1d_fwd": (c_int32, [POINTER(ConvShape)] + [_P] * 7),
     "slx_cconv1d_bwd_workspace_bytes": (c_size_t, [POINTER(ConvShape)]),
     "slx_cconv1d_bwd": (c_int32, [POINTER(ConvShape)] + [_P] * 11 + [c_size_t, _P]),

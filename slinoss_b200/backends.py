@@ -1,11 +1,11 @@
 """Drop-in backends for the reference's ``SLinOSSMixer`` backend switch.
 
 Each class implements the matching Protocol of slinoss/layers/backend.py
-(``ScanBackend`` :238, ``ScanPrepBackend`` :114, ``CConv1dBackend`` :174) and is
-handed to the mixer through its constructor:
+(``ScanBackend`` :238, ``ScanPrepBackend`` :114, ``CConv1dBackend`` :174,
+``MixerDecodeBackend`` :251) and is handed to the mixer through its constructor:
 
     SLinOSSMixer(..., backend=B200ScanBackend(), scanprep_backend=B200ScanPrepBackend(),
-                 cconv_backend=B200CConv1dBackend())
+                 cconv_backend=B200CConv1dBackend(), decode_backend=B200MixerDecodeBackend())
 
 The classes accept the reference's own ``ScanInputs`` / ``ScanPrepInputs`` /
 ``ScanState`` objects (only attributes are read) and return this package's
@@ -19,6 +19,7 @@ from typing import Optional, Tuple, Union
 import torch
 
 from .ops.cconv1d import cconv1d_b200
+from .ops.decode import mixer_decode_step_b200
 from .ops.scanprep import scanprep_b200
 from .ops.v2x2ssd import v2x2ssd_b200
 from .types import ScanInputs, ScanState
@@ -85,4 +86,44 @@ class B200CConv1dBackend:
         return cconv1d_b200(x, owner.dw_weight, owner.dw_bias, conv_state)
 
 
-__all__ = ["B200ScanBackend", "B200ScanPrepBackend", "B200CConv1dBackend"]
+class B200MixerDecodeBackend:
+    """``MixerDecodeBackend`` (backend.py:251-268): one token through scan prep, one recurrence
+    step, skip and gate.  ``owner`` is the mixer: ``owner.scanprep`` carries the prep parameters
+    and hyper-parameters (read as in mixer.py:758-782), ``inputs`` is a ``MixerDecodeInputs``
+    (``value, params, bc, gate, skip``), ``state`` a ``ScanState`` whose tensors are updated in
+    place when they have the layout the kernel writes (fp32 state, activation-dtype rows)."""
+
+    def __init__(self, *, state_cls=ScanState) -> None:
+        self.state_cls = state_cls
+
+    def supports(self, owner, *, batch_size: int, device: torch.device, dtype: torch.dtype) -> bool:
+        del batch_size
+        return (device.type == "cuda" and dtype in (torch.float32, torch.bfloat16, torch.float16)
+                and int(owner.d_state) % 2 == 0 and getattr(owner, "output_norm", None) is None)
+
+    def __call__(self, owner, inputs, state):
+        sp = owner.scanprep
+        v = inputs.value
+        b, H, P = map(int, v.shape)
+        N = int(inputs.bc.shape[-1])
+
+        def reuse(t, shape, dtype):
+            ok = (t is not None and tuple(t.shape) == shape and t.dtype == dtype and t.is_contiguous()
+                  and t.device == v.device)
+            return t if ok else None
+
+        gated, fin, b_last, u_last = mixer_decode_step_b200(
+            v.contiguous(), inputs.params.contiguous(), inputs.bc.contiguous(), inputs.gate.contiguous(),
+            inputs.skip, initial_states=state.state, B_prev=state.b_prev, U_prev=state.u_prev,
+            dt_min=sp.dt_min, dt_max=sp.dt_max, r_min=sp.r_min, r_max=sp.r_max, theta_bound=sp.theta_bound,
+            k_max=sp.k_max, eps=sp.eps, dt_bias=sp.dt_bias, gamma_bias=sp.gamma_bias, omega_bias=sp.omega_bias,
+            mix_r_bias=sp.mix_r_bias, mix_theta_bias=sp.mix_theta_bias, mix_k_prev_bias=sp.mix_k_prev_bias,
+            mix_k_curr_bias=sp.mix_k_curr_bias, b_scale=getattr(sp, "b_scale", None),
+            c_scale=getattr(sp, "c_scale", None), normalize_bc=bool(getattr(sp, "normalize_bc", True)),
+            final_state_out=reuse(state.state, (b, H, P, 2 * N), torch.float32),
+            b_last_out=reuse(state.b_prev, (b, H, 2 * N), v.dtype),
+            u_last_out=reuse(state.u_prev, (b, H, P), v.dtype))
+        return gated, self.state_cls(state=fin, b_prev=b_last, u_prev=u_last)
+
+
+__all__ = ["B200ScanBackend", "B200ScanPrepBackend", "B200CConv1dBackend", "B200MixerDecodeBackend"]

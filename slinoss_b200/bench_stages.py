@@ -219,6 +219,38 @@ def conv_stage(b, T, Cn, dtype):
     _emit("cconv1d_bwd", _time(bwd), b * T * Cn * 3 * es, 0, hbm, tfl, src)
 
 
+def decode_stage(b, H, P, N, dtype):
+    """One-token decode step at a serving batch, through the C ABI; state updated out of place
+    and in place (what a ScanState carried between tokens does)."""
+    dev = torch.device("cuda")
+    hbm, tfl, src = _peaks()
+    g = torch.Generator().manual_seed(3)
+    r = lambda *sh: torch.randn(*sh, generator=g)
+    value, gate = r(b, H, P).to(dtype).to(dev), r(b, H, P).to(dtype).to(dev)
+    params, bc = r(b, H, 13).to(dtype).to(dev), r(b, H, 4, N).to(dtype).to(dev)
+    skip = r(H, P).to(dtype).to(dev)
+    bias = torch.zeros(H, 13, device=dev)
+    scale = torch.ones(H, 4, N, device=dev)
+    st_in, st_out = r(b, H, P, 2 * N).to(dev), torch.empty(b, H, P, 2 * N, device=dev)
+    bp, up = r(b, H, 2 * N).to(dtype).to(dev), r(b, H, P).to(dtype).to(dev)
+    bl, ul = torch.empty_like(bp), torch.empty_like(up)
+    out = torch.empty(b, H * P, device=dev, dtype=dtype)
+    s = _lib.DecodeShape(b, H, P, N, _lib.dtype_code(dtype), 1, 1e-4, 1e-1, 0.9, 1.0, math.pi, 0.5, 1e-8)
+    lib, st, ck = _lib.lib(), _lib.stream_ptr(dev), _lib.check
+
+    def call(zin, zout):
+        ck(lib.slx_decode_step(byref(s), value.data_ptr(), params.data_ptr(), bc.data_ptr(), gate.data_ptr(),
+                               skip.data_ptr(), bias.data_ptr(), scale.data_ptr(), zin.data_ptr(), bp.data_ptr(),
+                               up.data_ptr(), out.data_ptr(), zout.data_ptr(), bl.data_ptr(), ul.data_ptr(), st),
+           "decode")
+
+    nbytes = b * H * 2 * P * 2 * N * 4
+    _emit("decode_step", _time(lambda: call(st_in, st_out)), nbytes, 0, hbm, tfl, src,
+          dict(note=f"b{b} H{H} P{P} N{N}, state read from one buffer and written to another"))
+    _emit("decode_step_in_place", _time(lambda: call(st_in, st_in)), nbytes, 0, hbm, tfl, src,
+          dict(note="state updated in place"))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=4)
@@ -231,6 +263,8 @@ def main():
     ap.add_argument("--no-scan", action="store_true")
     ap.add_argument("--prep", action="store_true")
     ap.add_argument("--conv", action="store_true")
+    ap.add_argument("--decode", action="store_true", help="one-token decode step at batch --decode-batch")
+    ap.add_argument("--decode-batch", type=int, default=256)
     ap.add_argument("--reps", type=int, default=10, help="timed launches per stage")
     ap.add_argument("--warm", type=int, default=3, help="untimed launches per stage")
     a = ap.parse_args()
@@ -243,6 +277,8 @@ def main():
         prep_stage(a.batch, a.T, a.heads, a.P, a.N, dt)
     if a.conv:
         conv_stage(a.batch, a.T, a.heads * a.P, dt)
+    if a.decode:
+        decode_stage(a.decode_batch, a.heads, a.P, a.N, dt)
 
 
 if __name__ == "__main__":

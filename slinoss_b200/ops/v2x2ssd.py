@@ -276,9 +276,17 @@ class _V2x2SSDFn(torch.autograd.Function):
 @torch.compiler.disable
 def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=None, U_prev=None,
                  compute_dtype: Optional[torch.dtype] = None,
-                 output_dtype: Optional[torch.dtype] = None, return_state: bool = False):
+                 output_dtype: Optional[torch.dtype] = None, return_state: bool = False,
+                 retile: bool = True):
     """Drop-in for ``v2x2ssd_cute`` (cute/api.py:52): returns ``Y`` or
-    ``(Y, final_state, B_last, U_last)``; differentiable in all eight inputs."""
+    ``(Y, final_state, B_last, U_last)``; differentiable in all eight inputs.
+
+    ``chunk_size`` only says how the sequence is tiled; none of the returned values depends
+    on it beyond rounding.  With ``retile`` (default) half-precision inputs of head dim 64 and
+    state width up to 256 are tiled in the 128-token chunks of the tcgen05 kernels whatever
+    ``chunk_size`` asks for (the reference's default is 64); ``retile=False`` keeps the
+    requested tiling (fp32-exact kernels for anything but 128).
+    """
     b, h, T, N, P = _validate_inputs(U, M, K, B, C, initial_states, B_prev, U_prev)
     if U.device.type != "cuda":
         raise ValueError("slinoss_b200 v2x2ssd requires CUDA tensors.")
@@ -302,6 +310,8 @@ def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=
     Ua, Ba, Ca = (t if t.dtype == act else t.to(act) for t in (U, B, C))
     Mf = M if M.dtype == torch.float32 else M.to(torch.float32)
     Kf = K if K.dtype == torch.float32 else K.to(torch.float32)
+    if retile and act in (torch.bfloat16, torch.float16) and P == 64 and D % 64 == 0 and D <= 256:
+        chunk_size = 128
     needs_grad = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (U, M, K, B, C, initial_states, B_prev, U_prev))
     if needs_grad:

@@ -19,6 +19,9 @@ scan_cfg0_f32.npz    b2 H4 T256 P32 N16 chunk 64, fp32, scan inputs produced by
 scan_bf16.npz        b1 H2 T192 P64 N32 chunk 64, bf16 inputs / fp32 compute.
 prep_f32.npz         SLinOSSScanPrep forward + gradients incl. all parameters.
 conv_f64.npz         depthwise causal conv (width 4 and 2), with/without state.
+decode_f32.npz       one-token mixer decode step (SLinOSSMixer._decode_step_reference):
+                     scan prep of one token, one recurrence step from a carried
+                     state, skip and gate; inputs, parameters, outputs, next state.
 """
 
 from __future__ import annotations
@@ -223,8 +226,53 @@ def _conv_case():
     print("conv_f64.npz written")
 
 
+def _decode_case():
+    """b3 H2 P8 N16, fp32: two consecutive decode steps of a randomised mixer."""
+    from slinoss.layers import SLinOSSMixer  # type: ignore
+    from slinoss.layers.backend import (MixerDecodeInputs, ReferenceCConv1dBackend,  # type: ignore
+                                        ReferenceScanBackend)
+    from slinoss.layers.state import ScanState  # type: ignore
+
+    b, H, P, N = 3, 2, 8, 16
+    torch.manual_seed(21)
+    mixer = SLinOSSMixer(d_model=H * P, d_state=N, expand=1, d_head=P, d_conv=4, chunk_size=16,
+                         backend=ReferenceScanBackend(), scanprep_backend=ReferenceScanPrepBackend(),
+                         cconv_backend=ReferenceCConv1dBackend())
+    with torch.no_grad():
+        for prm in mixer.scanprep.parameters():
+            prm.add_(0.3 * torch.randn_like(prm))
+        mixer.skip.add_(0.5 * torch.randn_like(mixer.skip))
+    gen = torch.Generator().manual_seed(22)
+    state = ScanState(state=torch.randn(b, H, P, 2 * N, generator=gen),
+                      b_prev=torch.randn(b, H, 2 * N, generator=gen),
+                      u_prev=torch.randn(b, H, P, generator=gen))
+    out = dict(state0=_np(state.state), b_prev0=_np(state.b_prev), u_prev0=_np(state.u_prev),
+               skip=_np(mixer.skip.reshape(H, P)))
+    for n in PREP_PARAM_NAMES:
+        out[n] = _np(getattr(mixer.scanprep, n))
+    for n in ("dt_min", "dt_max", "r_min", "r_max", "theta_bound", "k_max", "eps"):
+        out["hp_" + n] = np.float64(getattr(mixer.scanprep, n))
+    with torch.no_grad():
+        for step in range(2):
+            inp = MixerDecodeInputs(value=torch.randn(b, H, P, generator=gen),
+                                    params=1.5 * torch.randn(b, H, 13, generator=gen),
+                                    bc=torch.randn(b, H, 4, N, generator=gen),
+                                    gate=torch.randn(b, H, P, generator=gen),
+                                    skip=mixer.skip.reshape(H, P))
+            y, state = mixer._decode_step_reference(inp, state)
+            out.update({f"value{step}": _np(inp.value), f"params{step}": _np(inp.params),
+                        f"bc{step}": _np(inp.bc), f"gate{step}": _np(inp.gate), f"y{step}": _np(y),
+                        f"state{step + 1}": _np(state.state), f"b_prev{step + 1}": _np(state.b_prev),
+                        f"u_prev{step + 1}": _np(state.u_prev)})
+    np.savez_compressed(OUT / "decode_f32.npz", **out)
+    print("decode_f32.npz written")
+
+
 def main() -> int:
     torch.set_num_threads(8)
+    if "--only-decode" in sys.argv:
+        _decode_case()
+        return 0
     _scan_case("scan_small_f64.npz", b=1, h=2, T=37, N=3, P=5, L=16, dtype=torch.float32,
                compute_dtype=torch.float64, streaming=True, with_init=True, seed=11,
                stages=True)
@@ -234,6 +282,7 @@ def main() -> int:
     _cfg0()
     _prep_case()
     _conv_case()
+    _decode_case()
     return 0
 
 

@@ -82,9 +82,9 @@ def test_exact_zero_transition_rejected():
         oscan.v2x2ssd_fwd(g["U"], M, g["K"], g["B"], g["C"], chunk_size=16)
 
 
-def _prep_cfg(g):
+def _prep_cfg(g, n_heads=None, d_state=None, d_head=None):
     H, _, N = g["b_scale"].shape
-    P = g["value"].shape[-1] // H
+    P = d_head if d_head is not None else g["value"].shape[-1] // H
     return oprep.PrepConfig(n_heads=H, d_state=N, d_head=P,
                             **{k[3:]: float(v) for k, v in g.items() if k.startswith("hp_")})
 
@@ -206,3 +206,22 @@ def test_prep_coefficient_vjp_matches_float64_autograd():
     M2, K2 = oprep.coefficients_fwd(params.detach().numpy(), bias.numpy(), cfg)
     assert rel_err(M2, M.detach().numpy()) < 1e-13 and rel_err(K2, K.detach().numpy()) < 1e-13
     assert rel_err(dp, gp.numpy()) < 1e-12
+
+
+def test_decode_step_two_tokens():
+    """One-token decode step against SLinOSSMixer._decode_step_reference, two steps chained."""
+    from oracle import decode as odec
+
+    g = golden("decode_f32.npz")
+    cfg = _prep_cfg(g, n_heads=g["skip"].shape[0], d_state=g["bc0"].shape[-1], d_head=g["skip"].shape[1])
+    bias, scale = _prep_tables(g)
+    st, bp, up = g["state0"], g["b_prev0"], g["u_prev0"]
+    for step in range(2):
+        y, st, bp, up = odec.decode_step(g[f"value{step}"], g[f"params{step}"], g[f"bc{step}"],
+                                         g[f"gate{step}"], g["skip"], bias, scale, cfg,
+                                         state=st, b_prev=bp, u_prev=up)
+        # the taps carry the reference's fp32 cancellation noise (see test_prep_forward)
+        assert rel_err(y, g[f"y{step}"]) < 1e-4
+        assert rel_err(st, g[f"state{step + 1}"]) < 1e-4
+        assert rel_err(bp, g[f"b_prev{step + 1}"]) < 2e-6
+        assert rel_err(up, g[f"u_prev{step + 1}"]) < 1e-7

@@ -115,3 +115,17 @@ def test_strong_decay_takes_per_element_path():
     tol = {k: 2e-2 for k in errs}
     tol["dM"] = 4e-2
     assert all(errs[k] < tol[k] for k in errs), errs
+
+
+def test_requested_chunk_is_retiled_to_the_tensor_chunk():
+    """chunk_size is a tiling hint: half inputs at P=64 run in 128-token chunks whatever is asked."""
+    import slinoss_b200 as sb
+
+    inp = make_scan_inputs(1, 2, 320, 64, 64, torch.bfloat16, seed=5, dist="cfg2")
+    args = [inp[k] for k in ("U", "M", "K", "B", "C")]
+    y64 = sb.v2x2ssd_b200(*args, chunk_size=64)
+    y128 = sb.v2x2ssd_b200(*args, chunk_size=128)
+    assert torch.equal(y64, y128)
+    y_exact = sb.v2x2ssd_b200(*args, chunk_size=64, retile=False)
+    assert not torch.equal(y_exact, y128)
+    assert rel_err(to_np(y_exact), to_np(y128)) < 1e-2
