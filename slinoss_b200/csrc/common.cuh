@@ -122,6 +122,78 @@ __device__ __forceinline__ void chunk_prefix_warp(int run_warp, const float *__r
   }
 }
 
+// The same prefix for chunks of 128 tokens with the four multipliers of every lane already in
+// registers (tokens 4*lane .. 4*lane+3; 1 past the end of the sequence): lets a kernel request
+// them before its bulk copies and run the prefix when they have arrived.  Called by one warp.
+__device__ __forceinline__ void chunk_prefix_load4(const float *__restrict__ Mchunk, int valid, float2 (&m)[4]) {
+  const int lane = threadIdx.x & 31;
+  const int t0 = 4 * lane;
+  if (t0 + 3 < valid && (reinterpret_cast<uintptr_t>(Mchunk) & 15) == 0) {
+    const float4 a = *reinterpret_cast<const float4 *>(Mchunk + 2 * (size_t)t0);
+    const float4 b = *reinterpret_cast<const float4 *>(Mchunk + 2 * (size_t)t0 + 4);
+    m[0] = make_float2(a.x, a.y);
+    m[1] = make_float2(a.z, a.w);
+    m[2] = make_float2(b.x, b.y);
+    m[3] = make_float2(b.z, b.w);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      m[i] = (t0 + i < valid) ? *reinterpret_cast<const float2 *>(Mchunk + 2 * (size_t)(t0 + i)) : make_float2(1.f, 0.f);
+  }
+}
+__device__ __forceinline__ void chunk_prefix_fast128(const float2 (&min)[4], float *lp, float2 *ph, float2 *mraw,
+                                                     int *bad_flag) {
+  const int lane = threadIdx.x & 31;
+  const int t0 = 4 * lane;
+  float lsum = 0.f;
+  float2 psum = make_float2(1.f, 0.f);
+  float lloc[4];
+  float2 ploc[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 m = min[i];
+    float m2 = fmaf(m.x, m.x, m.y * m.y);
+    if (m2 == 0.f) {
+      if (bad_flag) atomicExch(bad_flag, 1);
+      m2 = 1.f;
+      m = make_float2(1.f, 0.f);
+    }
+    const float inv = rsqrtf(m2);
+    mraw[t0 + i] = m;
+    lsum += 0.5f * __logf(m2);
+    psum = cmul(psum, make_float2(m.x * inv, m.y * inv));
+    lloc[i] = lsum;
+    ploc[i] = psum;
+  }
+  float lincl = lsum;
+  float2 pincl = psum;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const float lo = __shfl_up_sync(0xffffffffu, lincl, off);
+    const float px = __shfl_up_sync(0xffffffffu, pincl.x, off);
+    const float py = __shfl_up_sync(0xffffffffu, pincl.y, off);
+    if (lane >= off) {
+      lincl += lo;
+      pincl = cmul(pincl, make_float2(px, py));
+    }
+  }
+  float lex = __shfl_up_sync(0xffffffffu, lincl, 1);
+  float pex_x = __shfl_up_sync(0xffffffffu, pincl.x, 1);
+  float pex_y = __shfl_up_sync(0xffffffffu, pincl.y, 1);
+  if (lane == 0) {
+    lex = 0.f;
+    pex_x = 1.f;
+    pex_y = 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 p = cmul(ploc[i], make_float2(pex_x, pex_y));
+    const float inv = rsqrtf(p.x * p.x + p.y * p.y);
+    ph[t0 + i] = make_float2(p.x * inv, p.y * inv);
+    lp[t0 + i] = lloc[i] + lex;
+  }
+}
+
 __device__ __forceinline__ void chunk_prefix_warp0(const float *__restrict__ Mchunk, int L, int valid, float *lp,
                                                    float2 *ph, float2 *mraw, int *bad_flag) {
   chunk_prefix_warp<false>(0, Mchunk, L, valid, lp, ph, mraw, bad_flag);

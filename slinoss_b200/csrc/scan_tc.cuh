@@ -158,6 +158,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
       zr[k2][1] = src[1];
     }
   };
+  float2 mreg[4];  // the prefix warp's multipliers, requested ahead of the bulk copies
+  if ((tid >> 5) == 2) chunk_prefix_load4(a.M + tok0 * 2, valid, mreg);
   // U tile straight into its operand tile (no transform needed), same commit group as slab 0
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -179,7 +181,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
     umma::mbar_init(mbar_s, 1);
     umma::fence_mbar_init();
   }
-  chunk_prefix_warp<true>(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, a.bad);
+  if (warp == 2) chunk_prefix_fast128(mreg, lp, ph, mraw, a.bad);
   if (tid >= 128) {
     int t = tid - 128;
     float2 vp = make_float2(0.f, 0.f), vc = vp;
@@ -415,6 +417,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_outer_tc_kernel(OuterArgs
   // place, the X slabs land raw in their operand tiles and are weighted in place by the
   // thread that requested them once the chunk's coefficients exist.
   const int j = tid & 7, r0 = tid >> 3;
+  float2 mreg[4];  // the prefix warp's multipliers, requested first
+  if (warp == 2) chunk_prefix_load4(a.M + tok0 * 2, valid, mreg);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int r = r0 + 32 * i;
@@ -444,7 +448,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_outer_tc_kernel(OuterArgs
       else if (a.Bprev) bv = *reinterpret_cast<const float2 *>(a.Bprev + (size_t)bh * d.D + 2 * n);
     }
   }
-  chunk_prefix_warp<true>(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, nullptr);
+  if (warp == 2) chunk_prefix_fast128(mreg, lp, ph, mraw, nullptr);
   if (MODE == 0 && warp == 2) {
     // chunk transition = product of the raw multipliers: four per lane, then a butterfly
     float2 acc = cmul(cmul(mraw[4 * lane], mraw[4 * lane + 1]), cmul(mraw[4 * lane + 2], mraw[4 * lane + 3]));

@@ -83,6 +83,8 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
   const int j = tid & 7, r0 = tid >> 3;  // r0 in [0,64)
   const float *z0 = a.starts + ((size_t)bh * d.NC + c) * P * d.D;
   const float *lam = a.d_inc + ((size_t)bh * d.NC + c) * P * d.D;
+  float2 mreg[4];  // the prefix warp's multipliers, requested ahead of the bulk copies
+  if (warp == 2) chunk_prefix_load4(a.M + tok0 * 2, valid, mreg);
   // U and dY land in their operand tiles by asynchronous copy (rows past the chunk end are
   // zero-filled); the first raw (C, B) slab follows as a second group
 #pragma unroll
@@ -137,7 +139,7 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
     umma::mbar_init(mbar_s, 1);
     umma::fence_mbar_init();
   }
-  chunk_prefix_warp<true>(2, a.M + tok0 * 2, L, valid, lp, ph, mraw, nullptr);
+  if (warp == 2) chunk_prefix_fast128(mreg, lp, ph, mraw, nullptr);
   if (tid >= 128 && tid < 256) {
     int t = tid - 128;
     float2 vp = make_float2(0.f, 0.f), vc = vp;
