@@ -343,18 +343,30 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_kernel(
   }
 }
 
+// One thread per (channel, slot) of the partials, slots = (dw4[0..3], dbias); the parts are summed
+// in their fixed order, eight loads in flight.
 __global__ void cconv1d_reduce_kernel(const float *__restrict__ part, float *__restrict__ dweight,
                                       float *__restrict__ dbias, int n_parts, int C, int W) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  float acc[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int p = 0; p < n_parts; ++p) {
-    const float *pp = part + ((long long)p * C + c) * 5;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= C * 5) return;
+  const size_t stride = (size_t)C * 5;
+  float acc = 0.f;
+  int p = 0;
+  for (; p + 8 <= n_parts; p += 8) {
+    float v[8];
 #pragma unroll
-    for (int k = 0; k < 5; ++k) acc[k] += pp[k];
+    for (int i = 0; i < 8; ++i) v[i] = part[(size_t)(p + i) * stride + e];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += v[i];
   }
-  for (int j = 0; j < W; ++j) dweight[(long long)c * W + j] = acc[j + (4 - W)];
-  if (dbias) dbias[c] = acc[4];
+  for (; p < n_parts; ++p) acc += part[(size_t)p * stride + e];
+  const int c = e / 5, k = e % 5;
+  if (k == 4) {
+    if (dbias) dbias[c] = acc;
+  } else {
+    const int j = k - (4 - W);
+    if (j >= 0) dweight[(long long)c * W + j] = acc;
+  }
 }
 
 static int check_conv(const slx_conv_shape *s, ConvDims *d) {
@@ -458,7 +470,7 @@ int slx_cconv1d_bwd(const slx_conv_shape *s, const void *x, const void *weight, 
   });
   rc = check_launch("cconv1d_bwd");
   if (rc) return rc;
-  cconv1d_reduce_kernel<<<(d.C + 127) / 128, 128, 0, st>>>(part, dweight, dbias, d.batch * n_tiles, d.C, d.W);
+  cconv1d_reduce_kernel<<<(d.C * 5 + 255) / 256, 256, 0, st>>>(part, dweight, dbias, d.batch * n_tiles, d.C, d.W);
   return check_launch("cconv1d_reduce");
 }
 

@@ -343,7 +343,17 @@ __global__ void __launch_bounds__(256) scanprep_fwd_kernel(const T *__restrict__
   }
 }
 
-// Backward.  grid = (tiles over T, batch*H): every CTA works on one head, so the
+template <typename T>
+__device__ __forceinline__ void scanprep_bwd_coef_tile(const T *__restrict__ params, const float *__restrict__ bias,
+                                                       const float *__restrict__ dM, const float *__restrict__ dK,
+                                                       T *__restrict__ d_params, float *__restrict__ part,
+                                                       const PrepDims &d, const PrepHyper &hp, int rows_per_tile,
+                                                       int tile, int n_tiles);
+
+// Backward.  grid = (2 * tiles over T, batch*H).  CTAs with blockIdx.x < n_tiles stream the wide
+// rows; the others run the coefficient-map VJP of the same tiles (scanprep_bwd_coef_tile): its long
+// scalar chains fill issue slots that the streaming CTAs leave idle while they wait on memory.
+// Every CTA works on one head, so the
 // per-head parameter gradients reduce inside the CTA first (registers ->
 // shared memory in a fixed order) and then across CTAs in a second kernel.
 // Partial layout: part[(bh * n_tiles + tile)][4*N + 13].
@@ -355,7 +365,12 @@ __global__ void __launch_bounds__(256, KMAX == 1 ? 2 : 1) scanprep_bwd_kernel(co
                                                            const T *__restrict__ dB, const T *__restrict__ dC,
                                                            T *__restrict__ d_value, T *__restrict__ d_params,
                                                            T *__restrict__ d_bc, float *__restrict__ part, PrepDims d,
-                                                           PrepHyper hp, int rows_per_tile) {
+                                                           PrepHyper hp, int rows_per_tile, int n_tiles) {
+  if ((int)blockIdx.x >= n_tiles) {
+    scanprep_bwd_coef_tile<T>(params, bias, dM, dK, d_params, part, d, hp, rows_per_tile, (int)blockIdx.x - n_tiles,
+                              n_tiles);
+    return;
+  }
   constexpr int GPB = 256 / G;  // KMAX sweeps of VEC*G state lanes cover N
   extern __shared__ float red[];  // GPB * (4N + 13)
   const int q = threadIdx.x % G, grp = threadIdx.x / G;
@@ -577,13 +592,13 @@ __global__ void __launch_bounds__(256, KMAX == 1 ? 2 : 1) scanprep_bwd_kernel(co
     }
   }
   __syncthreads();
-  float *outp = part + ((size_t)bh * gridDim.x + blockIdx.x) * W;
+  float *outp = part + ((size_t)bh * n_tiles + blockIdx.x) * W;
   for (int e = threadIdx.x; e < W; e += 256) {
     if (!d.normalize && e < 4 * d.N) {
       outp[e] = 0.f;
       continue;
     }
-    if (e >= 4 * d.N) continue;  // the 13 bias slots belong to scanprep_bwd_coef_kernel
+    if (e >= 4 * d.N) continue;  // the 13 bias slots belong to the coefficient CTAs
     float acc = 0.f;
     for (int g = 0; g < GPB; ++g) acc += red[(size_t)g * W + e];
     outp[e] = acc;
@@ -592,18 +607,17 @@ __global__ void __launch_bounds__(256, KMAX == 1 ? 2 : 1) scanprep_bwd_kernel(co
 
 // Coefficient-map VJP of the backward: one row per thread (rows_per_tile == blockDim.x),
 // d_params rows and the per-tile partial sums of the 13 bias gradients
-// (part[(bh * n_tiles + tile)][4N .. 4N+13)).  Little traffic, long scalar chains: kept apart
-// from the streaming kernel above so that neither limits the other's occupancy.
+// (part[(bh * n_tiles + tile)][4N .. 4N+13)).  Little traffic, long scalar chains: run by CTAs of
+// their own inside the backward launch.
 template <typename T>
-__global__ void __launch_bounds__(256) scanprep_bwd_coef_kernel(const T *__restrict__ params,
-                                                                const float *__restrict__ bias,
-                                                                const float *__restrict__ dM,
-                                                                const float *__restrict__ dK, T *__restrict__ d_params,
-                                                                float *__restrict__ part, PrepDims d, PrepHyper hp,
-                                                                int rows_per_tile) {
+__device__ __forceinline__ void scanprep_bwd_coef_tile(const T *__restrict__ params, const float *__restrict__ bias,
+                                                       const float *__restrict__ dM, const float *__restrict__ dK,
+                                                       T *__restrict__ d_params, float *__restrict__ part,
+                                                       const PrepDims &d, const PrepHyper &hp, int rows_per_tile,
+                                                       int tile, int n_tiles) {
   const int bh = blockIdx.y, b = bh / d.H, h = bh % d.H;
   const int W = 4 * d.N + 13;
-  const int t_lo = blockIdx.x * rows_per_tile;
+  const int t_lo = tile * rows_per_tile;
   const int t_hi = min(d.T, t_lo + rows_per_tile);
   __shared__ float sbias[8][13];
   {
@@ -642,7 +656,7 @@ __global__ void __launch_bounds__(256) scanprep_bwd_coef_kernel(const T *__restr
   if (threadIdx.x < 13) {
     float acc = 0.f;
     for (int w = 0; w < 8; ++w) acc += sbias[w][threadIdx.x];
-    part[((size_t)bh * gridDim.x + blockIdx.x) * W + 4 * d.N + threadIdx.x] = acc;
+    part[((size_t)bh * n_tiles + tile) * W + 4 * d.N + threadIdx.x] = acc;
   }
 }
 
@@ -654,8 +668,18 @@ __global__ void scanprep_reduce_kernel(const float *__restrict__ part, float *__
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= W) return;
   float acc = 0.f;
-  for (int b = 0; b < batch; ++b)
-    for (int tile = 0; tile < n_tiles; ++tile) acc += part[((size_t)(b * H + h) * n_tiles + tile) * W + e];
+  for (int b = 0; b < batch; ++b) {
+    const float *pb = part + ((size_t)(b * H + h) * n_tiles) * W + e;
+    int tile = 0;
+    for (; tile + 8 <= n_tiles; tile += 8) {  // eight loads in flight, summed in the fixed order
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = pb[(size_t)(tile + i) * W];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc += v[i];
+    }
+    for (; tile < n_tiles; ++tile) acc += pb[(size_t)tile * W];
+  }
   if (e < 4 * N) {
     if (d_scale) d_scale[(size_t)h * 4 * N + e] = acc;
   } else {
@@ -752,19 +776,15 @@ static int launch_prep_bwd(const slx_prep_shape *s, const PrepDims &d, const voi
     auto kern = scanprep_bwd_kernel<T, VEC, G, KM>;                                                           \
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);    \
     if (e != cudaSuccess) return fail((int)e, "scanprep_bwd smem attribute: %s", cudaGetErrorString(e));      \
-    kern<<<dim3(pl.n_tiles, d.batch * d.H), 256, pl.smem, st>>>(                                              \
+    kern<<<dim3(2 * pl.n_tiles, d.batch * d.H), 256, pl.smem, st>>>(                                          \
         (const T *)params, (const T *)bc, bias, scale, (const T *)dU, dM, dK, (const T *)dB, (const T *)dC,   \
-        (T *)d_value, (T *)d_params, (T *)d_bc, part, d, hp, pl.rows_per_tile);                               \
+        (T *)d_value, (T *)d_params, (T *)d_bc, part, d, hp, pl.rows_per_tile, pl.n_tiles);                   \
   }
   if (pl.kmax <= 1) SLX_PREP_BWD(1)
   else if (pl.kmax == 2) SLX_PREP_BWD(2)
   else SLX_PREP_BWD(4)
 #undef SLX_PREP_BWD
   int rc = check_launch("scanprep_bwd");
-  if (rc) return rc;
-  scanprep_bwd_coef_kernel<T><<<dim3(pl.n_tiles, d.batch * d.H), 256, 0, st>>>(
-      (const T *)params, bias, dM, dK, (T *)d_params, part, d, hp, pl.rows_per_tile);
-  rc = check_launch("scanprep_bwd_coef");
   if (rc) return rc;
   int W = 4 * d.N + 13;
   scanprep_reduce_kernel<<<dim3((W + 127) / 128, d.H), 128, 0, st>>>(part, d_bias, d_scale, d.batch, d.H, pl.n_tiles,
