@@ -94,6 +94,74 @@ __device__ __forceinline__ void store_vec(T *p, const float (&v)[VEC]) {
   }
 }
 
+// ---- the 13-value parameter row of one (batch, head, token) ---------------------------------
+// Half types: the row is 26 bytes at an arbitrary 2-byte offset.  `wide` loads the two or three
+// aligned 16-byte vectors that cover it and picks the 13 values out by the (per-thread) offset;
+// the caller passes wide = true only when every such vector lies inside the tensor (base and row
+// stride multiples of 16 bytes, row width a multiple of 16 bytes).  Stores pair the values into
+// 4-byte words wherever the address allows: 7 stores instead of 13.
+template <typename T, int O>
+__device__ __forceinline__ void pick13(const uint32_t (&w)[12], float (&p)[13]) {
+#pragma unroll
+  for (int i = 0; i < 13; ++i) {
+    const uint32_t word = w[(O + i) >> 1];
+    const unsigned short hbits = ((O + i) & 1) ? (unsigned short)(word >> 16) : (unsigned short)(word & 0xffffu);
+    T v;
+    *reinterpret_cast<unsigned short *>(&v) = hbits;
+    p[i] = to_f(v);
+  }
+}
+template <typename T>
+__device__ __forceinline__ void load_row13(const T *pr, bool wide, float (&p)[13]) {
+  if constexpr (sizeof(T) == 2) {
+    if (wide) {
+      const uintptr_t a = reinterpret_cast<uintptr_t>(pr);
+      const uint4 *base = reinterpret_cast<const uint4 *>(a & ~uintptr_t(15));
+      const int o = (int)((a & 15) >> 1);
+      const uint4 v0 = base[0], v1 = base[1];
+      uint4 v2 = make_uint4(0, 0, 0, 0);
+      if (o > 3) v2 = base[2];  // elements o .. o+12 reach past the second vector
+      const uint32_t w[12] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w, v2.x, v2.y, v2.z, v2.w};
+      switch (o) {
+        case 0: pick13<T, 0>(w, p); break;
+        case 1: pick13<T, 1>(w, p); break;
+        case 2: pick13<T, 2>(w, p); break;
+        case 3: pick13<T, 3>(w, p); break;
+        case 4: pick13<T, 4>(w, p); break;
+        case 5: pick13<T, 5>(w, p); break;
+        case 6: pick13<T, 6>(w, p); break;
+        default: pick13<T, 7>(w, p); break;
+      }
+      return;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 13; ++i) p[i] = to_f(pr[i]);
+}
+template <typename T>
+__device__ __forceinline__ void store_row13(T *pr, const float (&v)[13]) {
+  if constexpr (sizeof(T) == 2) {
+    auto pair = [&](int i) {
+      T lo = from_f<T>(v[i]), hi = from_f<T>(v[i + 1]);
+      const uint32_t word = (uint32_t)(*reinterpret_cast<unsigned short *>(&lo)) |
+                            ((uint32_t)(*reinterpret_cast<unsigned short *>(&hi)) << 16);
+      *reinterpret_cast<uint32_t *>(pr + i) = word;
+    };
+    if ((reinterpret_cast<uintptr_t>(pr) & 3) == 0) {
+#pragma unroll
+      for (int i = 0; i < 12; i += 2) pair(i);
+      pr[12] = from_f<T>(v[12]);
+    } else {
+      pr[0] = from_f<T>(v[0]);
+#pragma unroll
+      for (int i = 1; i < 13; i += 2) pair(i);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 13; ++i) pr[i] = from_f<T>(v[i]);
+  }
+}
+
 template <int G>
 __device__ __forceinline__ float group_sum_f(float v) {
 #pragma unroll
@@ -105,6 +173,7 @@ struct PrepDims {
   int batch, T, H, P, N;
   int normalize;
   long long vs, ps, bs;  // row strides (elements)
+  int wide_params;        // the covering 16-byte vectors of every params row lie inside the tensor
 };
 
 // Rows are ordered (b, h, t) so that a CTA's consecutive rows write contiguous
@@ -135,8 +204,9 @@ __global__ void __launch_bounds__(256) scanprep_fwd_kernel(const T *__restrict__
         const int b = (int)(row / ((long long)d.T * d.H));
         float p[13];
         const T *pr = params + ((long long)b * d.T + t) * d.ps + (long long)h * 13;
+        load_row13<T>(pr, d.wide_params != 0, p);
 #pragma unroll
-        for (int i = 0; i < 13; ++i) p[i] = to_f(pr[i]) + bias[h * 13 + i];
+        for (int i = 0; i < 13; ++i) p[i] += bias[h * 13 + i];
         CoefOut o = coef_forward(p, hp, nullptr);
         *reinterpret_cast<float2 *>(M + row * 2) = o.rho;
         *reinterpret_cast<float4 *>(K + row * 4) = make_float4(o.kp.x, o.kp.y, o.kc.x, o.kc.y);
@@ -629,19 +699,17 @@ __device__ __forceinline__ void scanprep_bwd_coef_tile(const T *__restrict__ par
       const long long orow = ((long long)bh) * d.T + t;
       float p[13], dp[13];
       const T *pr = params + in_row * d.ps + (long long)h * 13;
+      load_row13<T>(pr, d.wide_params != 0, p);
 #pragma unroll
-      for (int i = 0; i < 13; ++i) p[i] = to_f(pr[i]) + bias[h * 13 + i];
+      for (int i = 0; i < 13; ++i) p[i] += bias[h * 13 + i];
       CoefCtx ctx;
       coef_forward(p, hp, &ctx);
       float2 dm = *reinterpret_cast<const float2 *>(dM + orow * 2);
       float4 dk = *reinterpret_cast<const float4 *>(dK + orow * 4);
       coef_backward(ctx, hp, dm, make_float2(dk.x, dk.y), make_float2(dk.z, dk.w), dp);
-      T *dpr = d_params + in_row * ((long long)d.H * 13) + (long long)h * 13;
+      store_row13<T>(d_params + in_row * ((long long)d.H * 13) + (long long)h * 13, dp);
 #pragma unroll
-      for (int i = 0; i < 13; ++i) {
-        dpr[i] = from_f<T>(dp[i]);
-        dbias[i] += dp[i];
-      }
+      for (int i = 0; i < 13; ++i) dbias[i] += dp[i];
     }
 #pragma unroll
     for (int i = 0; i < 13; ++i) {
@@ -710,10 +778,18 @@ static int check_prep(const slx_prep_shape *s, PrepDims *d) {
   d->batch = s->batch; d->T = s->T; d->H = s->heads; d->P = s->P; d->N = s->N;
   d->normalize = s->normalize_bc;
   d->vs = s->value_stride; d->ps = s->params_stride; d->bs = s->bc_stride;
+  d->wide_params = 0;
   return SLX_OK;
 }
 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// every aligned 16-byte vector that covers a 13-value params row of a half type lies inside its
+// own (16-byte aligned, 16-byte multiple) row of the tensor
+static int params_rows_wide(const slx_prep_shape *s, const void *params) {
+  return s->dtype != SLX_F32 && aligned16(params) && (s->params_stride * 2) % 16 == 0 &&
+         ((long long)s->heads * 13 * 2) % 16 == 0;
+}
 
 // vector width (elements) usable for this problem: 16-byte vectors when every
 // row start and row width is 16-byte aligned, else scalar
@@ -813,6 +889,7 @@ int slx_scanprep_fwd(const slx_prep_shape *s, const void *value, const void *par
   if (rc) return rc;
   SLX_REQUIRE(value && params && bc && bias && U && M && K && B && C, SLX_E_NULL, "scanprep_fwd: NULL tensor");
   SLX_REQUIRE(!s->normalize_bc || scale, SLX_E_NULL, "scanprep_fwd: scale is NULL with normalize_bc set");
+  d.wide_params = params_rows_wide(s, params);
   cudaStream_t st = as_stream(stream);
   SLX_PREP_T(s->dtype, {
     int vec = pick_vec<T_>(s, {value, bc, U, B, C});
@@ -840,6 +917,7 @@ int slx_scanprep_bwd(const slx_prep_shape *s, const void *params, const void *bc
   SLX_REQUIRE(params && bc && bias && dU && dM && dK && dB && dC && d_value && d_params && d_bc && d_bias, SLX_E_NULL,
               "scanprep_bwd: NULL tensor");
   SLX_REQUIRE(!s->normalize_bc || (scale && d_scale), SLX_E_NULL, "scanprep_bwd: scale/d_scale NULL");
+  d.wide_params = params_rows_wide(s, params);
   size_t need = slx_scanprep_bwd_workspace_bytes(s);
   SLX_REQUIRE(workspace && workspace_bytes >= need, SLX_E_WORKSPACE, "scanprep_bwd: workspace of %zu bytes needed",
               need);

@@ -70,6 +70,8 @@ def test_prep_golden_fp32():
     (torch.float32, 16, 32, 4, 2, 256),     # BASELINE config 0 shape
     (torch.float32, 5, 6, 2, 1, 33),        # scalar path (nothing 16-byte aligned)
     (torch.bfloat16, 64, 64, 12, 1, 70),    # config-1 head shape; inputs are slices of one projection
+    (torch.bfloat16, 32, 64, 8, 2, 300),    # heads % 8 == 0: parameter rows read as aligned 16-byte vectors
+    (torch.float16, 16, 16, 16, 1, 515),    # same, several tiles, every row offset inside a vector occurs
 ])
 def test_prep_seeded_vs_oracle(dtype, N, P, H, b, T):
     gen = torch.Generator().manual_seed(N + T)
