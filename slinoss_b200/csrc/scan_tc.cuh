@@ -271,6 +271,12 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
       float tmp[8] = {zr[k][0].x, zr[k][0].y, zr[k][0].z, zr[k][0].w, zr[k][1].x, zr[k][1].y, zr[k][1].z, zr[k][1].w};
       *reinterpret_cast<uint4 *>(tZ + umma::swz_off(p, jj)) = pack8<T>(tmp);
     }
+    // Every thread has consumed its own raw slots (it alone wrote and read them) and its Z0
+    // registers: request the next slab now, a whole staging phase ahead of its use.
+    if (sl + 1 < NB) {
+      prefetch_cb(sl + 1);
+      prefetch_z(sl + 1);
+    }
     umma::fence_smem_to_async();
     SLX_FSTAMP(10 + 4 * sl);
     __syncthreads();
@@ -286,10 +292,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
         umma::mma_ss(tmem + 128, da, umma::desc_kmajor(sZ, kk), id_o, (sl | kk) != 0);
       }
       umma::commit(mbar_s);
-    }
-    if (sl + 1 < NB) {  // staging tiles were consumed before the barrier: refill them
-      prefetch_cb(sl + 1);
-      prefetch_z(sl + 1);
     }
   }
   SLX_FSTAMP(2);
