@@ -68,11 +68,14 @@ int slx_chunk_increment_fwd(const slx_scan_shape *s, const void *U,
                             float *m_chunk, void *stream);
 
 /* Replaces reference.py:1015 state_passing (CuTe: kernels/fwd/__init__.py:897).
- * chunk_starts may alias inc (the pass is then in place). */
+ * chunk_starts may alias inc (the pass is then in place).  chunk_starts == NULL
+ * asks for final_state only (nothing else is written): the affine offset of a
+ * segment when segments are chained across devices. */
 int slx_state_passing_fwd(int32_t batch_heads, int32_t n_chunks, int32_t P,
                           int32_t N, const float *inc, const float *m_chunk,
                           const float *initial_states /*[opt]*/,
-                          float *chunk_starts, float *final_state, void *stream);
+                          float *chunk_starts /*[opt]*/, float *final_state,
+                          void *stream);
 
 /* Replaces reference.py:1059 chunk_scan (CuTe: kernels/fwd/__init__.py:1125). */
 int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M,
@@ -108,13 +111,16 @@ int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *
  * and m.py:83 fused): on return d_inc[c] = dL/d(end state of chunk c) (it may
  * alias dZ0), d_initial = dL/d(initial state), and zdot (BH,NC,2) holds
  * sum_{p,n} conj(end_state_c) * d_inc[c], the chunk-level term of dM.
- * final_state is the forward's fp32 final state. */
+ * final_state is the forward's fp32 final state.
+ * zdot and zdot_partials NULL: no dot products (chunk_starts and final_state are
+ * then not read).  d_inc NULL as well: only d_initial is written. */
 int slx_state_passing_bwd(int32_t batch_heads, int32_t n_chunks, int32_t P,
                           int32_t N, const float *dZ0, const float *m_chunk,
-                          const float *chunk_starts, const float *final_state,
-                          const float *d_final /*[opt]*/, float *d_inc,
-                          float *d_initial /*[opt]*/, float *zdot,
-                          float *zdot_partials /* workspace */, void *stream);
+                          const float *chunk_starts /*[opt]*/,
+                          const float *final_state /*[opt]*/,
+                          const float *d_final /*[opt]*/, float *d_inc /*[opt]*/,
+                          float *d_initial /*[opt]*/, float *zdot /*[opt]*/,
+                          float *zdot_partials /* workspace, [opt] */, void *stream);
 
 /* Per-chunk backward given d_inc (from slx_state_passing_bwd) and zdot: writes
  * dU, dB, dC (activation dtype; the last row of every chunk still lacks the
@@ -144,6 +150,27 @@ int slx_v2x2ssd_bwd(const slx_scan_shape *s, const void *U, const float *M,
                     float *dK, void *dB, void *dC, float *d_initial /*[opt]*/,
                     float *dB_prev /*[opt]*/, float *dU_prev /*[opt]*/,
                     void *workspace, size_t workspace_bytes, void *stream);
+
+/* The backward in two calls, for a sequence whose segments live on different
+ * devices (no counterpart in the reference, which has no distributed code).
+ * _begin computes dZ0 into the workspace and the segment's d_initial for a zero
+ * d_final (fp32, like d_initial); the caller chains the true d_final across
+ * segments (d_initial = d_initial_zero_final + conj(prod m_chunk) d_final) and
+ * then calls _finish with the same workspace, which runs the rest of
+ * slx_v2x2ssd_bwd without recomputing dZ0.  Same workspace size. */
+int slx_v2x2ssd_bwd_begin(const slx_scan_shape *s, const float *M, const void *C,
+                          const float *m_chunk, const void *dY,
+                          float *d_initial_zero_final, void *workspace,
+                          size_t workspace_bytes, void *stream);
+int slx_v2x2ssd_bwd_finish(const slx_scan_shape *s, const void *U, const float *M,
+                           const float *K, const void *B, const void *C,
+                           const float *B_prev /*[opt]*/, const float *U_prev /*[opt]*/,
+                           const float *chunk_starts, const float *m_chunk,
+                           const float *final_state, const void *dY,
+                           const float *d_final /*[opt]*/, void *dU, float *dM,
+                           float *dK, void *dB, void *dC, float *d_initial /*[opt]*/,
+                           float *dB_prev /*[opt]*/, float *dU_prev /*[opt]*/,
+                           void *workspace, size_t workspace_bytes, void *stream);
 
 /* ---- scan preparation ---------------------------------------------------- */
 

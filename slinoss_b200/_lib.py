@@ -60,6 +60,8 @@ SIGNATURES = {
     "slx_state_passing_bwd": (c_int32, [c_int32] * 4 + [_P] * 10),
     "slx_chunk_scan_bwd": (c_int32, [POINTER(ScanShape)] + [_P] * 19),
     "slx_v2x2ssd_bwd": (c_int32, [POINTER(ScanShape)] + [_P] * 21 + [c_size_t, _P]),
+    "slx_v2x2ssd_bwd_begin": (c_int32, [POINTER(ScanShape)] + [_P] * 6 + [c_size_t, _P]),
+    "slx_v2x2ssd_bwd_finish": (c_int32, [POINTER(ScanShape)] + [_P] * 21 + [c_size_t, _P]),
     "slx_scanprep_fwd": (c_int32, [POINTER(PrepShape)] + [_P] * 11),
     "slx_scanprep_bwd_workspace_bytes": (c_size_t, [POINTER(PrepShape)]),
     "slx_scanprep_bwd": (c_int32, [POINTER(PrepShape)] + [_P] * 15 + [c_size_t, _P]),

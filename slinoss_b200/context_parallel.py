@@ -49,7 +49,7 @@ class B200Engine:
         from .ops.v2x2ssd import chunk_increment_b200, state_passing_b200
 
         inc, mch = chunk_increment_b200(U, M, K, B, B_prev=Bp, U_prev=Up, chunk_size=L)
-        _, f0 = state_passing_b200(inc, mch, initial_states=None)
+        _, f0 = state_passing_b200(inc, mch, initial_states=None, want_starts=False)
         return inc, mch, f0
 
     def forward_finish(self, U, M, K, B, C, inc, mch, z_in, Bp, Up, L):
@@ -60,34 +60,17 @@ class B200Engine:
         return Y, starts, final
 
     def backward_zero(self, U, M, K, B, C, mch, starts, final, dY, L):
-        """d_initial of the segment for d_final = 0 (needs only dZ0 and the reverse state pass)."""
-        from ctypes import byref
+        """d_initial of the segment for d_final = 0, plus the workspace that already holds dZ0
+        (handed back to ``backward_full`` so that it is not computed twice)."""
+        from .ops.v2x2ssd import _bwd_begin
 
-        from . import _lib
-        from .ops.v2x2ssd import _shape
+        return _bwd_begin(M, C, mch, dY, L, int(U.shape[-1]))
 
-        b, h, T, P = map(int, U.shape)
-        D = int(B.shape[-1])
-        NC = int(mch.shape[2])
-        s = _shape(b, h, T, P, D // 2, L, U.dtype)
-        dev = U.device
-        dz0 = torch.empty((b, h, NC, P, D), device=dev, dtype=torch.float32)
-        g0 = torch.empty((b, h, P, D), device=dev, dtype=torch.float32)
-        zdot = torch.empty((b, h, NC, 2), device=dev, dtype=torch.float32)
-        part = torch.empty((b * h * NC * 2 * 64,), device=dev, dtype=torch.float32)
-        lib, st = _lib.lib(), _lib.stream_ptr(dev)
-        _lib.check(lib.slx_chunk_scan_bwd_dz0(byref(s), M.data_ptr(), C.data_ptr(), dY.data_ptr(), dz0.data_ptr(), st),
-                   "dZ0")
-        _lib.check(lib.slx_state_passing_bwd(b * h, NC, P, D // 2, dz0.data_ptr(), mch.data_ptr(), starts.data_ptr(),
-                                             final.data_ptr(), None, dz0.data_ptr(), g0.data_ptr(), zdot.data_ptr(),
-                                             part.data_ptr(), st), "reverse state pass")
-        return g0
-
-    def backward_full(self, U, M, K, B, C, Bp, Up, mch, starts, final, dY, d_final, L):
+    def backward_full(self, U, M, K, B, C, Bp, Up, mch, starts, final, dY, d_final, L, token=None):
         from .ops.v2x2ssd import _bwd_impl
 
         return _bwd_impl(U, M, K, B, C, Bp, Up, starts, mch, final, dY, d_final, L, want_initial=True,
-                         want_prev=Bp is not None)
+                         want_prev=Bp is not None, workspace=token)
 
 
 def _send(t, dst, group):
@@ -150,7 +133,8 @@ class _ContextParallelScanFn(torch.autograd.Function):
         dev = U.device
         dY = torch.zeros_like(U) if dY is None else dY.to(U.dtype).contiguous()
         # reverse chain of d_final: d_initial(r) = g0(r) + conj(m_seg(r)) d_final(r)
-        g0 = engine.backward_zero(U, M, K, B, C, mch, starts, final, dY, L)
+        res = engine.backward_zero(U, M, K, B, C, mch, starts, final, dY, L)
+        g0, token = res if isinstance(res, tuple) else (res, None)  # an engine may hand over reusable work
         if r == R - 1:
             d_final = None if d_final_in is None else d_final_in.float().contiguous()
         else:
@@ -159,8 +143,9 @@ class _ContextParallelScanFn(torch.autograd.Function):
             m_conj = m_seg * torch.tensor([1.0, -1.0], device=dev, dtype=m_seg.dtype)
             d_init_chain = g0 if d_final is None else g0 + _cmul(m_conj, d_final)
             _send(d_init_chain, r - 1, group)
+        extra = {} if token is None else {"token": token}
         dU, dM, dK, dB, dC, d_init, dBp, dUp = engine.backward_full(U, M, K, B, C, Bp, Up, mch, starts, final, dY,
-                                                                    d_final, L)
+                                                                    d_final, L, **extra)
         # halo gradients go back to the previous rank's last token
         if r > 0:
             _send(torch.cat([dBp, dUp], dim=-1).contiguous(), r - 1, group)

@@ -196,7 +196,7 @@ static int launch_state_bwd(int BH, int NC, int P, int N, const float *dZ0, cons
                                                                d_initial, partials, NC, elems / 2);
   }
   int rc = check_launch("state_passing_bwd");
-  if (rc) return rc;
+  if (rc || partials == nullptr) return rc;
   int rows = BH * NC;
   zdot_reduce_kernel<<<(rows + 255) / 256, 256, 0, st>>>(partials, zdot, rows, nblk);
   return check_launch("zdot_reduce");
@@ -276,7 +276,7 @@ int slx_state_passing_fwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const fl
                           const float *initial_states, float *chunk_starts, float *final_state, void *stream) {
   SLX_REQUIRE(BH > 0 && NC > 0 && P > 0 && N > 0, SLX_E_SHAPE, "state_passing_fwd: sizes must be positive");
   SLX_REQUIRE(BH <= 65535, SLX_E_UNSUPPORTED, "batch_heads=%d exceeds 65535", BH);
-  SLX_REQUIRE(inc && m_chunk && chunk_starts && final_state, SLX_E_NULL, "state_passing_fwd: NULL tensor");
+  SLX_REQUIRE(inc && m_chunk && final_state, SLX_E_NULL, "state_passing_fwd: NULL tensor");
   return launch_state_fwd(BH, NC, P, N, inc, m_chunk, initial_states, chunk_starts, final_state, as_stream(stream));
 }
 
@@ -340,8 +340,12 @@ int slx_state_passing_bwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const fl
                           float *d_initial, float *zdot, float *zdot_partials, void *stream) {
   SLX_REQUIRE(BH > 0 && NC > 0 && P > 0 && N > 0, SLX_E_SHAPE, "state_passing_bwd: sizes must be positive");
   SLX_REQUIRE(BH <= 65535, SLX_E_UNSUPPORTED, "batch_heads=%d exceeds 65535", BH);
-  SLX_REQUIRE(dZ0 && m_chunk && chunk_starts && final_state && d_inc && zdot && zdot_partials, SLX_E_NULL,
-              "state_passing_bwd: NULL tensor");
+  SLX_REQUIRE(dZ0 && m_chunk, SLX_E_NULL, "state_passing_bwd: NULL tensor");
+  SLX_REQUIRE((zdot == nullptr) == (zdot_partials == nullptr), SLX_E_NULL,
+              "state_passing_bwd: zdot and zdot_partials go together");
+  SLX_REQUIRE(zdot == nullptr || (chunk_starts && final_state), SLX_E_NULL,
+              "state_passing_bwd: zdot needs chunk_starts and final_state");
+  SLX_REQUIRE(d_inc || d_initial, SLX_E_NULL, "state_passing_bwd: neither d_inc nor d_initial asked for");
   return launch_state_bwd(BH, NC, P, N, dZ0, m_chunk, chunk_starts, final_state, d_final, d_inc, d_initial, zdot,
                           zdot_partials, as_stream(stream));
 }
@@ -369,11 +373,11 @@ int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M, c
   return rc;
 }
 
-int slx_v2x2ssd_bwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
-                    const void *C, const float *B_prev, const float *U_prev, const float *chunk_starts,
-                    const float *m_chunk, const float *final_state, const void *dY, const float *d_final, void *dU,
-                    float *dM, float *dK, void *dB, void *dC, float *d_initial, float *dB_prev, float *dU_prev,
-                    void *workspace, size_t workspace_bytes, void *stream) {
+static int v2x2ssd_bwd_impl(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
+                            const void *C, const float *B_prev, const float *U_prev, const float *chunk_starts,
+                            const float *m_chunk, const float *final_state, const void *dY, const float *d_final,
+                            void *dU, float *dM, float *dK, void *dB, void *dC, float *d_initial, float *dB_prev,
+                            float *dU_prev, void *workspace, size_t workspace_bytes, void *stream, bool dz0_ready) {
   ScanDims d;
   int rc = check_shape(s, &d);
   if (rc) return rc;
@@ -393,8 +397,10 @@ int slx_v2x2ssd_bwd(const slx_scan_shape *s, const void *U, const float *M, cons
   float *carryU = reinterpret_cast<float *>(base + w.carryU);
   cudaStream_t st = as_stream(stream);
 
-  rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, d_inc, stream);
-  if (rc) return rc;
+  if (!dz0_ready) {
+    rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, d_inc, stream);
+    if (rc) return rc;
+  }
   rc = launch_state_bwd(d.BH, d.NC, d.P, d.N, d_inc, m_chunk, chunk_starts, final_state, d_final, d_inc, d_initial,
                         zdot, partials, st);
   if (rc) return rc;
@@ -407,6 +413,43 @@ int slx_v2x2ssd_bwd(const slx_scan_shape *s, const void *U, const float *M, cons
     rc = check_launch("carry_fixup");
   });
   return rc;
+}
+
+int slx_v2x2ssd_bwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
+                    const void *C, const float *B_prev, const float *U_prev, const float *chunk_starts,
+                    const float *m_chunk, const float *final_state, const void *dY, const float *d_final, void *dU,
+                    float *dM, float *dK, void *dB, void *dC, float *d_initial, float *dB_prev, float *dU_prev,
+                    void *workspace, size_t workspace_bytes, void *stream) {
+  return v2x2ssd_bwd_impl(s, U, M, K, B, C, B_prev, U_prev, chunk_starts, m_chunk, final_state, dY, d_final, dU, dM,
+                          dK, dB, dC, d_initial, dB_prev, dU_prev, workspace, workspace_bytes, stream, false);
+}
+
+int slx_v2x2ssd_bwd_begin(const slx_scan_shape *s, const float *M, const void *C, const float *m_chunk,
+                          const void *dY, float *d_initial_zero_final, void *workspace, size_t workspace_bytes,
+                          void *stream) {
+  ScanDims d;
+  int rc = check_shape(s, &d);
+  if (rc) return rc;
+  SLX_REQUIRE(M && C && m_chunk && dY && d_initial_zero_final, SLX_E_NULL, "v2x2ssd_bwd_begin: NULL tensor");
+  const BwdWs w = bwd_ws(d);
+  SLX_REQUIRE(workspace != nullptr && workspace_bytes >= w.total, SLX_E_WORKSPACE,
+              "v2x2ssd_bwd_begin: workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
+  SLX_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, SLX_E_WORKSPACE,
+              "v2x2ssd_bwd_begin: workspace must be 256-byte aligned");
+  float *dz0 = reinterpret_cast<float *>(static_cast<char *>(workspace) + w.d_inc);
+  rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, dz0, stream);
+  if (rc) return rc;
+  return launch_state_bwd(d.BH, d.NC, d.P, d.N, dz0, m_chunk, nullptr, nullptr, nullptr, nullptr,
+                          d_initial_zero_final, nullptr, nullptr, as_stream(stream));
+}
+
+int slx_v2x2ssd_bwd_finish(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
+                           const void *C, const float *B_prev, const float *U_prev, const float *chunk_starts,
+                           const float *m_chunk, const float *final_state, const void *dY, const float *d_final,
+                           void *dU, float *dM, float *dK, void *dB, void *dC, float *d_initial, float *dB_prev,
+                           float *dU_prev, void *workspace, size_t workspace_bytes, void *stream) {
+  return v2x2ssd_bwd_impl(s, U, M, K, B, C, B_prev, U_prev, chunk_starts, m_chunk, final_state, dY, d_final, dU, dM,
+                          dK, dB, dC, d_initial, dB_prev, dU_prev, workspace, workspace_bytes, stream, true);
 }
 
 }  // extern "C"

@@ -37,7 +37,8 @@ __device__ __forceinline__ float2 cdot(float4 a, float4 b) {
 // One thread owns VEC/2 complex state lanes for the whole sequence of chunks;
 // consecutive threads own consecutive lanes, so every access is a full-width
 // coalesced 8/16-byte vector.  `starts` may alias `inc`: each chunk's increment
-// is read before its slot is overwritten.
+// is read before its slot is overwritten.  `starts` may be NULL: only the final state is wanted
+// (the affine offset of a segment in the context-parallel chain), and the pass writes nothing else.
 template <int VEC>
 __global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc, const float *__restrict__ m_chunk,
                                                                 const float *__restrict__ init, float *starts,
@@ -49,7 +50,7 @@ __global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc
   if (i >= n_vec) return;
   const size_t per = (size_t)n_vec;
   const V *incv = reinterpret_cast<const V *>(inc) + (size_t)bh * NC * per + i;
-  V *stv = reinterpret_cast<V *>(starts) + (size_t)bh * NC * per + i;
+  V *stv = starts ? reinterpret_cast<V *>(starts) + (size_t)bh * NC * per + i : nullptr;
   const float2 *mc = reinterpret_cast<const float2 *>(m_chunk) + (size_t)bh * NC;
   V z = init ? reinterpret_cast<const V *>(init)[(size_t)bh * per + i] : vzero(V());
   int c = 0;
@@ -57,19 +58,19 @@ __global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc
     V v0 = incv[(size_t)(c + 0) * per], v1 = incv[(size_t)(c + 1) * per];
     V v2 = incv[(size_t)(c + 2) * per], v3 = incv[(size_t)(c + 3) * per];
     float2 m0 = mc[c], m1 = mc[c + 1], m2 = mc[c + 2], m3 = mc[c + 3];
-    stv[(size_t)(c + 0) * per] = z;
+    if (stv) stv[(size_t)(c + 0) * per] = z;
     z = axpy_c(m0, z, v0);
-    stv[(size_t)(c + 1) * per] = z;
+    if (stv) stv[(size_t)(c + 1) * per] = z;
     z = axpy_c(m1, z, v1);
-    stv[(size_t)(c + 2) * per] = z;
+    if (stv) stv[(size_t)(c + 2) * per] = z;
     z = axpy_c(m2, z, v2);
-    stv[(size_t)(c + 3) * per] = z;
+    if (stv) stv[(size_t)(c + 3) * per] = z;
     z = axpy_c(m3, z, v3);
   }
   for (; c < NC; ++c) {
     V v = incv[(size_t)c * per];
     float2 m = mc[c];
-    stv[(size_t)c * per] = z;
+    if (stv) stv[(size_t)c * per] = z;
     z = axpy_c(m, z, v);
   }
   reinterpret_cast<V *>(final_state)[(size_t)bh * per + i] = z;
@@ -78,7 +79,9 @@ __global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc
 // Reverse pass: g = d_final; for c = NC-1..0:
 //   zdot_partial[c] = sum conj(end_state_c) * g      (end_state_c = starts[c+1] or final)
 //   d_inc[c] = g;  g = dZ0[c] + conj(m_chunk[c]) * g
-// d_initial = g.  d_inc may alias dZ0.
+// d_initial = g.  d_inc may alias dZ0.  With zdot_partials == NULL the dot products (and the reads
+// of starts / final_state) are skipped, with d_inc == NULL nothing but d_initial is written: that
+// is the reduce-only pass that gives a segment's d_initial for a zero d_final.
 template <int VEC>
 __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0, const float *__restrict__ m_chunk,
                                                                 const float *__restrict__ starts,
@@ -94,7 +97,32 @@ __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0
   const int iv = live ? i : 0;
   const size_t per = (size_t)n_vec;
   const V *dzv = reinterpret_cast<const V *>(dZ0) + (size_t)bh * NC * per + iv;
-  V *div = reinterpret_cast<V *>(d_inc) + (size_t)bh * NC * per + iv;
+  V *div = d_inc ? reinterpret_cast<V *>(d_inc) + (size_t)bh * NC * per + iv : nullptr;
+  if (zdot_partials == nullptr) {  // reduce-only / no dot products: a plain reverse recurrence
+    const float2 *mc0 = reinterpret_cast<const float2 *>(m_chunk) + (size_t)bh * NC;
+    V g0 = (d_final && live) ? reinterpret_cast<const V *>(d_final)[(size_t)bh * per + iv] : vzero(V());
+    int c = NC - 1;
+    for (; c >= 3; c -= 4) {  // four loads in flight
+      V d0 = dzv[(size_t)(c - 0) * per], d1 = dzv[(size_t)(c - 1) * per];
+      V d2 = dzv[(size_t)(c - 2) * per], d3 = dzv[(size_t)(c - 3) * per];
+      const float2 m0 = mc0[c], m1 = mc0[c - 1], m2 = mc0[c - 2], m3 = mc0[c - 3];
+      if (div && live) div[(size_t)(c - 0) * per] = g0;
+      g0 = axpy_c(cconj(m0), g0, d0);
+      if (div && live) div[(size_t)(c - 1) * per] = g0;
+      g0 = axpy_c(cconj(m1), g0, d1);
+      if (div && live) div[(size_t)(c - 2) * per] = g0;
+      g0 = axpy_c(cconj(m2), g0, d2);
+      if (div && live) div[(size_t)(c - 3) * per] = g0;
+      g0 = axpy_c(cconj(m3), g0, d3);
+    }
+    for (; c >= 0; --c) {
+      V dz = dzv[(size_t)c * per];
+      if (div && live) div[(size_t)c * per] = g0;
+      g0 = axpy_c(cconj(mc0[c]), g0, dz);
+    }
+    if (d_initial && live) reinterpret_cast<V *>(d_initial)[(size_t)bh * per + iv] = g0;
+    return;
+  }
   const V *stv = reinterpret_cast<const V *>(starts) + (size_t)bh * NC * per + iv;
   const float2 *mc = reinterpret_cast<const float2 *>(m_chunk) + (size_t)bh * NC;
   V g = (d_final && live) ? reinterpret_cast<const V *>(d_final)[(size_t)bh * per + iv] : vzero(V());
@@ -118,7 +146,7 @@ __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0
       reinterpret_cast<float2 *>(zdot_partials)[((size_t)bh * NC + c) * gridDim.x + blockIdx.x] = acc;
     }
     __syncthreads();
-    if (live) div[(size_t)c * per] = g;
+    if (live && div) div[(size_t)c * per] = g;
     g = axpy_c(cconj(m), g, dz);
     endst = st;
   }

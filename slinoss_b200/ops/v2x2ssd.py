@@ -144,15 +144,16 @@ def chunk_increment_b200(U, M, K, B, *, B_prev=None, U_prev=None, chunk_size: in
     return inc, mch
 
 
-def state_passing_b200(inc, m_chunk, *, initial_states=None):
-    """Stage 2 -> ``(chunk_starts, final_state)`` fp32."""
+def state_passing_b200(inc, m_chunk, *, initial_states=None, want_starts: bool = True):
+    """Stage 2 -> ``(chunk_starts, final_state)`` fp32.  ``want_starts=False`` returns
+    ``(None, final_state)`` and writes nothing but the final state (half the traffic)."""
     _require_cuda(inc, m_chunk, initial_states)
     b, h, NC, P, D = map(int, inc.shape)
     init = _f32(initial_states)
-    starts = torch.empty_like(inc)
+    starts = torch.empty_like(inc) if want_starts else None
     final = torch.empty((b, h, P, D), device=inc.device, dtype=torch.float32)
     _lib.check(_lib.lib().slx_state_passing_fwd(
-        b * h, NC, P, D // 2, inc.data_ptr(), m_chunk.data_ptr(), _lib.ptr(init), starts.data_ptr(),
+        b * h, NC, P, D // 2, inc.data_ptr(), m_chunk.data_ptr(), _lib.ptr(init), _lib.ptr(starts),
         final.data_ptr(), _lib.stream_ptr(inc.device)), "state_passing")
     return starts, final
 
@@ -191,8 +192,25 @@ def _fwd_impl(U, M, K, B, C, init32, bp32, up32, L):
     return Y, final, starts, mch
 
 
+def _bwd_begin(M, C, mch, dY, L, P):
+    """First half of the two-call backward: dZ0 into a fresh workspace and the segment's
+    d_initial for a zero d_final.  Returns ``(g0, workspace)``; pass the workspace to
+    ``_bwd_impl(..., workspace=...)``."""
+    b, h, T, D = map(int, C.shape)
+    s = _shape(b, h, T, P, D // 2, L, C.dtype)
+    dev = C.device
+    L_ = _lib.lib()
+    nbytes = int(L_.slx_v2x2ssd_bwd_workspace_bytes(byref(s)))
+    ws = torch.empty((nbytes,), device=dev, dtype=torch.uint8)
+    g0 = torch.empty((b, h, P, D), device=dev, dtype=torch.float32)
+    _lib.check(L_.slx_v2x2ssd_bwd_begin(byref(s), M.data_ptr(), C.data_ptr(), mch.data_ptr(), dY.data_ptr(),
+                                        g0.data_ptr(), ws.data_ptr(), nbytes, _lib.stream_ptr(dev)),
+               "v2x2ssd backward (begin)")
+    return g0, ws
+
+
 def _bwd_impl(U, M, K, B, C, bp32, up32, starts, mch, final32, dY, d_final32, L, *,
-              want_initial: bool, want_prev: bool):
+              want_initial: bool, want_prev: bool, workspace=None):
     b, h, T, P = map(int, U.shape)
     D = int(B.shape[-1])
     s = _shape(b, h, T, P, D // 2, L, U.dtype)
@@ -205,8 +223,9 @@ def _bwd_impl(U, M, K, B, C, bp32, up32, starts, mch, final32, dY, d_final32, L,
     dUp = torch.empty((b, h, P), device=dev, dtype=torch.float32) if want_prev else None
     L_ = _lib.lib()
     nbytes = int(L_.slx_v2x2ssd_bwd_workspace_bytes(byref(s)))
-    ws = torch.empty((nbytes,), device=dev, dtype=torch.uint8)
-    _lib.check(L_.slx_v2x2ssd_bwd(
+    ws = torch.empty((nbytes,), device=dev, dtype=torch.uint8) if workspace is None else workspace
+    entry = L_.slx_v2x2ssd_bwd if workspace is None else L_.slx_v2x2ssd_bwd_finish  # dZ0 already there
+    _lib.check(entry(
         byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
         _lib.ptr(bp32), _lib.ptr(up32), starts.data_ptr(), mch.data_ptr(), final32.data_ptr(),
         dY.data_ptr(), _lib.ptr(d_final32), dU.data_ptr(), dM.data_ptr(), dK.data_ptr(),

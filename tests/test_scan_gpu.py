@@ -173,3 +173,30 @@ def test_backend_object_matches_op():
                           U_prev=inp["U_prev"], return_state=True)
     assert torch.equal(y, ref[0]) and torch.equal(nxt.state, ref[1])
     assert nxt.state.dtype == torch.bfloat16 and nxt.b_prev.shape == (1, 2, 32)
+
+
+@pytest.mark.parametrize("dtype,T,N,P,L", [(torch.float32, 160, 16, 32, 32), (torch.bfloat16, 384, 64, 64, 128)])
+def test_two_call_backward_and_final_only_state_pass(dtype, T, N, P, L):
+    """slx_v2x2ssd_bwd_begin + _finish give the bits of the single call; the first half's
+    d_initial is the single call's for a zero d_final; the final-only state pass gives the
+    final state of the full one."""
+    import slinoss_b200 as sb
+    from slinoss_b200.ops.v2x2ssd import _bwd_begin, _bwd_impl, _fwd_impl
+
+    inp = make_scan_inputs(2, 2, T, N, P, dtype, seed=77, streaming=True, with_init=True)
+    U, M, K, B, C = (inp[k] for k in ("U", "M", "K", "B", "C"))
+    init, bp, up = inp["initial_states"].float(), inp["B_prev"].float(), inp["U_prev"].float()
+    Y, fin, starts, mch = _fwd_impl(U, M, K, B, C, init, bp, up, L)
+    dY, dfin = inp["dY"], inp["d_final"].float()
+    one = _bwd_impl(U, M, K, B, C, bp, up, starts, mch, fin, dY, dfin, L, want_initial=True, want_prev=True)
+    g0, ws = _bwd_begin(M, C, mch, dY, L, P)
+    two = _bwd_impl(U, M, K, B, C, bp, up, starts, mch, fin, dY, dfin, L, want_initial=True, want_prev=True,
+                    workspace=ws)
+    for a, b_ in zip(one, two):
+        assert torch.equal(a, b_)
+    zero = _bwd_impl(U, M, K, B, C, bp, up, starts, mch, fin, dY, None, L, want_initial=True, want_prev=True)
+    assert torch.equal(g0, zero[5])
+    inc, mch2 = sb.chunk_increment_b200(U, M, K, B, B_prev=bp, U_prev=up, chunk_size=L)
+    st_full, fin_full = sb.state_passing_b200(inc, mch2, initial_states=init)
+    none, fin_only = sb.state_passing_b200(inc, mch2, initial_states=init, want_starts=False)
+    assert none is None and torch.equal(fin_only, fin_full) and torch.equal(fin_full, fin)
