@@ -4,6 +4,8 @@
 #include <cstdio>
 #include <type_traits>
 
+#include <initializer_list>
+
 #include "scan_simt.cuh"
 #include "scan_tc.cuh"
 #include "scan_tc_bwd.cuh"
@@ -121,6 +123,15 @@ static int launch_scan_bwd(const ScanDims &d, const ScanBwdArgs<T> &a, cudaStrea
 
 // ---- tensor-core path selection ----------------------------------------------------
 static int g_use_tc = 1;  // 0 forces the fp32-exact CUDA-core kernels for every dtype
+
+// every kernel of this file reads and writes its tensors with 8- and 16-byte accesses
+static bool all_aligned16(std::initializer_list<const void *> ptrs) {
+  for (const void *p : ptrs)
+    if (p != nullptr && (reinterpret_cast<uintptr_t>(p) & 15) != 0) return false;
+  return true;
+}
+#define SLX_REQUIRE_ALIGNED(what, ...) \
+  SLX_REQUIRE(all_aligned16({__VA_ARGS__}), SLX_E_UNSUPPORTED, what ": tensor pointers must be 16-byte aligned")
 
 static bool tc_eligible(const ScanDims &d, int dtype) {
   return g_use_tc && (dtype == SLX_BF16 || dtype == SLX_F16) && d.L == kTcL && d.P == kTcP && d.D % 64 == 0 &&
@@ -261,6 +272,7 @@ int slx_chunk_increment_fwd(const slx_scan_shape *s, const void *U, const float 
   int rc = check_shape(s, &d);
   if (rc) return rc;
   SLX_REQUIRE(U && M && K && B && inc && m_chunk, SLX_E_NULL, "chunk_increment_fwd: NULL tensor");
+  SLX_REQUIRE_ALIGNED("chunk_increment_fwd", U, M, K, B, B_prev, U_prev, inc, m_chunk);
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
   if (tc_eligible(d, s->dtype)) {
     if (s->dtype == SLX_BF16)
@@ -277,6 +289,7 @@ int slx_state_passing_fwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const fl
   SLX_REQUIRE(BH > 0 && NC > 0 && P > 0 && N > 0, SLX_E_SHAPE, "state_passing_fwd: sizes must be positive");
   SLX_REQUIRE(BH <= 65535, SLX_E_UNSUPPORTED, "batch_heads=%d exceeds 65535", BH);
   SLX_REQUIRE(inc && m_chunk && final_state, SLX_E_NULL, "state_passing_fwd: NULL tensor");
+  SLX_REQUIRE_ALIGNED("state_passing_fwd", inc, initial_states, chunk_starts, final_state);
   return launch_state_fwd(BH, NC, P, N, inc, m_chunk, initial_states, chunk_starts, final_state, as_stream(stream));
 }
 
@@ -287,6 +300,7 @@ int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M, c
   int rc = check_shape(s, &d);
   if (rc) return rc;
   SLX_REQUIRE(U && M && K && B && C && chunk_starts && Y, SLX_E_NULL, "chunk_scan_fwd: NULL tensor");
+  SLX_REQUIRE_ALIGNED("chunk_scan_fwd", U, M, K, B, C, chunk_starts, B_prev, U_prev, Y);
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
   if (tc_eligible(d, s->dtype)) {
     if (s->dtype == SLX_BF16)
@@ -324,6 +338,7 @@ int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *
   int rc = check_shape(s, &d);
   if (rc) return rc;
   SLX_REQUIRE(M && C && dY && dZ0, SLX_E_NULL, "chunk_scan_bwd_dz0: NULL tensor");
+  SLX_REQUIRE_ALIGNED("chunk_scan_bwd_dz0", M, C, dY, dZ0);
   if (tc_eligible(d, s->dtype)) {
     if (s->dtype == SLX_BF16)
       return launch_outer_tc<__nv_bfloat16, 1>(d, dY, C, M, nullptr, nullptr, nullptr, dZ0, nullptr,
@@ -341,6 +356,7 @@ int slx_state_passing_bwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const fl
   SLX_REQUIRE(BH > 0 && NC > 0 && P > 0 && N > 0, SLX_E_SHAPE, "state_passing_bwd: sizes must be positive");
   SLX_REQUIRE(BH <= 65535, SLX_E_UNSUPPORTED, "batch_heads=%d exceeds 65535", BH);
   SLX_REQUIRE(dZ0 && m_chunk, SLX_E_NULL, "state_passing_bwd: NULL tensor");
+  SLX_REQUIRE_ALIGNED("state_passing_bwd", dZ0, chunk_starts, final_state, d_final, d_inc, d_initial);
   SLX_REQUIRE((zdot == nullptr) == (zdot_partials == nullptr), SLX_E_NULL,
               "state_passing_bwd: zdot and zdot_partials go together");
   SLX_REQUIRE(zdot == nullptr || (chunk_starts && final_state), SLX_E_NULL,
@@ -360,6 +376,8 @@ int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M, c
   SLX_REQUIRE(U && M && K && B && C && chunk_starts && d_inc && zdot && dY && dU && dM && dK && dB && dC && carryB &&
                   carryU,
               SLX_E_NULL, "chunk_scan_bwd: NULL tensor");
+  SLX_REQUIRE_ALIGNED("chunk_scan_bwd", U, M, K, B, C, B_prev, U_prev, chunk_starts, d_inc, dY, dU, dM, dK, dB, dC,
+                      carryB, carryU);
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
   const bool tc = tc_eligible(d, s->dtype);
   SLX_DISPATCH_T(s->dtype, {
@@ -383,6 +401,7 @@ static int v2x2ssd_bwd_impl(const slx_scan_shape *s, const void *U, const float 
   if (rc) return rc;
   SLX_REQUIRE(U && M && K && B && C && chunk_starts && m_chunk && final_state && dY && dU && dM && dK && dB && dC,
               SLX_E_NULL, "v2x2ssd_bwd: NULL tensor");
+  SLX_REQUIRE_ALIGNED("v2x2ssd_bwd", final_state, d_final, d_initial, dB_prev, dU_prev);
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
   const BwdWs w = bwd_ws(d);
   SLX_REQUIRE(workspace != nullptr && workspace_bytes >= w.total, SLX_E_WORKSPACE,

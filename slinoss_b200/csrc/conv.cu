@@ -18,7 +18,8 @@
 namespace slx {
 
 constexpr int kConvThreads = 128;
-constexpr int kConvAhead = 8;  // rows each thread requests ahead of its walk
+constexpr int kConvAhead = 8;      // rows each thread requests ahead of its walk (backward: x and dy)
+constexpr int kConvAheadFwd = 8;   // forward: x only (16 measured slower)
 constexpr int kConvVec = 4;    // channels per thread: 8-byte vectors of half types, 16-byte of fp32
 
 template <typename T, int VEC>
@@ -125,15 +126,15 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_fwd_kernel(const T *__re
   load_cat<T, VEC>(x, state, d, b, t_lo - 3, c0, x0);
   load_cat<T, VEC>(x, state, d, b, t_lo - 2, c0, x1);
   load_cat<T, VEC>(x, state, d, b, t_lo - 1, c0, x2);
-  // kConvAhead rows are requested before any of them is used, so that each thread keeps
+  // kConvAheadFwd rows are requested before any of them is used, so that each thread keeps
   // several independent loads in flight along its otherwise sequential walk
-  for (int tb = t_lo; tb < t_hi; tb += kConvAhead) {
-    RowSlice<T, VEC> xr[kConvAhead];
+  for (int tb = t_lo; tb < t_hi; tb += kConvAheadFwd) {
+    RowSlice<T, VEC> xr[kConvAheadFwd];
 #pragma unroll
-    for (int u = 0; u < kConvAhead; ++u)
+    for (int u = 0; u < kConvAheadFwd; ++u)
       if (tb + u < t_hi) ld_raw<T, VEC>(x + (long long)b * d.xbs + (long long)(tb + u) * d.xs + c0, xr[u]);
 #pragma unroll
-    for (int u = 0; u < kConvAhead; ++u) {
+    for (int u = 0; u < kConvAheadFwd; ++u) {
       const int t = tb + u;
       if (t >= t_hi) break;
       float o[VEC];

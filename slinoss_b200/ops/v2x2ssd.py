@@ -113,8 +113,16 @@ def _require_cuda(*tensors) -> None:
             raise ValueError("slinoss_b200 v2x2ssd requires CUDA tensors.")
 
 
+def _aligned(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """The kernels use 16-byte accesses: a view that starts at an odd offset of its storage is
+    copied to a fresh (aligned) tensor."""
+    if t is None or t.data_ptr() % 16 == 0:
+        return t
+    return t.clone(memory_format=torch.contiguous_format)
+
+
 def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
-    return None if t is None else t.detach().to(torch.float32).contiguous()
+    return None if t is None else _aligned(t.detach().to(torch.float32).contiguous())
 
 
 def _shape(b, h, T, P, N, L, dtype) -> _lib.ScanShape:
@@ -272,7 +280,7 @@ class _V2x2SSDFn(torch.autograd.Function):
             d_final = dB_last = dU_last = None
         dU = dM = dK = dB = dC = d_init = dBp = dUp = None
         if dY is not None or d_final is not None:
-            dYc = (torch.zeros_like(U) if dY is None else dY.to(U.dtype).contiguous())
+            dYc = (torch.zeros_like(U) if dY is None else _aligned(dY.to(U.dtype).contiguous()))
             dfin = None if d_final is None else d_final.to(torch.float32).contiguous()
             dU, dM, dK, dB, dC, d_init, dBp, dUp = _bwd_impl(
                 U, M, K, B, C, bp32, up32, starts, mch, final32, dYc, dfin, ctx.L,
@@ -329,6 +337,7 @@ def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=
     Ua, Ba, Ca = (t if t.dtype == act else t.to(act) for t in (U, B, C))
     Mf = M if M.dtype == torch.float32 else M.to(torch.float32)
     Kf = K if K.dtype == torch.float32 else K.to(torch.float32)
+    Ua, Ba, Ca, Mf, Kf = (_aligned(t) for t in (Ua, Ba, Ca, Mf, Kf))
     if retile and act in (torch.bfloat16, torch.float16) and P == 64 and D % 64 == 0 and D <= 256:
         chunk_size = 128
     needs_grad = torch.is_grad_enabled() and any(

@@ -88,3 +88,25 @@ def test_scan_backend_threads_state_through(monkeypatch):
 def test_unsupported_chunk_is_a_value_error():
     with pytest.raises(ValueError, match="chunk_size must be one of"):
         op._shape(1, 1, 8, 4, 2, 48, torch.float32)
+
+
+def test_decode_step_host_checks():
+    """The decode step raises on CPU tensors and on mismatched shapes before any launch."""
+    import types
+
+    kw = dict(dt_min=1e-4, dt_max=1e-1, r_min=0.9, r_max=1.0, theta_bound=3.14, k_max=0.5, eps=1e-8,
+              b_scale=torch.ones(2, 2, 4), c_scale=torch.ones(2, 2, 4),
+              **{k: torch.zeros(2) for k in ("dt_bias", "gamma_bias", "omega_bias", "mix_r_bias", "mix_theta_bias",
+                                             "mix_k_prev_bias", "mix_k_curr_bias")})
+    v, p, bc, g, sk = (torch.zeros(1, 2, 8), torch.zeros(1, 2, 13), torch.zeros(1, 2, 4, 4), torch.zeros(1, 2, 8),
+                       torch.zeros(2, 8))
+    with pytest.raises(ValueError, match="requires CUDA"):
+        slinoss_b200.mixer_decode_step_b200(v, p, bc, g, sk, **kw)
+    be = backends.B200MixerDecodeBackend()
+    owner = types.SimpleNamespace(d_state=4, output_norm=None)
+    assert not be.supports(owner, batch_size=1, device=torch.device("cpu"), dtype=torch.float32)
+    assert be.supports(owner, batch_size=300, device=torch.device("cuda", 0), dtype=torch.bfloat16)
+    assert not be.supports(types.SimpleNamespace(d_state=5, output_norm=None), batch_size=1,
+                           device=torch.device("cuda", 0), dtype=torch.bfloat16)
+    assert not be.supports(types.SimpleNamespace(d_state=4, output_norm=object()), batch_size=1,
+                           device=torch.device("cuda", 0), dtype=torch.bfloat16)

@@ -200,3 +200,32 @@ def test_two_call_backward_and_final_only_state_pass(dtype, T, N, P, L):
     st_full, fin_full = sb.state_passing_b200(inc, mch2, initial_states=init)
     none, fin_only = sb.state_passing_b200(inc, mch2, initial_states=init, want_starts=False)
     assert none is None and torch.equal(fin_only, fin_full) and torch.equal(fin_full, fin)
+
+
+def test_views_at_odd_storage_offsets_are_handled():
+    """Contiguous views whose first element is not 16-byte aligned are copied by the op; the C
+    ABI itself refuses such pointers instead of issuing misaligned vector accesses."""
+    import ctypes
+
+    import slinoss_b200 as sb
+    from slinoss_b200 import _lib
+
+    inp = make_scan_inputs(1, 2, 128, 64, 64, torch.bfloat16, seed=3, dist="cfg2")
+
+    def shifted(t):  # same values, storage offset of one element
+        flat = torch.empty(t.numel() + 1, dtype=t.dtype, device=t.device)
+        flat[1:].copy_(t.reshape(-1))
+        return flat[1:].view(t.shape)
+
+    args = [inp[k] for k in ("U", "M", "K", "B", "C")]
+    y_ref = sb.v2x2ssd_b200(*args, chunk_size=128)
+    sh = [shifted(t) for t in args]
+    assert any(t.data_ptr() % 16 for t in sh)
+    assert torch.equal(sb.v2x2ssd_b200(*sh, chunk_size=128), y_ref)
+    U, M, K, B, C = sh
+    s = _lib.ScanShape(2, 128, 64, 64, 128, _lib.dtype_code(torch.bfloat16))
+    inc = torch.empty(1, 2, 1, 64, 128, device="cuda")
+    mch = torch.empty(1, 2, 1, 2, device="cuda")
+    rc = _lib.lib().slx_chunk_increment_fwd(ctypes.byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(),
+                                            None, None, inc.data_ptr(), mch.data_ptr(), _lib.stream_ptr(U.device))
+    assert rc == -3 and b"16-byte aligned" in _lib.lib().slx_last_error_string()
