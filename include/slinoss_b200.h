@@ -21,6 +21,9 @@
  *   chunk tensors (BH, NC, P, 2N) / (BH, NC, 2), NC = ceil(T / chunk), fp32
  * Tokens past T in the last chunk behave as M=1, K=U=B=C=0
  * (reference.py:541-667).  Nullable pointers are marked [opt].
+ * The scan entry points read and write with 16-byte accesses: every tensor
+ * pointer handed to them must be 16-byte aligned (SLX_E_UNSUPPORTED otherwise).
+ * Scan prep and conv take any alignment and pick their vector width from it.
  */
 #ifndef SLINOSS_B200_H_
 #define SLINOSS_B200_H_
