@@ -301,6 +301,13 @@ int slx_set_tensor_path(int enable);
  * out and the affected launch produced undefined values. */
 int slx_read_tc_status(int *host_out);
 
+/* Synchronising read-and-clear of the scan's input status word: *host_out != 0
+ * means some launch since the last read met a transition M of magnitude exactly 0.
+ * The reference raises for such input (reference.py:480-485: the log-magnitude /
+ * phase split does not exist); these kernels cannot raise from the device, so they
+ * set this word and fill the affected chunk and everything downstream with NaN. */
+int slx_read_scan_status(int *host_out);
+
 /* Diagnostic (synchronising): 64 clock64() stamps written by CTA (0,0) of the
  * last tensor-core backward launch at its phase boundaries. */
 int slx_read_phase_clock(long long *host_out64);

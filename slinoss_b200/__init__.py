@@ -5,7 +5,7 @@ from thin torch host code.  Importing this package does not need a GPU; calling
 an op does, and needs the built library (``python -m slinoss_b200.build``).
 """
 
-from ._lib import read_tc_status, set_tensor_path
+from ._lib import read_scan_status, read_tc_status, set_tensor_path
 from .backends import (B200CConv1dBackend, B200MixerDecodeBackend, B200ScanBackend,
                        B200ScanPrepBackend)
 from .ops import (cconv1d_b200, chunk_increment_b200, chunk_scan_b200, mixer_decode_step_b200,
@@ -16,5 +16,5 @@ __all__ = [
     "v2x2ssd_b200", "chunk_increment_b200", "state_passing_b200", "chunk_scan_b200",
     "scanprep_b200", "cconv1d_b200", "B200ScanBackend", "B200ScanPrepBackend",
     "B200CConv1dBackend", "B200MixerDecodeBackend", "mixer_decode_step_b200", "ScanInputs", "ScanPrepInputs", "ScanState", "set_tensor_path",
-    "read_tc_status",
+    "read_tc_status", "read_scan_status",
 ]

@@ -68,6 +68,7 @@ SIGNATURES = {
     "slx_cconv1d_bwd_noalloc": (c_int32, [POINTER(ConvShape)] + [_P] * 11),
     "slx_set_tensor_path": (c_int32, [c_int32]),
     "slx_read_tc_status": (c_int32, [POINTER(c_int32)]),
+    "slx_read_scan_status": (c_int32, [POINTER(c_int32)]),
     "slx_read_phase_clock": (c_int32, [POINTER(c_int64)]),
     "slx_umma_selftest": (c_int32, [c_int32] + [_P] * 5),
     "slx_decode_step": (c_int32, [POINTER(DecodeShape)] + [_P] * 15),
@@ -127,6 +128,14 @@ def set_tensor_path(enable: bool) -> bool:
     """Process-wide switch between the tcgen05 kernels (default, where a shape is
     eligible) and the fp32-exact CUDA-core kernels.  Returns the previous value."""
     return bool(lib().slx_set_tensor_path(1 if enable else 0))
+
+
+def read_scan_status() -> int:
+    """Synchronising read-and-clear of the scan's input status word (non-zero: some launch
+    since the last read met a transition of magnitude exactly 0 and produced NaN)."""
+    out = c_int32(0)
+    check(lib().slx_read_scan_status(ctypes.byref(out)), "read_scan_status")
+    return int(out.value)
 
 
 def read_tc_status() -> int:

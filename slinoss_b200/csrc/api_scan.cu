@@ -264,6 +264,14 @@ int slx_read_tc_status(int *host_out) {
   if (e != cudaSuccess) return fail((int)e, "read_tc_status: %s", cudaGetErrorString(e));
   return SLX_OK;
 }
+int slx_read_scan_status(int *host_out) {
+  SLX_REQUIRE(host_out != nullptr, SLX_E_NULL, "read_scan_status: NULL pointer");
+  int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_scan_bad, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_scan_bad, &zero, sizeof(int));
+  if (e != cudaSuccess) return fail((int)e, "read_scan_status: %s", cudaGetErrorString(e));
+  return SLX_OK;
+}
 const char *slx_last_error_string(void) { return g_err; }
 
 int slx_chunk_increment_fwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,

@@ -49,7 +49,9 @@ __device__ __forceinline__ float2 cscale(float2 a, float s) { return make_float2
 // (slinoss/ops/v2x2ssd/reference.py:466-491): lp[t] = sum_{tau<=t} log|m_tau|,
 // ph[t] = normalised prod_{tau<=t} m_tau/|m_tau|.  Tokens >= valid act as m = 1.
 // Executed by warp 0 of the CTA; results land in shared memory (lp, ph of
-// length L) and the caller synchronises.  An exactly-zero |m| sets *bad_flag.
+// length L) and the caller synchronises.  An exactly-zero |m| has no log-magnitude / phase
+// split (the reference raises, reference.py:480-485): it sets *bad_flag and poisons the chunk
+// with NaN, which the state pass carries into everything downstream.
 template <bool FAST = false>
 __device__ __forceinline__ void chunk_prefix_warp(int run_warp, const float *__restrict__ Mchunk, int L, int valid,
                                                   float *lp, float2 *ph, float2 *mraw, int *bad_flag) {
@@ -70,7 +72,7 @@ __device__ __forceinline__ void chunk_prefix_warp(int run_warp, const float *__r
         if (m2 == 0.f) {
           if (bad_flag) atomicExch(bad_flag, 1);
           m2 = 1.f;
-          m = make_float2(1.f, 0.f);
+          m = make_float2(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000));  // poison: see header
         }
         inv = rsqrtf(m2);
         lg = 0.5f * __logf(m2);
@@ -79,7 +81,7 @@ __device__ __forceinline__ void chunk_prefix_warp(int run_warp, const float *__r
         if (mag == 0.f) {
           if (bad_flag) atomicExch(bad_flag, 1);
           mag = 1.f;
-          m = make_float2(1.f, 0.f);
+          m = make_float2(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
         }
         inv = 1.f / mag;
         lg = logf(mag);
@@ -156,7 +158,7 @@ __device__ __forceinline__ void chunk_prefix_fast128(const float2 (&min)[4], flo
     if (m2 == 0.f) {
       if (bad_flag) atomicExch(bad_flag, 1);
       m2 = 1.f;
-      m = make_float2(1.f, 0.f);
+      m = make_float2(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
     }
     const float inv = rsqrtf(m2);
     mraw[t0 + i] = m;

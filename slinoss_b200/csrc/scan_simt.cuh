@@ -20,6 +20,8 @@
 
 namespace slx {
 
+__device__ int g_scan_bad = 0;  // becomes 1 when a kernel met a transition of magnitude exactly 0
+
 constexpr int kThreads = 256;
 constexpr int kPMax = 64;
 constexpr int kLdP = kPMax + 1;
@@ -148,7 +150,7 @@ __global__ void __launch_bounds__(kThreads) chunk_outer_kernel(OuterArgs<T> a) {
   const int valid = min(L, d.T - t0);
   const size_t tok0 = (size_t)bh * d.T + t0;
 
-  chunk_prefix_warp0(a.M + tok0 * 2, L, valid, lp, ph, mraw, nullptr);
+  chunk_prefix_warp0(a.M + tok0 * 2, L, valid, lp, ph, mraw, &g_scan_bad);
   for (int idx = tid; idx < L * d.P; idx += kThreads) {
     int t = idx / d.P, p = idx - t * d.P;
     As[t * kLdP + p] = (t < valid) ? to_f(a.A[(tok0 + t) * d.P + p]) : 0.f;
@@ -257,7 +259,7 @@ struct ScanFwdArgs {
   const T *U, *B, *C;
   const float *M, *K, *starts, *Bprev, *Uprev;
   T *Y;
-  int *bad;  // set to 1 when some |m| == 0 (reference.py:480-485 raises)
+  int *bad;  // unused (the kernels report through g_scan_bad)
   ScanDims d;
 };
 
@@ -292,7 +294,7 @@ __global__ void __launch_bounds__(kThreads) chunk_scan_fwd_kernel(ScanFwdArgs<T>
   const int valid = min(L, d.T - t0);
   const size_t tok0 = (size_t)bh * d.T + t0;
 
-  chunk_prefix_warp0(a.M + tok0 * 2, L, valid, lp, ph, mraw, a.bad);
+  chunk_prefix_warp0(a.M + tok0 * 2, L, valid, lp, ph, mraw, &g_scan_bad);
   for (int t = tid; t < L; t += kThreads) {
     float2 vp = make_float2(0.f, 0.f), vc = vp;
     if (t < valid) {
@@ -492,7 +494,7 @@ __global__ void __launch_bounds__(kThreads) chunk_scan_bwd_kernel(ScanBwdArgs<T>
   const int valid = min(L, d.T - t0);
   const size_t tok0 = (size_t)bh * d.T + t0;
 
-  chunk_prefix_warp0(a.M + tok0 * 2, L, valid, lp, ph, mraw, nullptr);
+  chunk_prefix_warp0(a.M + tok0 * 2, L, valid, lp, ph, mraw, &g_scan_bad);
   for (int t = tid; t < L; t += kThreads) {
     float2 vp = make_float2(0.f, 0.f), vc = vp;
     if (t < valid) {

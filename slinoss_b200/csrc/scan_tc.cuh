@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
     umma::mbar_init(mbar_s, 1);
     umma::fence_mbar_init();
   }
-  if (warp == 2) chunk_prefix_fast128(mreg, lp, ph, mraw, a.bad);
+  if (warp == 2) chunk_prefix_fast128(mreg, lp, ph, mraw, &g_scan_bad);
   if (tid >= 128) {
     int t = tid - 128;
     float2 vp = make_float2(0.f, 0.f), vc = vp;
@@ -450,7 +450,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_outer_tc_kernel(OuterArgs
       else if (a.Bprev) bv = *reinterpret_cast<const float2 *>(a.Bprev + (size_t)bh * d.D + 2 * n);
     }
   }
-  if (warp == 2) chunk_prefix_fast128(mreg, lp, ph, mraw, nullptr);
+  if (warp == 2) chunk_prefix_fast128(mreg, lp, ph, mraw, &g_scan_bad);
   if (MODE == 0 && warp == 2) {
     // chunk transition = product of the raw multipliers: four per lane, then a butterfly
     float2 acc = cmul(cmul(mraw[4 * lane], mraw[4 * lane + 1]), cmul(mraw[4 * lane + 2], mraw[4 * lane + 3]));

@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
     umma::mbar_init(mbar_s, 1);
     umma::fence_mbar_init();
   }
-  if (warp == 2) chunk_prefix_fast128(mreg, lp, ph, mraw, nullptr);
+  if (warp == 2) chunk_prefix_fast128(mreg, lp, ph, mraw, &g_scan_bad);
   if (tid >= 128 && tid < 256) {
     int t = tid - 128;
     float2 vp = make_float2(0.f, 0.f), vc = vp;

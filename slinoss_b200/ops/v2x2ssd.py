@@ -304,7 +304,7 @@ class _V2x2SSDFn(torch.autograd.Function):
 def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=None, U_prev=None,
                  compute_dtype: Optional[torch.dtype] = None,
                  output_dtype: Optional[torch.dtype] = None, return_state: bool = False,
-                 retile: bool = True):
+                 retile: bool = True, strict: bool = False):
     """Drop-in for ``v2x2ssd_cute`` (cute/api.py:52): returns ``Y`` or
     ``(Y, final_state, B_last, U_last)``; differentiable in all eight inputs.
 
@@ -313,6 +313,11 @@ def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=
     state width up to 256 are tiled in the 128-token chunks of the tcgen05 kernels whatever
     ``chunk_size`` asks for (the reference's default is 64); ``retile=False`` keeps the
     requested tiling (fp32-exact kernels for anything but 128).
+
+    A transition ``M`` of magnitude exactly 0 makes the reference raise ``ValueError``
+    (reference.py:480-485).  The kernels cannot raise: they fill the affected outputs with NaN
+    and set a status word (``read_scan_status``).  ``strict=True`` reads that word after the
+    forward (one device synchronisation per call) and raises like the reference.
     """
     b, h, T, N, P = _validate_inputs(U, M, K, B, C, initial_states, B_prev, U_prev)
     if U.device.type != "cuda":
@@ -342,16 +347,24 @@ def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=
         chunk_size = 128
     needs_grad = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (U, M, K, B, C, initial_states, B_prev, U_prev))
+    if strict:
+        _lib.read_scan_status()  # clear what earlier calls may have left
+
+    def _checked(out):
+        if strict and _lib.read_scan_status():
+            raise ValueError("M has an entry of magnitude exactly 0: the chunked scan needs abs(M) > 0.")
+        return out
+
     if needs_grad:
-        return _V2x2SSDFn.apply(Ua, Mf, Kf, Ba, Ca, initial_states, B_prev, U_prev, int(chunk_size),
-                                odtype, bool(return_state))
+        return _checked(_V2x2SSDFn.apply(Ua, Mf, Kf, Ba, Ca, initial_states, B_prev, U_prev, int(chunk_size),
+                                         odtype, bool(return_state)))
     Y, final32, _, _ = _fwd_impl(Ua, Mf, Kf, Ba, Ca, _f32(initial_states), _f32(B_prev),
                                  _f32(U_prev), int(chunk_size))
     Y = Y.to(odtype)
     if not return_state:
-        return Y
-    return (Y, final32.to(odtype), B[:, :, -1, :].to(odtype).contiguous(),
-            U[:, :, -1, :].to(odtype).contiguous())
+        return _checked(Y)
+    return _checked((Y, final32.to(odtype), B[:, :, -1, :].to(odtype).contiguous(),
+                     U[:, :, -1, :].to(odtype).contiguous()))
 
 
 __all__ = ["v2x2ssd_b200", "chunk_increment_b200", "state_passing_b200", "chunk_scan_b200"]

@@ -229,3 +229,26 @@ def test_views_at_odd_storage_offsets_are_handled():
     rc = _lib.lib().slx_chunk_increment_fwd(ctypes.byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(),
                                             None, None, inc.data_ptr(), mch.data_ptr(), _lib.stream_ptr(U.device))
     assert rc == -3 and b"16-byte aligned" in _lib.lib().slx_last_error_string()
+
+
+@pytest.mark.parametrize("dtype,L", [(torch.float32, 32), (torch.bfloat16, 128)])
+def test_zero_transition_is_flagged_not_silently_replaced(dtype, L):
+    """abs(M) == 0 makes the reference raise (reference.py:480-485).  Here the outputs of the
+    zero transition's token and everything after it are NaN, a status word is set, and strict=True
+    raises."""
+    import slinoss_b200 as sb
+
+    inp = make_scan_inputs(1, 2, 384, 64, 64, dtype, seed=8)
+    M = inp["M"].clone()
+    M[0, 1, 200] = 0.0
+    args = [inp["U"], M, inp["K"], inp["B"], inp["C"]]
+    sb.read_scan_status()
+    y = sb.v2x2ssd_b200(*args, chunk_size=L)
+    assert sb.read_scan_status() == 1 and sb.read_scan_status() == 0
+    c0 = (200 // L) * L
+    assert bool(torch.isfinite(y[0, 0]).all()) and bool(torch.isfinite(y[0, 1, :c0]).all())
+    assert bool(torch.isnan(y[0, 1, 200:]).all())   # from the zero transition on, through every later chunk
+    with pytest.raises(ValueError, match="magnitude exactly 0"):
+        sb.v2x2ssd_b200(*args, chunk_size=L, strict=True)
+    y_ok = sb.v2x2ssd_b200(inp["U"], inp["M"], inp["K"], inp["B"], inp["C"], chunk_size=L, strict=True)
+    assert bool(torch.isfinite(y_ok).all())
