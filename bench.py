@@ -457,7 +457,7 @@ def main() -> int:
     flops = dense_flops_bwd_chunk(L, P, D) * BH * NC
     achieved = flops / (k_ms * 1e-3) / 1e12
     # DRAM bytes of one launch: ncu measured 429.2 MB for 1024 chunks of this kernel at P64 N128
-    # (profiles/stage_kernels_b1h32T4096_ncu_sections.md); the kernel's traffic is per chunk
+    # (the capture's summary is committed under profiles/); the kernel's traffic is per chunk
     traffic = None
     if L == 128 and P == 64 and N == 128:
         traffic = 429.2e6 / 1024 * BH * NC
