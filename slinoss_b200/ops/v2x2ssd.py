@@ -247,7 +247,7 @@ class _V2x2SSDFn(torch.autograd.Function):
     ``_V2x2SSDCuTeTrainingFn`` (cute/autograd.py:40-266)."""
 
     @staticmethod
-    def forward(ctx, U, M, K, B, C, initial_states, B_prev, U_prev, L, odtype, return_state):
+    def forward(ctx, U, M, K, B, C, initial_states, B_prev, U_prev, L, odtype, return_state, residual="fp32"):
         init32, bp32, up32 = _f32(initial_states), _f32(B_prev), _f32(U_prev)
         Y, final32, starts, mch = _fwd_impl(U.detach(), M.detach(), K.detach(), B.detach(),
                                             C.detach(), init32, bp32, up32, L)
@@ -257,6 +257,15 @@ class _V2x2SSDFn(torch.autograd.Function):
         ctx.has_prev = B_prev is not None
         ctx.init_dtype = None if initial_states is None else initial_states.dtype
         ctx.prev_dtype = None if B_prev is None else B_prev.dtype
+        # What is kept of the chunk-start states (the largest residual, (b,h,NC,P,2N) fp32):
+        # "fp32" as computed; "half" rounded to the activation dtype (half the bytes; the tensor-core
+        # kernels round Z0 to that dtype anyway); "recompute" nothing: the backward rebuilds them
+        # from the inputs with one more chunk-increment and state pass.
+        ctx.residual = residual
+        if residual == "half" and U.dtype != torch.float32:
+            starts = starts.to(U.dtype)
+        elif residual == "recompute":
+            starts = init32 if init32 is not None else final32.new_empty(0)
         saved = [U, M, K, B, C, mch, starts, final32]
         if ctx.has_prev:
             saved += [bp32, up32]
@@ -282,6 +291,13 @@ class _V2x2SSDFn(torch.autograd.Function):
         if dY is not None or d_final is not None:
             dYc = (torch.zeros_like(U) if dY is None else _aligned(dY.to(U.dtype).contiguous()))
             dfin = None if d_final is None else d_final.to(torch.float32).contiguous()
+            if ctx.residual == "recompute":
+                init32 = starts if starts.numel() else None
+                inc, _ = chunk_increment_b200(U, M, K, B, B_prev=bp32, U_prev=up32, chunk_size=ctx.L)
+                starts, _ = state_passing_b200(inc, mch, initial_states=init32)
+                del inc
+            elif starts.dtype != torch.float32:
+                starts = starts.to(torch.float32)
             dU, dM, dK, dB, dC, d_init, dBp, dUp = _bwd_impl(
                 U, M, K, B, C, bp32, up32, starts, mch, final32, dYc, dfin, ctx.L,
                 want_initial=ctx.has_init, want_prev=ctx.has_prev)
@@ -297,14 +313,14 @@ class _V2x2SSDFn(torch.autograd.Function):
             d_init = d_init.to(ctx.init_dtype)
         if dBp is not None:
             dBp, dUp = dBp.to(ctx.prev_dtype), dUp.to(ctx.prev_dtype)
-        return dU, dM, dK, dB, dC, d_init, dBp, dUp, None, None, None
+        return dU, dM, dK, dB, dC, d_init, dBp, dUp, None, None, None, None
 
 
 @torch.compiler.disable
 def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=None, U_prev=None,
                  compute_dtype: Optional[torch.dtype] = None,
                  output_dtype: Optional[torch.dtype] = None, return_state: bool = False,
-                 retile: bool = True, strict: bool = False):
+                 retile: bool = True, strict: bool = False, residual: str = "fp32"):
     """Drop-in for ``v2x2ssd_cute`` (cute/api.py:52): returns ``Y`` or
     ``(Y, final_state, B_last, U_last)``; differentiable in all eight inputs.
 
@@ -318,7 +334,15 @@ def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=
     (reference.py:480-485).  The kernels cannot raise: they fill the affected outputs with NaN
     and set a status word (``read_scan_status``).  ``strict=True`` reads that word after the
     forward (one device synchronisation per call) and raises like the reference.
+
+    ``residual`` chooses what autograd keeps of the chunk-start states, the largest residual
+    ((batch, heads, chunks, P, 2N) fp32, which the reference saves as is, cute/autograd.py:98):
+    ``"fp32"`` (default), ``"half"`` (rounded to the activation dtype: half the bytes, one
+    conversion pass each way) or ``"recompute"`` (nothing kept; the backward rebuilds them with
+    one more chunk-increment and state pass).
     """
+    if residual not in ("fp32", "half", "recompute"):
+        raise ValueError(f"residual must be 'fp32', 'half' or 'recompute'. Got {residual!r}.")
     b, h, T, N, P = _validate_inputs(U, M, K, B, C, initial_states, B_prev, U_prev)
     if U.device.type != "cuda":
         raise ValueError("slinoss_b200 v2x2ssd requires CUDA tensors.")
@@ -357,7 +381,7 @@ def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=
 
     if needs_grad:
         return _checked(_V2x2SSDFn.apply(Ua, Mf, Kf, Ba, Ca, initial_states, B_prev, U_prev, int(chunk_size),
-                                         odtype, bool(return_state)))
+                                         odtype, bool(return_state), residual))
     Y, final32, _, _ = _fwd_impl(Ua, Mf, Kf, Ba, Ca, _f32(initial_states), _f32(B_prev),
                                  _f32(U_prev), int(chunk_size))
     Y = Y.to(odtype)

@@ -129,3 +129,30 @@ def test_requested_chunk_is_retiled_to_the_tensor_chunk():
     y_exact = sb.v2x2ssd_b200(*args, chunk_size=64, retile=False)
     assert not torch.equal(y_exact, y128)
     assert rel_err(to_np(y_exact), to_np(y128)) < 1e-2
+
+
+def test_residual_formats():
+    """What autograd keeps of the chunk-start states: 'recompute' gives the bits of the default,
+    'half' stays inside the half-precision tolerance."""
+    import slinoss_b200 as sb
+
+    inp = make_scan_inputs(2, 2, 512, 128, 64, torch.bfloat16, seed=17, streaming=True, with_init=True, dist="cfg2")
+
+    def run(residual):
+        lv = {k: inp[k].detach().clone().requires_grad_(True) for k in ("U", "M", "K", "B", "C", "initial_states",
+                                                                       "B_prev", "U_prev")}
+        Y, fin, _, _ = sb.v2x2ssd_b200(lv["U"], lv["M"], lv["K"], lv["B"], lv["C"], chunk_size=128,
+                                       initial_states=lv["initial_states"], B_prev=lv["B_prev"],
+                                       U_prev=lv["U_prev"], return_state=True, residual=residual)
+        g = torch.autograd.grad([Y, fin], list(lv.values()), [inp["dY"], inp["d_final"].to(fin.dtype)])
+        return Y, g
+
+    y0, g0 = run("fp32")
+    y1, g1 = run("recompute")
+    assert torch.equal(y0, y1) and all(torch.equal(a, b) for a, b in zip(g0, g1))
+    y2, g2 = run("half")
+    assert torch.equal(y0, y2)
+    for a, b in zip(g0, g2):
+        assert rel_err(to_np(b), to_np(a)) < 5e-3
+    with pytest.raises(ValueError, match="residual must be"):
+        sb.v2x2ssd_b200(inp["U"], inp["M"], inp["K"], inp["B"], inp["C"], chunk_size=128, residual="fp16")
