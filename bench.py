@@ -420,18 +420,21 @@ def main() -> int:
         U, M, Kt, B, C, dY = (inp[k].detach() for k in ("U", "M", "K", "B", "C", "dY"))
         Y = torch.empty_like(U)
         final = torch.empty((b, h, P, D), **f32)
-        starts = torch.empty((b, h, NC, P, D), **f32)
+        starts = torch.empty((b, h, NC, P, D), device=dev, dtype=_lib.starts_dtype(shape))
+        inc_buf = torch.empty((b, h, NC, P, D), **f32)
         mch = torch.empty((b, h, NC, 2), **f32)
         _lib.check(lib.slx_v2x2ssd_fwd(byref(shape), U.data_ptr(), M.data_ptr(), Kt.data_ptr(), B.data_ptr(),
                                        C.data_ptr(), None, None, None, Y.data_ptr(), final.data_ptr(),
-                                       starts.data_ptr(), mch.data_ptr(), None, st), "fwd")
-        d_inc = torch.empty_like(starts)
+                                       starts.data_ptr(), mch.data_ptr(), inc_buf.data_ptr(), st), "fwd")
+        del inc_buf
+        d_inc = torch.empty((b, h, NC, P, D), **f32)
         zdot = torch.empty((b, h, NC, 2), **f32)
         part = torch.empty((BH * NC * 2 * 64,), **f32)
         _lib.check(lib.slx_chunk_scan_bwd_dz0(byref(shape), M.data_ptr(), C.data_ptr(), dY.data_ptr(),
                                               d_inc.data_ptr(), st), "dz0")
         _lib.check(lib.slx_state_passing_bwd(BH, NC, P, N, d_inc.data_ptr(), mch.data_ptr(), starts.data_ptr(),
-                                             final.data_ptr(), None, d_inc.data_ptr(), None, zdot.data_ptr(),
+                                             _lib.dtype_code(starts.dtype), final.data_ptr(), None,
+                                             d_inc.data_ptr(), None, zdot.data_ptr(),
                                              part.data_ptr(), st), "state bwd")
         dU, dB, dC = torch.empty_like(U), torch.empty_like(B), torch.empty_like(C)
         dM, dK = torch.empty_like(M), torch.empty_like(Kt)

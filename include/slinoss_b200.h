@@ -18,7 +18,10 @@
  *   M        (BH, T, 2)        fp32 packed complex
  *   K        (BH, T, 2, 2)     fp32, tap 0 = prev, tap 1 = curr, each (re,im)
  *   states   (BH, P, 2N)       fp32 interleaved complex
- *   chunk tensors (BH, NC, P, 2N) / (BH, NC, 2), NC = ceil(T / chunk), fp32
+ *   chunk tensors (BH, NC, P, 2N) / (BH, NC, 2), NC = ceil(T / chunk), fp32;
+ *            chunk_starts alone is stored in slx_scan_starts_dtype(shape): the
+ *            activation dtype where the tensor-core kernels run (they round it
+ *            to that dtype anyway), fp32 otherwise
  * Tokens past T in the last chunk behave as M=1, K=U=B=C=0
  * (reference.py:541-667).  Nullable pointers are marked [opt].
  * The scan entry points read and write with 16-byte accesses: every tensor
@@ -35,7 +38,7 @@
 extern "C" {
 #endif
 
-#define SLX_ABI_VERSION 2
+#define SLX_ABI_VERSION 3
 
 typedef enum { SLX_F32 = 0, SLX_BF16 = 1, SLX_F16 = 2 } slx_dtype;
 
@@ -58,6 +61,9 @@ typedef struct {
 } slx_scan_shape;
 
 int slx_abi_version(void);
+
+/* slx_dtype in which the stages of this shape exchange chunk_starts. */
+int slx_scan_starts_dtype(const slx_scan_shape *s);
 const char *slx_last_error_string(void);
 
 /* ---- forward stages --------------------------------------------------- */
@@ -71,32 +77,36 @@ int slx_chunk_increment_fwd(const slx_scan_shape *s, const void *U,
                             float *m_chunk, void *stream);
 
 /* Replaces reference.py:1015 state_passing (CuTe: kernels/fwd/__init__.py:897).
- * chunk_starts may alias inc (the pass is then in place).  chunk_starts == NULL
+ * chunk_starts holds starts_dtype values (slx_dtype); with SLX_F32 it may alias
+ * inc (the pass is then in place).  chunk_starts == NULL
  * asks for final_state only (nothing else is written): the affine offset of a
  * segment when segments are chained across devices. */
 int slx_state_passing_fwd(int32_t batch_heads, int32_t n_chunks, int32_t P,
                           int32_t N, const float *inc, const float *m_chunk,
                           const float *initial_states /*[opt]*/,
-                          float *chunk_starts /*[opt]*/, float *final_state,
-                          void *stream);
+                          void *chunk_starts /*[opt]*/, int32_t starts_dtype,
+                          float *final_state, void *stream);
 
 /* Replaces reference.py:1059 chunk_scan (CuTe: kernels/fwd/__init__.py:1125). */
 int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M,
                        const float *K, const void *B, const void *C,
-                       const float *chunk_starts, const float *B_prev /*[opt]*/,
-                       const float *U_prev /*[opt]*/, void *Y, void *stream);
+                       const void *chunk_starts /* slx_scan_starts_dtype(s) */,
+                       const float *B_prev /*[opt]*/, const float *U_prev /*[opt]*/,
+                       void *Y, void *stream);
 
 /* Replaces reference.py:1195 v2x2ssd / cute/kernels/fwd/__init__.py:1691
  * v2x2ssd_fwd_cute: the three stages back to back on one stream.
- * increments: scratch of the size of chunk_starts for the chunk increments.
- * NULL makes chunk_starts double as the increment buffer: no extra memory, but
- * the state pass then overwrites each line it has just read, which runs at
- * well under half the speed of the two-buffer pass on B200. */
+ * increments: fp32 scratch of (BH, NC, P, 2N) floats for the chunk increments.
+ * NULL makes chunk_starts double as the increment buffer (only where
+ * slx_scan_starts_dtype(s) is fp32): no extra memory, but the state pass then
+ * overwrites each line it has just read, which runs at well under half the
+ * speed of the two-buffer pass on B200. */
 int slx_v2x2ssd_fwd(const slx_scan_shape *s, const void *U, const float *M,
                     const float *K, const void *B, const void *C,
                     const float *initial_states /*[opt]*/,
                     const float *B_prev /*[opt]*/, const float *U_prev /*[opt]*/,
-                    void *Y, float *final_state, float *chunk_starts,
+                    void *Y, float *final_state,
+                    void *chunk_starts /* slx_scan_starts_dtype(s) */,
                     float *m_chunk, float *increments /*[opt]*/, void *stream);
 
 /* ---- backward ----------------------------------------------------------- */
@@ -119,7 +129,7 @@ int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *
  * then not read).  d_inc NULL as well: only d_initial is written. */
 int slx_state_passing_bwd(int32_t batch_heads, int32_t n_chunks, int32_t P,
                           int32_t N, const float *dZ0, const float *m_chunk,
-                          const float *chunk_starts /*[opt]*/,
+                          const void *chunk_starts /*[opt]*/, int32_t starts_dtype,
                           const float *final_state /*[opt]*/,
                           const float *d_final /*[opt]*/, float *d_inc /*[opt]*/,
                           float *d_initial /*[opt]*/, float *zdot /*[opt]*/,
@@ -135,7 +145,7 @@ int slx_state_passing_bwd(int32_t batch_heads, int32_t n_chunks, int32_t P,
 int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M,
                        const float *K, const void *B, const void *C,
                        const float *B_prev /*[opt]*/, const float *U_prev /*[opt]*/,
-                       const float *chunk_starts, const float *d_inc,
+                       const void *chunk_starts, const float *d_inc,
                        const float *zdot, const void *dY, void *dU, float *dM,
                        float *dK, void *dB, void *dC, float *carryB,
                        float *carryU, void *stream);
@@ -147,7 +157,7 @@ int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M,
 int slx_v2x2ssd_bwd(const slx_scan_shape *s, const void *U, const float *M,
                     const float *K, const void *B, const void *C,
                     const float *B_prev /*[opt]*/, const float *U_prev /*[opt]*/,
-                    const float *chunk_starts, const float *m_chunk,
+                    const void *chunk_starts, const float *m_chunk,
                     const float *final_state, const void *dY,
                     const float *d_final /*[opt]*/, void *dU, float *dM,
                     float *dK, void *dB, void *dC, float *d_initial /*[opt]*/,
@@ -168,7 +178,7 @@ int slx_v2x2ssd_bwd_begin(const slx_scan_shape *s, const float *M, const void *C
 int slx_v2x2ssd_bwd_finish(const slx_scan_shape *s, const void *U, const float *M,
                            const float *K, const void *B, const void *C,
                            const float *B_prev /*[opt]*/, const float *U_prev /*[opt]*/,
-                           const float *chunk_starts, const float *m_chunk,
+                           const void *chunk_starts, const float *m_chunk,
                            const float *final_state, const void *dY,
                            const float *d_final /*[opt]*/, void *dU, float *dM,
                            float *dK, void *dB, void *dC, float *d_initial /*[opt]*/,

@@ -50,14 +50,15 @@ class ConvShape(Structure):
 _P = c_void_p
 SIGNATURES = {
     "slx_abi_version": (c_int32, []),
+    "slx_scan_starts_dtype": (c_int32, [POINTER(ScanShape)]),
     "slx_last_error_string": (c_char_p, []),
     "slx_chunk_increment_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 9),
-    "slx_state_passing_fwd": (c_int32, [c_int32] * 4 + [_P] * 6),
+    "slx_state_passing_fwd": (c_int32, [c_int32] * 4 + [_P] * 4 + [c_int32] + [_P] * 2),
     "slx_chunk_scan_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 10),
     "slx_v2x2ssd_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 14),
     "slx_v2x2ssd_bwd_workspace_bytes": (c_size_t, [POINTER(ScanShape)]),
     "slx_chunk_scan_bwd_dz0": (c_int32, [POINTER(ScanShape)] + [_P] * 5),
-    "slx_state_passing_bwd": (c_int32, [c_int32] * 4 + [_P] * 10),
+    "slx_state_passing_bwd": (c_int32, [c_int32] * 4 + [_P] * 3 + [c_int32] + [_P] * 7),
     "slx_chunk_scan_bwd": (c_int32, [POINTER(ScanShape)] + [_P] * 19),
     "slx_v2x2ssd_bwd": (c_int32, [POINTER(ScanShape)] + [_P] * 21 + [c_size_t, _P]),
     "slx_v2x2ssd_bwd_begin": (c_int32, [POINTER(ScanShape)] + [_P] * 6 + [c_size_t, _P]),
@@ -102,6 +103,15 @@ def dtype_code(dt: torch.dtype) -> int:
         return _DTYPE_CODE[dt]
     except KeyError:
         raise TypeError(f"unsupported dtype {dt}; expected float32, bfloat16 or float16") from None
+
+
+_CODE_DTYPE = {v: k for k, v in _DTYPE_CODE.items()}
+
+
+def starts_dtype(shape: "ScanShape") -> torch.dtype:
+    """dtype in which the stages of this shape exchange chunk_starts (the activation dtype where
+    the tensor-core kernels run, fp32 otherwise)."""
+    return _CODE_DTYPE[int(lib().slx_scan_starts_dtype(ctypes.byref(shape)))]
 
 
 def ptr(t: Optional[torch.Tensor]) -> Optional[int]:

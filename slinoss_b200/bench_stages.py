@@ -82,7 +82,8 @@ def scan_stages(b, h, T, P, N, L, dtype):
     s = _lib.ScanShape(BH, T, P, N, L, _lib.dtype_code(dtype))
     f32 = dict(device=dev, dtype=torch.float32)
     inc = torch.empty((b, h, NC, P, D), **f32)
-    starts = torch.empty_like(inc)
+    starts = torch.empty(inc.shape, device=dev, dtype=_lib.starts_dtype(s))
+    sdt = _lib.dtype_code(starts.dtype)
     mch = torch.empty((b, h, NC, 2), **f32)
     final = torch.empty((b, h, P, D), **f32)
     Y = torch.empty_like(U)
@@ -104,16 +105,17 @@ def scan_stages(b, h, T, P, N, L, dtype):
     _emit("chunk_increment_fwd", _time(inc_fn), ht * (es * (P + D) + 24) + state_bytes, 2 * ht * P * D, hbm, tfl, src)
 
     def sp_fn():
-        ck(lib.slx_state_passing_fwd(BH, NC, P, N, inc.data_ptr(), mch.data_ptr(), None, starts.data_ptr(),
+        ck(lib.slx_state_passing_fwd(BH, NC, P, N, inc.data_ptr(), mch.data_ptr(), None, starts.data_ptr(), sdt,
                                      final.data_ptr(), st), "sp")
 
-    _emit("state_passing_fwd", _time(sp_fn), 2 * state_bytes, 0, hbm, tfl, src)
+    starts_bytes = starts.numel() * starts.element_size()
+    _emit("state_passing_fwd", _time(sp_fn), state_bytes + starts_bytes, 0, hbm, tfl, src)
 
     def scan_fn():
         ck(lib.slx_chunk_scan_fwd(byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
                                   starts.data_ptr(), None, None, Y.data_ptr(), st), "scan")
 
-    _emit("chunk_scan_fwd", _time(scan_fn), ht * (es * (2 * P + 2 * D) + 24) + state_bytes,
+    _emit("chunk_scan_fwd", _time(scan_fn), ht * (es * (2 * P + 2 * D) + 24) + starts_bytes,
           ht * (2 * L * (D + P) + 2 * P * D), hbm, tfl, src)
 
     def dz0_fn():
@@ -122,11 +124,11 @@ def scan_stages(b, h, T, P, N, L, dtype):
     _emit("chunk_scan_bwd_dz0", _time(dz0_fn), ht * (es * (P + D) + 8) + state_bytes, 2 * ht * P * D, hbm, tfl, src)
 
     def spb_fn():
-        ck(lib.slx_state_passing_bwd(BH, NC, P, N, dz0.data_ptr(), mch.data_ptr(), starts.data_ptr(),
+        ck(lib.slx_state_passing_bwd(BH, NC, P, N, dz0.data_ptr(), mch.data_ptr(), starts.data_ptr(), sdt,
                                      final.data_ptr(), None, d_inc.data_ptr(), None, zdot.data_ptr(),
                                      part.data_ptr(), st), "spb")
 
-    _emit("state_passing_bwd", _time(spb_fn), 3 * state_bytes, 0, hbm, tfl, src)
+    _emit("state_passing_bwd", _time(spb_fn), 2 * state_bytes + starts_bytes, 0, hbm, tfl, src)
 
     def bwd_fn():
         ck(lib.slx_chunk_scan_bwd(byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(), None,
@@ -134,7 +136,7 @@ def scan_stages(b, h, T, P, N, L, dtype):
                                   dU.data_ptr(), dM.data_ptr(), dK.data_ptr(), dB.data_ptr(), dC.data_ptr(),
                                   cB.data_ptr(), cU.data_ptr(), st), "bwd")
 
-    _emit("chunk_scan_bwd", _time(bwd_fn), ht * (es * (3 * P + 4 * D) + 48) + 2 * state_bytes,
+    _emit("chunk_scan_bwd", _time(bwd_fn), ht * (es * (3 * P + 4 * D) + 48) + state_bytes + starts_bytes,
           ht * 2 * (2 * L * P + 3 * L * D + 3 * P * D), hbm, tfl, src)
 
 

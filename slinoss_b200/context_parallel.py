@@ -55,7 +55,12 @@ class B200Engine:
     def forward_finish(self, U, M, K, B, C, inc, mch, z_in, Bp, Up, L):
         from .ops.v2x2ssd import chunk_scan_b200, state_passing_b200
 
-        starts, final = state_passing_b200(inc, mch, initial_states=z_in)
+        from . import _lib
+        from .ops.v2x2ssd import _shape
+
+        b, h, T, P = map(int, U.shape)
+        sdt = _lib.starts_dtype(_shape(b, h, T, P, int(B.shape[-1]) // 2, L, U.dtype))
+        starts, final = state_passing_b200(inc, mch, initial_states=z_in, starts_dtype=sdt)
         Y = chunk_scan_b200(U, M, K, B, C, starts, B_prev=Bp, U_prev=Up, chunk_size=L)
         return Y, starts, final
 

@@ -138,6 +138,10 @@ static bool tc_eligible(const ScanDims &d, int dtype) {
          d.D >= 64 && d.D <= 256;
 }
 
+// dtype of the chunk-start states between the stages: the activation dtype on the tensor-core
+// path (those kernels round Z0 to it anyway; half the bytes of fp32), fp32 otherwise
+static int starts_dtype_of(const ScanDims &d, int dtype) { return tc_eligible(d, dtype) ? dtype : (int)SLX_F32; }
+
 template <typename T>
 static int launch_scan_fwd_tc(const ScanDims &d, const void *U, const float *M, const float *K, const void *B,
                               const void *C, const float *starts, const float *Bprev, const float *Uprev, void *Y,
@@ -173,19 +177,28 @@ static int launch_scan_bwd_tc(const ScanDims &d, const ScanBwdArgs<T> &a, cudaSt
   return check_launch("chunk_scan_bwd_tc");
 }
 
-static int launch_state_fwd(int BH, int NC, int P, int N, const float *inc, const float *m_chunk, const float *init,
-                            float *starts, float *final_state, cudaStream_t st) {
+template <typename ST>
+static int launch_state_fwd_t(int BH, int NC, int P, int N, const float *inc, const float *m_chunk, const float *init,
+                              ST *starts, float *final_state, cudaStream_t st) {
   const int elems = P * 2 * N;
   if (elems % 4 == 0) {
     int nv = elems / 4;
-    state_passing_fwd_kernel<4><<<dim3((nv + 255) / 256, BH), 256, 0, st>>>(inc, m_chunk, init, starts, final_state,
-                                                                          NC, nv);
+    state_passing_fwd_kernel<4, ST><<<dim3((nv + 255) / 256, BH), 256, 0, st>>>(inc, m_chunk, init, starts,
+                                                                              final_state, NC, nv);
   } else {
     int nv = elems / 2;
-    state_passing_fwd_kernel<2><<<dim3((nv + 255) / 256, BH), 256, 0, st>>>(inc, m_chunk, init, starts, final_state,
-                                                                          NC, nv);
+    state_passing_fwd_kernel<2, ST><<<dim3((nv + 255) / 256, BH), 256, 0, st>>>(inc, m_chunk, init, starts,
+                                                                              final_state, NC, nv);
   }
   return check_launch("state_passing_fwd");
+}
+static int launch_state_fwd(int BH, int NC, int P, int N, const float *inc, const float *m_chunk, const float *init,
+                            void *starts, int starts_dtype, float *final_state, cudaStream_t st) {
+  if (starts_dtype == SLX_BF16)
+    return launch_state_fwd_t<__nv_bfloat16>(BH, NC, P, N, inc, m_chunk, init, (__nv_bfloat16 *)starts, final_state, st);
+  if (starts_dtype == SLX_F16)
+    return launch_state_fwd_t<__half>(BH, NC, P, N, inc, m_chunk, init, (__half *)starts, final_state, st);
+  return launch_state_fwd_t<float>(BH, NC, P, N, inc, m_chunk, init, (float *)starts, final_state, st);
 }
 
 static int state_bwd_blocks(int P, int N) {
@@ -194,23 +207,36 @@ static int state_bwd_blocks(int P, int N) {
   return (nv + 255) / 256;
 }
 
-static int launch_state_bwd(int BH, int NC, int P, int N, const float *dZ0, const float *m_chunk, const float *starts,
-                            const float *final_state, const float *d_final, float *d_inc, float *d_initial,
-                            float *zdot, float *partials, cudaStream_t st) {
+template <typename ST>
+static int launch_state_bwd_t(int BH, int NC, int P, int N, const float *dZ0, const float *m_chunk, const ST *starts,
+                              const float *final_state, const float *d_final, float *d_inc, float *d_initial,
+                              float *zdot, float *partials, cudaStream_t st) {
   const int elems = P * 2 * N;
   const int nblk = state_bwd_blocks(P, N);
   if (elems % 4 == 0) {
-    state_passing_bwd_kernel<4><<<dim3(nblk, BH), 256, 0, st>>>(dZ0, m_chunk, starts, final_state, d_final, d_inc,
-                                                               d_initial, partials, NC, elems / 4);
+    state_passing_bwd_kernel<4, ST><<<dim3(nblk, BH), 256, 0, st>>>(dZ0, m_chunk, starts, final_state, d_final, d_inc,
+                                                                   d_initial, partials, NC, elems / 4);
   } else {
-    state_passing_bwd_kernel<2><<<dim3(nblk, BH), 256, 0, st>>>(dZ0, m_chunk, starts, final_state, d_final, d_inc,
-                                                               d_initial, partials, NC, elems / 2);
+    state_passing_bwd_kernel<2, ST><<<dim3(nblk, BH), 256, 0, st>>>(dZ0, m_chunk, starts, final_state, d_final, d_inc,
+                                                                   d_initial, partials, NC, elems / 2);
   }
   int rc = check_launch("state_passing_bwd");
   if (rc || partials == nullptr) return rc;
   int rows = BH * NC;
   zdot_reduce_kernel<<<(rows + 255) / 256, 256, 0, st>>>(partials, zdot, rows, nblk);
   return check_launch("zdot_reduce");
+}
+static int launch_state_bwd(int BH, int NC, int P, int N, const float *dZ0, const float *m_chunk, const void *starts,
+                            int starts_dtype, const float *final_state, const float *d_final, float *d_inc,
+                            float *d_initial, float *zdot, float *partials, cudaStream_t st) {
+  if (starts_dtype == SLX_BF16)
+    return launch_state_bwd_t<__nv_bfloat16>(BH, NC, P, N, dZ0, m_chunk, (const __nv_bfloat16 *)starts, final_state,
+                                             d_final, d_inc, d_initial, zdot, partials, st);
+  if (starts_dtype == SLX_F16)
+    return launch_state_bwd_t<__half>(BH, NC, P, N, dZ0, m_chunk, (const __half *)starts, final_state, d_final, d_inc,
+                                      d_initial, zdot, partials, st);
+  return launch_state_bwd_t<float>(BH, NC, P, N, dZ0, m_chunk, (const float *)starts, final_state, d_final, d_inc,
+                                   d_initial, zdot, partials, st);
 }
 
 // workspace layout of the backward (all fp32, 256-byte aligned sections)
@@ -264,6 +290,12 @@ int slx_read_tc_status(int *host_out) {
   if (e != cudaSuccess) return fail((int)e, "read_tc_status: %s", cudaGetErrorString(e));
   return SLX_OK;
 }
+int slx_scan_starts_dtype(const slx_scan_shape *s) {
+  ScanDims d;
+  if (check_shape(s, &d)) return SLX_F32;
+  return starts_dtype_of(d, s->dtype);
+}
+
 int slx_read_scan_status(int *host_out) {
   SLX_REQUIRE(host_out != nullptr, SLX_E_NULL, "read_scan_status: NULL pointer");
   int zero = 0;
@@ -293,16 +325,22 @@ int slx_chunk_increment_fwd(const slx_scan_shape *s, const void *U, const float 
 }
 
 int slx_state_passing_fwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const float *inc, const float *m_chunk,
-                          const float *initial_states, float *chunk_starts, float *final_state, void *stream) {
+                          const float *initial_states, void *chunk_starts, int32_t starts_dtype, float *final_state,
+                          void *stream) {
   SLX_REQUIRE(BH > 0 && NC > 0 && P > 0 && N > 0, SLX_E_SHAPE, "state_passing_fwd: sizes must be positive");
   SLX_REQUIRE(BH <= 65535, SLX_E_UNSUPPORTED, "batch_heads=%d exceeds 65535", BH);
   SLX_REQUIRE(inc && m_chunk && final_state, SLX_E_NULL, "state_passing_fwd: NULL tensor");
   SLX_REQUIRE_ALIGNED("state_passing_fwd", inc, initial_states, chunk_starts, final_state);
-  return launch_state_fwd(BH, NC, P, N, inc, m_chunk, initial_states, chunk_starts, final_state, as_stream(stream));
+  SLX_REQUIRE(starts_dtype == SLX_F32 || starts_dtype == SLX_BF16 || starts_dtype == SLX_F16, SLX_E_DTYPE,
+              "state_passing_fwd: bad starts_dtype %d", starts_dtype);
+  SLX_REQUIRE(starts_dtype == SLX_F32 || chunk_starts != (void *)inc, SLX_E_UNSUPPORTED,
+              "state_passing_fwd: the in-place pass needs fp32 chunk_starts");
+  return launch_state_fwd(BH, NC, P, N, inc, m_chunk, initial_states, chunk_starts, starts_dtype, final_state,
+                          as_stream(stream));
 }
 
 int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
-                       const void *C, const float *chunk_starts, const float *B_prev, const float *U_prev, void *Y,
+                       const void *C, const void *chunk_starts, const float *B_prev, const float *U_prev, void *Y,
                        void *stream) {
   ScanDims d;
   int rc = check_shape(s, &d);
@@ -312,23 +350,33 @@ int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M, c
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
   if (tc_eligible(d, s->dtype)) {
     if (s->dtype == SLX_BF16)
-      return launch_scan_fwd_tc<__nv_bfloat16>(d, U, M, K, B, C, chunk_starts, B_prev, U_prev, Y, as_stream(stream));
-    return launch_scan_fwd_tc<__half>(d, U, M, K, B, C, chunk_starts, B_prev, U_prev, Y, as_stream(stream));
+      return launch_scan_fwd_tc<__nv_bfloat16>(d, U, M, K, B, C, (const float *)chunk_starts, B_prev, U_prev, Y,
+                                               as_stream(stream));
+    return launch_scan_fwd_tc<__half>(d, U, M, K, B, C, (const float *)chunk_starts, B_prev, U_prev, Y,
+                                      as_stream(stream));
   }
-  SLX_DISPATCH_T(s->dtype, SLX_DISPATCH_L(d.L, rc = (launch_scan_fwd<T_, L_>(d, U, M, K, B, C, chunk_starts, B_prev,
+  SLX_DISPATCH_T(s->dtype, SLX_DISPATCH_L(d.L, rc = (launch_scan_fwd<T_, L_>(d, U, M, K, B, C, (const float *)chunk_starts, B_prev,
                                                                              U_prev, Y, as_stream(stream)))));
   return rc;
 }
 
 int slx_v2x2ssd_fwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
                     const void *C, const float *initial_states, const float *B_prev, const float *U_prev, void *Y,
-                    float *final_state, float *chunk_starts, float *m_chunk, float *increments, void *stream) {
-  float *inc = increments ? increments : chunk_starts;
+                    float *final_state, void *chunk_starts, float *m_chunk, float *increments, void *stream) {
+  ScanDims d0;
+  {
+    int rc0 = check_shape(s, &d0);
+    if (rc0) return rc0;
+  }
+  const int sdt = starts_dtype_of(d0, s->dtype);
+  SLX_REQUIRE(increments != nullptr || sdt == SLX_F32, SLX_E_NULL,
+              "v2x2ssd_fwd: this shape keeps chunk_starts in the activation dtype and needs the increments buffer");
+  float *inc = increments ? increments : (float *)chunk_starts;
   int rc = slx_chunk_increment_fwd(s, U, M, K, B, B_prev, U_prev, inc, m_chunk, stream);
   if (rc) return rc;
   SLX_REQUIRE(final_state != nullptr, SLX_E_NULL, "v2x2ssd_fwd: final_state is NULL");
   const int NC = (s->T + s->chunk - 1) / s->chunk;
-  rc = slx_state_passing_fwd(s->batch_heads, NC, s->P, s->N, inc, m_chunk, initial_states, chunk_starts,
+  rc = slx_state_passing_fwd(s->batch_heads, NC, s->P, s->N, inc, m_chunk, initial_states, chunk_starts, sdt,
                              final_state, stream);
   if (rc) return rc;
   return slx_chunk_scan_fwd(s, U, M, K, B, C, chunk_starts, B_prev, U_prev, Y, stream);
@@ -359,7 +407,8 @@ int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *
 }
 
 int slx_state_passing_bwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const float *dZ0, const float *m_chunk,
-                          const float *chunk_starts, const float *final_state, const float *d_final, float *d_inc,
+                          const void *chunk_starts, int32_t starts_dtype, const float *final_state,
+                          const float *d_final, float *d_inc,
                           float *d_initial, float *zdot, float *zdot_partials, void *stream) {
   SLX_REQUIRE(BH > 0 && NC > 0 && P > 0 && N > 0, SLX_E_SHAPE, "state_passing_bwd: sizes must be positive");
   SLX_REQUIRE(BH <= 65535, SLX_E_UNSUPPORTED, "batch_heads=%d exceeds 65535", BH);
@@ -370,12 +419,15 @@ int slx_state_passing_bwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const fl
   SLX_REQUIRE(zdot == nullptr || (chunk_starts && final_state), SLX_E_NULL,
               "state_passing_bwd: zdot needs chunk_starts and final_state");
   SLX_REQUIRE(d_inc || d_initial, SLX_E_NULL, "state_passing_bwd: neither d_inc nor d_initial asked for");
-  return launch_state_bwd(BH, NC, P, N, dZ0, m_chunk, chunk_starts, final_state, d_final, d_inc, d_initial, zdot,
+  SLX_REQUIRE(starts_dtype == SLX_F32 || starts_dtype == SLX_BF16 || starts_dtype == SLX_F16, SLX_E_DTYPE,
+              "state_passing_bwd: bad starts_dtype %d", starts_dtype);
+  return launch_state_bwd(BH, NC, P, N, dZ0, m_chunk, chunk_starts, starts_dtype, final_state, d_final, d_inc,
+                          d_initial, zdot,
                           zdot_partials, as_stream(stream));
 }
 
 int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
-                       const void *C, const float *B_prev, const float *U_prev, const float *chunk_starts,
+                       const void *C, const float *B_prev, const float *U_prev, const void *chunk_starts,
                        const float *d_inc, const float *zdot, const void *dY, void *dU, float *dM, float *dK,
                        void *dB, void *dC, float *carryB, float *carryU, void *stream) {
   ScanDims d;
@@ -389,7 +441,8 @@ int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M, c
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
   const bool tc = tc_eligible(d, s->dtype);
   SLX_DISPATCH_T(s->dtype, {
-    ScanBwdArgs<T_> a{(const T_ *)U, (const T_ *)B, (const T_ *)C, (const T_ *)dY, M, K, chunk_starts, d_inc, zdot,
+    ScanBwdArgs<T_> a{(const T_ *)U, (const T_ *)B, (const T_ *)C, (const T_ *)dY, M, K, (const float *)chunk_starts,
+                      d_inc, zdot,
                       B_prev, U_prev, (T_ *)dU, (T_ *)dB, (T_ *)dC, dM, dK, carryB, carryU, d};
     if constexpr (!std::is_same<T_, float>::value) {
       if (tc) return launch_scan_bwd_tc<T_>(d, a, as_stream(stream));
@@ -400,7 +453,7 @@ int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M, c
 }
 
 static int v2x2ssd_bwd_impl(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
-                            const void *C, const float *B_prev, const float *U_prev, const float *chunk_starts,
+                            const void *C, const float *B_prev, const float *U_prev, const void *chunk_starts,
                             const float *m_chunk, const float *final_state, const void *dY, const float *d_final,
                             void *dU, float *dM, float *dK, void *dB, void *dC, float *d_initial, float *dB_prev,
                             float *dU_prev, void *workspace, size_t workspace_bytes, void *stream, bool dz0_ready) {
@@ -428,7 +481,8 @@ static int v2x2ssd_bwd_impl(const slx_scan_shape *s, const void *U, const float 
     rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, d_inc, stream);
     if (rc) return rc;
   }
-  rc = launch_state_bwd(d.BH, d.NC, d.P, d.N, d_inc, m_chunk, chunk_starts, final_state, d_final, d_inc, d_initial,
+  rc = launch_state_bwd(d.BH, d.NC, d.P, d.N, d_inc, m_chunk, chunk_starts, starts_dtype_of(d, s->dtype), final_state,
+                        d_final, d_inc, d_initial,
                         zdot, partials, st);
   if (rc) return rc;
   rc = slx_chunk_scan_bwd(s, U, M, K, B, C, B_prev, U_prev, chunk_starts, d_inc, zdot, dY, dU, dM, dK, dB, dC, carryB,
@@ -443,7 +497,7 @@ static int v2x2ssd_bwd_impl(const slx_scan_shape *s, const void *U, const float 
 }
 
 int slx_v2x2ssd_bwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
-                    const void *C, const float *B_prev, const float *U_prev, const float *chunk_starts,
+                    const void *C, const float *B_prev, const float *U_prev, const void *chunk_starts,
                     const float *m_chunk, const float *final_state, const void *dY, const float *d_final, void *dU,
                     float *dM, float *dK, void *dB, void *dC, float *d_initial, float *dB_prev, float *dU_prev,
                     void *workspace, size_t workspace_bytes, void *stream) {
@@ -466,12 +520,12 @@ int slx_v2x2ssd_bwd_begin(const slx_scan_shape *s, const float *M, const void *C
   float *dz0 = reinterpret_cast<float *>(static_cast<char *>(workspace) + w.d_inc);
   rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, dz0, stream);
   if (rc) return rc;
-  return launch_state_bwd(d.BH, d.NC, d.P, d.N, dz0, m_chunk, nullptr, nullptr, nullptr, nullptr,
+  return launch_state_bwd(d.BH, d.NC, d.P, d.N, dz0, m_chunk, nullptr, SLX_F32, nullptr, nullptr, nullptr,
                           d_initial_zero_final, nullptr, nullptr, as_stream(stream));
 }
 
 int slx_v2x2ssd_bwd_finish(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
-                           const void *C, const float *B_prev, const float *U_prev, const float *chunk_starts,
+                           const void *C, const float *B_prev, const float *U_prev, const void *chunk_starts,
                            const float *m_chunk, const float *final_state, const void *dY, const float *d_final,
                            void *dU, float *dM, float *dK, void *dB, void *dC, float *d_initial, float *dB_prev,
                            float *dU_prev, void *workspace, size_t workspace_bytes, void *stream) {

@@ -130,7 +130,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   const int NB = d.D / 64;
   const uint32_t mbar_s = umma::smem_u32(&mbar);
   const int j = tid & 7, r0 = tid >> 3;  // staging: 16-byte chunk j of rows r0 + 32 i
-  const float *z0 = a.starts + ((size_t)bh * d.NC + c) * P * d.D;
+  // on this path the chunk-start states are stored in the activation dtype (api: slx_scan_starts_dtype)
+  const T *z0 = reinterpret_cast<const T *>(a.starts) + ((size_t)bh * d.NC + c) * P * d.D;
   auto prefetch_cb = [&](int sl) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -148,14 +149,12 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  float4 zr[2][2];
+  uint4 zr[2];
   auto prefetch_z = [&](int sl) {
 #pragma unroll
     for (int k2 = 0; k2 < 2; ++k2) {
       const int q = tid + kTcThreads * k2;
-      const float4 *src = reinterpret_cast<const float4 *>(z0 + (size_t)(q >> 3) * d.D + sl * 64 + 8 * (q & 7));
-      zr[k2][0] = src[0];
-      zr[k2][1] = src[1];
+      zr[k2] = *reinterpret_cast<const uint4 *>(z0 + (size_t)(q >> 3) * d.D + sl * 64 + 8 * (q & 7));
     }
   };
   float2 mreg[4];  // the prefix warp's multipliers, requested ahead of the bulk copies
@@ -268,8 +267,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
     for (int k = 0; k < 2; ++k) {
       int q = tid + kTcThreads * k;
       int p = q >> 3, jj = q & 7;
-      float tmp[8] = {zr[k][0].x, zr[k][0].y, zr[k][0].z, zr[k][0].w, zr[k][1].x, zr[k][1].y, zr[k][1].z, zr[k][1].w};
-      *reinterpret_cast<uint4 *>(tZ + umma::swz_off(p, jj)) = pack8<T>(tmp);
+      *reinterpret_cast<uint4 *>(tZ + umma::swz_off(p, jj)) = zr[k];
     }
     // Every thread has consumed its own raw slots (it alone wrote and read them) and its Z0
     // registers: request the next slab now, a whole staging phase ahead of its use.

@@ -81,7 +81,8 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
 #define SLX_STAMP(i) do { if (stamp_on) g_phase_clock[i] = clock64(); } while (0)
   SLX_STAMP(0);
   const int j = tid & 7, r0 = tid >> 3;  // r0 in [0,64)
-  const float *z0 = a.starts + ((size_t)bh * d.NC + c) * P * d.D;
+  // on this path the chunk-start states are stored in the activation dtype (api: slx_scan_starts_dtype)
+  const T *z0 = reinterpret_cast<const T *>(a.starts) + ((size_t)bh * d.NC + c) * P * d.D;
   const float *lam = a.d_inc + ((size_t)bh * d.NC + c) * P * d.D;
   float2 mreg[4];  // the prefix warp's multipliers, requested ahead of the bulk copies
   if (warp == 2) chunk_prefix_load4(a.M + tok0 * 2, valid, mreg);
@@ -123,12 +124,11 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
   prefetch_cb(0);
   // Z0 / Lambda slab (fp32): one 8-float item per thread, prefetched into registers
   const int zp = tid >> 3, zj = tid & 7;
-  float4 zr0, zr1, lr0, lr1;
+  uint4 zr;
+  float4 lr0, lr1;
   auto prefetch_zl = [&](int sl) {
-    const float4 *zs = reinterpret_cast<const float4 *>(z0 + (size_t)zp * d.D + sl * 64 + 8 * zj);
     const float4 *ls = reinterpret_cast<const float4 *>(lam + (size_t)zp * d.D + sl * 64 + 8 * zj);
-    zr0 = zs[0];
-    zr1 = zs[1];
+    zr = *reinterpret_cast<const uint4 *>(z0 + (size_t)zp * d.D + sl * 64 + 8 * zj);
     lr0 = ls[0];
     lr1 = ls[1];
   };

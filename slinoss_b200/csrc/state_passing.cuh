@@ -25,6 +25,38 @@ __device__ __forceinline__ float4 axpy_c(float2 m, float4 z, float4 v) {
   float2 b = axpy_c(m, make_float2(z.z, z.w), make_float2(v.z, v.w));
   return make_float4(a.x, a.y, b.x, b.y);
 }
+// chunk-start states are stored as ST (float, or the activation dtype on the tensor-core path:
+// those kernels round Z0 to it anyway); the recurrence itself stays in fp32 registers
+template <typename ST, int VEC>
+struct alignas(sizeof(ST) * VEC) PackedVec {
+  ST v[VEC];
+};
+template <typename ST>
+__device__ __forceinline__ void st_store(ST *p, float2 v) {
+  PackedVec<ST, 2> q;
+  q.v[0] = from_f<ST>(v.x);
+  q.v[1] = from_f<ST>(v.y);
+  *reinterpret_cast<PackedVec<ST, 2> *>(p) = q;
+}
+template <typename ST>
+__device__ __forceinline__ void st_store(ST *p, float4 v) {
+  PackedVec<ST, 4> q;
+  q.v[0] = from_f<ST>(v.x);
+  q.v[1] = from_f<ST>(v.y);
+  q.v[2] = from_f<ST>(v.z);
+  q.v[3] = from_f<ST>(v.w);
+  *reinterpret_cast<PackedVec<ST, 4> *>(p) = q;
+}
+template <typename ST>
+__device__ __forceinline__ void st_load(const ST *p, float2 &v) {
+  const PackedVec<ST, 2> q = *reinterpret_cast<const PackedVec<ST, 2> *>(p);
+  v = make_float2(to_f(q.v[0]), to_f(q.v[1]));
+}
+template <typename ST>
+__device__ __forceinline__ void st_load(const ST *p, float4 &v) {
+  const PackedVec<ST, 4> q = *reinterpret_cast<const PackedVec<ST, 4> *>(p);
+  v = make_float4(to_f(q.v[0]), to_f(q.v[1]), to_f(q.v[2]), to_f(q.v[3]));
+}
 __device__ __forceinline__ float2 vzero(float2) { return make_float2(0.f, 0.f); }
 __device__ __forceinline__ float4 vzero(float4) { return make_float4(0.f, 0.f, 0.f, 0.f); }
 // sum over the complex lanes of conj(a) * b
@@ -39,9 +71,9 @@ __device__ __forceinline__ float2 cdot(float4 a, float4 b) {
 // coalesced 8/16-byte vector.  `starts` may alias `inc`: each chunk's increment
 // is read before its slot is overwritten.  `starts` may be NULL: only the final state is wanted
 // (the affine offset of a segment in the context-parallel chain), and the pass writes nothing else.
-template <int VEC>
+template <int VEC, typename ST>
 __global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc, const float *__restrict__ m_chunk,
-                                                                const float *__restrict__ init, float *starts,
+                                                                const float *__restrict__ init, ST *starts,
                                                                 float *__restrict__ final_state, int NC,
                                                                 int n_vec /* P*D/VEC */) {
   using V = typename VecT<VEC>::type;
@@ -50,7 +82,8 @@ __global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc
   if (i >= n_vec) return;
   const size_t per = (size_t)n_vec;
   const V *incv = reinterpret_cast<const V *>(inc) + (size_t)bh * NC * per + i;
-  V *stv = starts ? reinterpret_cast<V *>(starts) + (size_t)bh * NC * per + i : nullptr;
+  ST *stv = starts ? starts + ((size_t)bh * NC * per + i) * VEC : nullptr;  // + c * per * VEC per chunk
+  const size_t cs = per * VEC;
   const float2 *mc = reinterpret_cast<const float2 *>(m_chunk) + (size_t)bh * NC;
   V z = init ? reinterpret_cast<const V *>(init)[(size_t)bh * per + i] : vzero(V());
   int c = 0;
@@ -58,19 +91,19 @@ __global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc
     V v0 = incv[(size_t)(c + 0) * per], v1 = incv[(size_t)(c + 1) * per];
     V v2 = incv[(size_t)(c + 2) * per], v3 = incv[(size_t)(c + 3) * per];
     float2 m0 = mc[c], m1 = mc[c + 1], m2 = mc[c + 2], m3 = mc[c + 3];
-    if (stv) stv[(size_t)(c + 0) * per] = z;
+    if (stv) st_store<ST>(stv + (size_t)(c + 0) * cs, z);
     z = axpy_c(m0, z, v0);
-    if (stv) stv[(size_t)(c + 1) * per] = z;
+    if (stv) st_store<ST>(stv + (size_t)(c + 1) * cs, z);
     z = axpy_c(m1, z, v1);
-    if (stv) stv[(size_t)(c + 2) * per] = z;
+    if (stv) st_store<ST>(stv + (size_t)(c + 2) * cs, z);
     z = axpy_c(m2, z, v2);
-    if (stv) stv[(size_t)(c + 3) * per] = z;
+    if (stv) st_store<ST>(stv + (size_t)(c + 3) * cs, z);
     z = axpy_c(m3, z, v3);
   }
   for (; c < NC; ++c) {
     V v = incv[(size_t)c * per];
     float2 m = mc[c];
-    if (stv) stv[(size_t)c * per] = z;
+    if (stv) st_store<ST>(stv + (size_t)c * cs, z);
     z = axpy_c(m, z, v);
   }
   reinterpret_cast<V *>(final_state)[(size_t)bh * per + i] = z;
@@ -82,9 +115,9 @@ __global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc
 // d_initial = g.  d_inc may alias dZ0.  With zdot_partials == NULL the dot products (and the reads
 // of starts / final_state) are skipped, with d_inc == NULL nothing but d_initial is written: that
 // is the reduce-only pass that gives a segment's d_initial for a zero d_final.
-template <int VEC>
+template <int VEC, typename ST>
 __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0, const float *__restrict__ m_chunk,
-                                                                const float *__restrict__ starts,
+                                                                const ST *__restrict__ starts,
                                                                 const float *__restrict__ final_state,
                                                                 const float *__restrict__ d_final, float *d_inc,
                                                                 float *__restrict__ d_initial,
@@ -123,14 +156,16 @@ __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0
     if (d_initial && live) reinterpret_cast<V *>(d_initial)[(size_t)bh * per + iv] = g0;
     return;
   }
-  const V *stv = reinterpret_cast<const V *>(starts) + (size_t)bh * NC * per + iv;
+  const ST *stv = starts + ((size_t)bh * NC * per + iv) * VEC;
+  const size_t cs = per * VEC;
   const float2 *mc = reinterpret_cast<const float2 *>(m_chunk) + (size_t)bh * NC;
   V g = (d_final && live) ? reinterpret_cast<const V *>(d_final)[(size_t)bh * per + iv] : vzero(V());
   V endst = reinterpret_cast<const V *>(final_state)[(size_t)bh * per + iv];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int c = NC - 1; c >= 0; --c) {
     V dz = dzv[(size_t)c * per];
-    V st = stv[(size_t)c * per];  // start of chunk c = end state of chunk c-1 (next iteration)
+    V st;  // start of chunk c = end state of chunk c-1 (next iteration)
+    st_load<ST>(stv + (size_t)c * cs, st);
     float2 m = mc[c];
     float2 part = live ? cdot(endst, g) : make_float2(0.f, 0.f);
 #pragma unroll

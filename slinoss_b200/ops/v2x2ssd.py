@@ -152,17 +152,20 @@ def chunk_increment_b200(U, M, K, B, *, B_prev=None, U_prev=None, chunk_size: in
     return inc, mch
 
 
-def state_passing_b200(inc, m_chunk, *, initial_states=None, want_starts: bool = True):
-    """Stage 2 -> ``(chunk_starts, final_state)`` fp32.  ``want_starts=False`` returns
-    ``(None, final_state)`` and writes nothing but the final state (half the traffic)."""
+def state_passing_b200(inc, m_chunk, *, initial_states=None, want_starts: bool = True,
+                       starts_dtype: torch.dtype = torch.float32):
+    """Stage 2 -> ``(chunk_starts, final_state)``.  The recurrence and ``final_state`` are fp32;
+    ``chunk_starts`` is stored as ``starts_dtype`` (fp32 like the reference by default; the fused
+    op uses the activation dtype where the tensor-core kernels run).  ``want_starts=False``
+    returns ``(None, final_state)`` and writes nothing but the final state (half the traffic)."""
     _require_cuda(inc, m_chunk, initial_states)
     b, h, NC, P, D = map(int, inc.shape)
     init = _f32(initial_states)
-    starts = torch.empty_like(inc) if want_starts else None
+    starts = torch.empty(inc.shape, device=inc.device, dtype=starts_dtype) if want_starts else None
     final = torch.empty((b, h, P, D), device=inc.device, dtype=torch.float32)
     _lib.check(_lib.lib().slx_state_passing_fwd(
         b * h, NC, P, D // 2, inc.data_ptr(), m_chunk.data_ptr(), _lib.ptr(init), _lib.ptr(starts),
-        final.data_ptr(), _lib.stream_ptr(inc.device)), "state_passing")
+        _lib.dtype_code(starts_dtype), final.data_ptr(), _lib.stream_ptr(inc.device)), "state_passing")
     return starts, final
 
 
@@ -172,6 +175,7 @@ def chunk_scan_b200(U, M, K, B, C, chunk_starts, *, B_prev=None, U_prev=None, ch
     b, h, T, P = map(int, U.shape)
     D = int(B.shape[-1])
     s = _shape(b, h, T, P, D // 2, int(chunk_size), U.dtype)
+    chunk_starts = _as_starts(chunk_starts, s)
     Y = torch.empty_like(U)
     bp, up = _f32(B_prev), _f32(U_prev)
     _lib.check(_lib.lib().slx_chunk_scan_fwd(
@@ -179,6 +183,13 @@ def chunk_scan_b200(U, M, K, B, C, chunk_starts, *, B_prev=None, U_prev=None, ch
         chunk_starts.data_ptr(), _lib.ptr(bp), _lib.ptr(up), Y.data_ptr(), _lib.stream_ptr(U.device)),
         "chunk_scan")
     return Y
+
+
+def _as_starts(chunk_starts: torch.Tensor, s: "_lib.ScanShape") -> torch.Tensor:
+    """chunk_starts in the dtype the kernels of this shape exchange it in (a conversion pass only
+    when the caller's tensor is in another dtype, e.g. fp32 starts from the stage-level API)."""
+    want = _lib.starts_dtype(s)
+    return chunk_starts if chunk_starts.dtype == want else chunk_starts.to(want)
 
 
 def _fwd_impl(U, M, K, B, C, init32, bp32, up32, L):
@@ -190,9 +201,10 @@ def _fwd_impl(U, M, K, B, C, init32, bp32, up32, L):
     dev = U.device
     Y = torch.empty_like(U)
     final = torch.empty((b, h, P, D), device=dev, dtype=torch.float32)
-    starts = torch.empty((b, h, NC, P, D), device=dev, dtype=torch.float32)
+    starts = torch.empty((b, h, NC, P, D), device=dev, dtype=_lib.starts_dtype(s))
     mch = torch.empty((b, h, NC, 2), device=dev, dtype=torch.float32)
-    inc = torch.empty_like(starts)  # separate increment buffer: the two-buffer state pass is ~2.5x faster
+    # separate fp32 increment buffer: the two-buffer state pass is ~2.5x faster than the in-place one
+    inc = torch.empty((b, h, NC, P, D), device=dev, dtype=torch.float32)
     _lib.check(_lib.lib().slx_v2x2ssd_fwd(
         byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
         _lib.ptr(init32), _lib.ptr(bp32), _lib.ptr(up32), Y.data_ptr(), final.data_ptr(),
@@ -231,6 +243,7 @@ def _bwd_impl(U, M, K, B, C, bp32, up32, starts, mch, final32, dY, d_final32, L,
     dUp = torch.empty((b, h, P), device=dev, dtype=torch.float32) if want_prev else None
     L_ = _lib.lib()
     nbytes = int(L_.slx_v2x2ssd_bwd_workspace_bytes(byref(s)))
+    starts = _as_starts(starts, s)
     ws = torch.empty((nbytes,), device=dev, dtype=torch.uint8) if workspace is None else workspace
     entry = L_.slx_v2x2ssd_bwd if workspace is None else L_.slx_v2x2ssd_bwd_finish  # dZ0 already there
     _lib.check(entry(
@@ -247,7 +260,7 @@ class _V2x2SSDFn(torch.autograd.Function):
     ``_V2x2SSDCuTeTrainingFn`` (cute/autograd.py:40-266)."""
 
     @staticmethod
-    def forward(ctx, U, M, K, B, C, initial_states, B_prev, U_prev, L, odtype, return_state, residual="fp32"):
+    def forward(ctx, U, M, K, B, C, initial_states, B_prev, U_prev, L, odtype, return_state, residual="keep"):
         init32, bp32, up32 = _f32(initial_states), _f32(B_prev), _f32(U_prev)
         Y, final32, starts, mch = _fwd_impl(U.detach(), M.detach(), K.detach(), B.detach(),
                                             C.detach(), init32, bp32, up32, L)
@@ -257,14 +270,12 @@ class _V2x2SSDFn(torch.autograd.Function):
         ctx.has_prev = B_prev is not None
         ctx.init_dtype = None if initial_states is None else initial_states.dtype
         ctx.prev_dtype = None if B_prev is None else B_prev.dtype
-        # What is kept of the chunk-start states (the largest residual, (b,h,NC,P,2N) fp32):
-        # "fp32" as computed; "half" rounded to the activation dtype (half the bytes; the tensor-core
-        # kernels round Z0 to that dtype anyway); "recompute" nothing: the backward rebuilds them
-        # from the inputs with one more chunk-increment and state pass.
+        # What is kept of the chunk-start states (the largest residual, (b,h,NC,P,2N)): "keep" as the
+        # kernels exchange them (activation dtype on the tensor-core path, fp32 otherwise);
+        # "recompute" nothing: the backward rebuilds them from the inputs with one more
+        # chunk-increment and state pass.
         ctx.residual = residual
-        if residual == "half" and U.dtype != torch.float32:
-            starts = starts.to(U.dtype)
-        elif residual == "recompute":
+        if residual == "recompute":
             starts = init32 if init32 is not None else final32.new_empty(0)
         saved = [U, M, K, B, C, mch, starts, final32]
         if ctx.has_prev:
@@ -293,11 +304,11 @@ class _V2x2SSDFn(torch.autograd.Function):
             dfin = None if d_final is None else d_final.to(torch.float32).contiguous()
             if ctx.residual == "recompute":
                 init32 = starts if starts.numel() else None
+                b_, h_, T_, P_ = map(int, U.shape)
+                sdt = _lib.starts_dtype(_shape(b_, h_, T_, P_, int(B.shape[-1]) // 2, ctx.L, U.dtype))
                 inc, _ = chunk_increment_b200(U, M, K, B, B_prev=bp32, U_prev=up32, chunk_size=ctx.L)
-                starts, _ = state_passing_b200(inc, mch, initial_states=init32)
+                starts, _ = state_passing_b200(inc, mch, initial_states=init32, starts_dtype=sdt)
                 del inc
-            elif starts.dtype != torch.float32:
-                starts = starts.to(torch.float32)
             dU, dM, dK, dB, dC, d_init, dBp, dUp = _bwd_impl(
                 U, M, K, B, C, bp32, up32, starts, mch, final32, dYc, dfin, ctx.L,
                 want_initial=ctx.has_init, want_prev=ctx.has_prev)
@@ -320,7 +331,7 @@ class _V2x2SSDFn(torch.autograd.Function):
 def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=None, U_prev=None,
                  compute_dtype: Optional[torch.dtype] = None,
                  output_dtype: Optional[torch.dtype] = None, return_state: bool = False,
-                 retile: bool = True, strict: bool = False, residual: str = "fp32"):
+                 retile: bool = True, strict: bool = False, residual: str = "keep"):
     """Drop-in for ``v2x2ssd_cute`` (cute/api.py:52): returns ``Y`` or
     ``(Y, final_state, B_last, U_last)``; differentiable in all eight inputs.
 
@@ -336,13 +347,13 @@ def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=
     forward (one device synchronisation per call) and raises like the reference.
 
     ``residual`` chooses what autograd keeps of the chunk-start states, the largest residual
-    ((batch, heads, chunks, P, 2N) fp32, which the reference saves as is, cute/autograd.py:98):
-    ``"fp32"`` (default), ``"half"`` (rounded to the activation dtype: half the bytes, one
-    conversion pass each way) or ``"recompute"`` (nothing kept; the backward rebuilds them with
-    one more chunk-increment and state pass).
+    ((batch, heads, chunks, P, 2N); the reference saves it in fp32, cute/autograd.py:98):
+    ``"keep"`` (default) as the kernels exchange it (activation dtype on the tensor-core path,
+    fp32 otherwise) or ``"recompute"`` (nothing kept; the backward rebuilds it with one more
+    chunk-increment and state pass, bitwise the same gradients).
     """
-    if residual not in ("fp32", "half", "recompute"):
-        raise ValueError(f"residual must be 'fp32', 'half' or 'recompute'. Got {residual!r}.")
+    if residual not in ("keep", "recompute"):
+        raise ValueError(f"residual must be 'keep' or 'recompute'. Got {residual!r}.")
     b, h, T, N, P = _validate_inputs(U, M, K, B, C, initial_states, B_prev, U_prev)
     if U.device.type != "cuda":
         raise ValueError("slinoss_b200 v2x2ssd requires CUDA tensors.")
