@@ -427,15 +427,17 @@ def main() -> int:
                                        C.data_ptr(), None, None, None, Y.data_ptr(), final.data_ptr(),
                                        starts.data_ptr(), mch.data_ptr(), inc_buf.data_ptr(), st), "fwd")
         del inc_buf
-        d_inc = torch.empty((b, h, NC, P, D), **f32)
+        dz0 = torch.empty((b, h, NC, P, D), **f32)
+        d_inc = torch.empty((b, h, NC, P, D), device=dev, dtype=starts.dtype)
         zdot = torch.empty((b, h, NC, 2), **f32)
         part = torch.empty((BH * NC * 2 * 64,), **f32)
         _lib.check(lib.slx_chunk_scan_bwd_dz0(byref(shape), M.data_ptr(), C.data_ptr(), dY.data_ptr(),
-                                              d_inc.data_ptr(), st), "dz0")
-        _lib.check(lib.slx_state_passing_bwd(BH, NC, P, N, d_inc.data_ptr(), mch.data_ptr(), starts.data_ptr(),
+                                              dz0.data_ptr(), st), "dz0")
+        _lib.check(lib.slx_state_passing_bwd(BH, NC, P, N, dz0.data_ptr(), mch.data_ptr(), starts.data_ptr(),
                                              _lib.dtype_code(starts.dtype), final.data_ptr(), None,
                                              d_inc.data_ptr(), None, zdot.data_ptr(),
                                              part.data_ptr(), st), "state bwd")
+        del dz0
         dU, dB, dC = torch.empty_like(U), torch.empty_like(B), torch.empty_like(C)
         dM, dK = torch.empty_like(M), torch.empty_like(Kt)
         cB, cU = torch.empty((b, h, NC, D), **f32), torch.empty((b, h, NC, P), **f32)

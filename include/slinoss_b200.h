@@ -19,9 +19,10 @@
  *   K        (BH, T, 2, 2)     fp32, tap 0 = prev, tap 1 = curr, each (re,im)
  *   states   (BH, P, 2N)       fp32 interleaved complex
  *   chunk tensors (BH, NC, P, 2N) / (BH, NC, 2), NC = ceil(T / chunk), fp32;
- *            chunk_starts alone is stored in slx_scan_starts_dtype(shape): the
- *            activation dtype where the tensor-core kernels run (they round it
- *            to that dtype anyway), fp32 otherwise
+ *            chunk_starts and d_inc (its gradient-side counterpart) are stored
+ *            in slx_scan_starts_dtype(shape): the activation dtype where the
+ *            tensor-core kernels run (they round both to that dtype for their
+ *            products anyway), fp32 otherwise
  * Tokens past T in the last chunk behave as M=1, K=U=B=C=0
  * (reference.py:541-667).  Nullable pointers are marked [opt].
  * The scan entry points read and write with 16-byte accesses: every tensor
@@ -62,7 +63,7 @@ typedef struct {
 
 int slx_abi_version(void);
 
-/* slx_dtype in which the stages of this shape exchange chunk_starts. */
+/* slx_dtype in which the stages of this shape exchange chunk_starts and d_inc. */
 int slx_scan_starts_dtype(const slx_scan_shape *s);
 const char *slx_last_error_string(void);
 
@@ -121,17 +122,18 @@ int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *
                            const void *dY, float *dZ0, void *stream);
 
 /* Reverse recurrence over chunks (cute/kernels/bwd/state_passing/state.py:119
- * and m.py:83 fused): on return d_inc[c] = dL/d(end state of chunk c) (it may
- * alias dZ0), d_initial = dL/d(initial state), and zdot (BH,NC,2) holds
- * sum_{p,n} conj(end_state_c) * d_inc[c], the chunk-level term of dM.
- * final_state is the forward's fp32 final state.
+ * and m.py:83 fused): on return d_inc[c] = dL/d(end state of chunk c), stored as
+ * starts_dtype (with SLX_F32 it may alias dZ0), d_initial = dL/d(initial state),
+ * and zdot (BH,NC,2) holds sum_{p,n} conj(end_state_c) * d_inc[c] (from the fp32
+ * values), the chunk-level term of dM.  final_state is the forward's fp32 final
+ * state; chunk_starts is read as starts_dtype.
  * zdot and zdot_partials NULL: no dot products (chunk_starts and final_state are
  * then not read).  d_inc NULL as well: only d_initial is written. */
 int slx_state_passing_bwd(int32_t batch_heads, int32_t n_chunks, int32_t P,
                           int32_t N, const float *dZ0, const float *m_chunk,
                           const void *chunk_starts /*[opt]*/, int32_t starts_dtype,
                           const float *final_state /*[opt]*/,
-                          const float *d_final /*[opt]*/, float *d_inc /*[opt]*/,
+                          const float *d_final /*[opt]*/, void *d_inc /*[opt]*/,
                           float *d_initial /*[opt]*/, float *zdot /*[opt]*/,
                           float *zdot_partials /* workspace, [opt] */, void *stream);
 
@@ -145,7 +147,7 @@ int slx_state_passing_bwd(int32_t batch_heads, int32_t n_chunks, int32_t P,
 int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M,
                        const float *K, const void *B, const void *C,
                        const float *B_prev /*[opt]*/, const float *U_prev /*[opt]*/,
-                       const void *chunk_starts, const float *d_inc,
+                       const void *chunk_starts, const void *d_inc,
                        const float *zdot, const void *dY, void *dU, float *dM,
                        float *dK, void *dB, void *dC, float *carryB,
                        float *carryU, void *stream);

@@ -88,7 +88,7 @@ def scan_stages(b, h, T, P, N, L, dtype):
     final = torch.empty((b, h, P, D), **f32)
     Y = torch.empty_like(U)
     dz0 = torch.empty_like(inc)
-    d_inc = torch.empty_like(inc)
+    d_inc = torch.empty_like(starts)
     zdot = torch.empty((b, h, NC, 2), **f32)
     part = torch.empty((BH * NC * 2 * 64,), **f32)
     dU, dB, dC = torch.empty_like(U), torch.empty_like(B), torch.empty_like(C)
@@ -128,7 +128,7 @@ def scan_stages(b, h, T, P, N, L, dtype):
                                      final.data_ptr(), None, d_inc.data_ptr(), None, zdot.data_ptr(),
                                      part.data_ptr(), st), "spb")
 
-    _emit("state_passing_bwd", _time(spb_fn), 2 * state_bytes + starts_bytes, 0, hbm, tfl, src)
+    _emit("state_passing_bwd", _time(spb_fn), state_bytes + 2 * starts_bytes, 0, hbm, tfl, src)
 
     def bwd_fn():
         ck(lib.slx_chunk_scan_bwd(byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(), None,
@@ -136,7 +136,7 @@ def scan_stages(b, h, T, P, N, L, dtype):
                                   dU.data_ptr(), dM.data_ptr(), dK.data_ptr(), dB.data_ptr(), dC.data_ptr(),
                                   cB.data_ptr(), cU.data_ptr(), st), "bwd")
 
-    _emit("chunk_scan_bwd", _time(bwd_fn), ht * (es * (3 * P + 4 * D) + 48) + state_bytes + starts_bytes,
+    _emit("chunk_scan_bwd", _time(bwd_fn), ht * (es * (3 * P + 4 * D) + 48) + 2 * starts_bytes,
           ht * 2 * (2 * L * P + 3 * L * D + 3 * P * D), hbm, tfl, src)
 
 

@@ -209,7 +209,7 @@ static int state_bwd_blocks(int P, int N) {
 
 template <typename ST>
 static int launch_state_bwd_t(int BH, int NC, int P, int N, const float *dZ0, const float *m_chunk, const ST *starts,
-                              const float *final_state, const float *d_final, float *d_inc, float *d_initial,
+                              const float *final_state, const float *d_final, ST *d_inc, float *d_initial,
                               float *zdot, float *partials, cudaStream_t st) {
   const int elems = P * 2 * N;
   const int nblk = state_bwd_blocks(P, N);
@@ -227,28 +227,35 @@ static int launch_state_bwd_t(int BH, int NC, int P, int N, const float *dZ0, co
   return check_launch("zdot_reduce");
 }
 static int launch_state_bwd(int BH, int NC, int P, int N, const float *dZ0, const float *m_chunk, const void *starts,
-                            int starts_dtype, const float *final_state, const float *d_final, float *d_inc,
+                            int starts_dtype, const float *final_state, const float *d_final, void *d_inc,
                             float *d_initial, float *zdot, float *partials, cudaStream_t st) {
   if (starts_dtype == SLX_BF16)
     return launch_state_bwd_t<__nv_bfloat16>(BH, NC, P, N, dZ0, m_chunk, (const __nv_bfloat16 *)starts, final_state,
-                                             d_final, d_inc, d_initial, zdot, partials, st);
+                                             d_final, (__nv_bfloat16 *)d_inc, d_initial, zdot, partials, st);
   if (starts_dtype == SLX_F16)
-    return launch_state_bwd_t<__half>(BH, NC, P, N, dZ0, m_chunk, (const __half *)starts, final_state, d_final, d_inc,
-                                      d_initial, zdot, partials, st);
-  return launch_state_bwd_t<float>(BH, NC, P, N, dZ0, m_chunk, (const float *)starts, final_state, d_final, d_inc,
-                                   d_initial, zdot, partials, st);
+    return launch_state_bwd_t<__half>(BH, NC, P, N, dZ0, m_chunk, (const __half *)starts, final_state, d_final,
+                                      (__half *)d_inc, d_initial, zdot, partials, st);
+  return launch_state_bwd_t<float>(BH, NC, P, N, dZ0, m_chunk, (const float *)starts, final_state, d_final,
+                                   (float *)d_inc, d_initial, zdot, partials, st);
 }
 
 // workspace layout of the backward (all fp32, 256-byte aligned sections)
 struct BwdWs {
-  size_t d_inc, zdot, partials, carryB, carryU, total;
+  size_t d_inc, dz0, zdot, partials, carryB, carryU, total;  // dz0 == d_inc where the reverse pass runs in place
 };
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
-static BwdWs bwd_ws(const ScanDims &d) {
+static BwdWs bwd_ws(const ScanDims &d, int dtype) {
   BwdWs w;
   size_t off = 0;
-  w.d_inc = off;
-  off += align256(sizeof(float) * (size_t)d.BH * d.NC * d.P * d.D);
+  const size_t n_state = (size_t)d.BH * d.NC * d.P * d.D;
+  w.dz0 = off;
+  off += align256(sizeof(float) * n_state);
+  if (starts_dtype_of(d, dtype) == SLX_F32) {
+    w.d_inc = w.dz0;  // fp32 d_inc overwrites dZ0 chunk by chunk
+  } else {
+    w.d_inc = off;  // d_inc in the activation dtype next to the fp32 dZ0
+    off += align256(2 * n_state);
+  }
   w.zdot = off;
   off += align256(sizeof(float) * (size_t)d.BH * d.NC * 2);
   w.partials = off;
@@ -385,7 +392,7 @@ int slx_v2x2ssd_fwd(const slx_scan_shape *s, const void *U, const float *M, cons
 size_t slx_v2x2ssd_bwd_workspace_bytes(const slx_scan_shape *s) {
   ScanDims d;
   if (check_shape(s, &d)) return 0;
-  return bwd_ws(d).total;
+  return bwd_ws(d, s->dtype).total;
 }
 
 int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *C, const void *dY, float *dZ0,
@@ -408,7 +415,7 @@ int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *
 
 int slx_state_passing_bwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const float *dZ0, const float *m_chunk,
                           const void *chunk_starts, int32_t starts_dtype, const float *final_state,
-                          const float *d_final, float *d_inc,
+                          const float *d_final, void *d_inc,
                           float *d_initial, float *zdot, float *zdot_partials, void *stream) {
   SLX_REQUIRE(BH > 0 && NC > 0 && P > 0 && N > 0, SLX_E_SHAPE, "state_passing_bwd: sizes must be positive");
   SLX_REQUIRE(BH <= 65535, SLX_E_UNSUPPORTED, "batch_heads=%d exceeds 65535", BH);
@@ -419,6 +426,8 @@ int slx_state_passing_bwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const fl
   SLX_REQUIRE(zdot == nullptr || (chunk_starts && final_state), SLX_E_NULL,
               "state_passing_bwd: zdot needs chunk_starts and final_state");
   SLX_REQUIRE(d_inc || d_initial, SLX_E_NULL, "state_passing_bwd: neither d_inc nor d_initial asked for");
+  SLX_REQUIRE(starts_dtype == SLX_F32 || d_inc != (const void *)dZ0, SLX_E_UNSUPPORTED,
+              "state_passing_bwd: the in-place pass needs fp32 d_inc");
   SLX_REQUIRE(starts_dtype == SLX_F32 || starts_dtype == SLX_BF16 || starts_dtype == SLX_F16, SLX_E_DTYPE,
               "state_passing_bwd: bad starts_dtype %d", starts_dtype);
   return launch_state_bwd(BH, NC, P, N, dZ0, m_chunk, chunk_starts, starts_dtype, final_state, d_final, d_inc,
@@ -428,7 +437,7 @@ int slx_state_passing_bwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const fl
 
 int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
                        const void *C, const float *B_prev, const float *U_prev, const void *chunk_starts,
-                       const float *d_inc, const float *zdot, const void *dY, void *dU, float *dM, float *dK,
+                       const void *d_inc, const float *zdot, const void *dY, void *dU, float *dM, float *dK,
                        void *dB, void *dC, float *carryB, float *carryU, void *stream) {
   ScanDims d;
   int rc = check_shape(s, &d);
@@ -442,7 +451,7 @@ int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M, c
   const bool tc = tc_eligible(d, s->dtype);
   SLX_DISPATCH_T(s->dtype, {
     ScanBwdArgs<T_> a{(const T_ *)U, (const T_ *)B, (const T_ *)C, (const T_ *)dY, M, K, (const float *)chunk_starts,
-                      d_inc, zdot,
+                      (const float *)d_inc, zdot,
                       B_prev, U_prev, (T_ *)dU, (T_ *)dB, (T_ *)dC, dM, dK, carryB, carryU, d};
     if constexpr (!std::is_same<T_, float>::value) {
       if (tc) return launch_scan_bwd_tc<T_>(d, a, as_stream(stream));
@@ -464,13 +473,14 @@ static int v2x2ssd_bwd_impl(const slx_scan_shape *s, const void *U, const float 
               SLX_E_NULL, "v2x2ssd_bwd: NULL tensor");
   SLX_REQUIRE_ALIGNED("v2x2ssd_bwd", final_state, d_final, d_initial, dB_prev, dU_prev);
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
-  const BwdWs w = bwd_ws(d);
+  const BwdWs w = bwd_ws(d, s->dtype);
   SLX_REQUIRE(workspace != nullptr && workspace_bytes >= w.total, SLX_E_WORKSPACE,
               "v2x2ssd_bwd: workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
   SLX_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, SLX_E_WORKSPACE,
               "v2x2ssd_bwd: workspace must be 256-byte aligned");
   char *base = static_cast<char *>(workspace);
-  float *d_inc = reinterpret_cast<float *>(base + w.d_inc);
+  void *d_inc = base + w.d_inc;
+  float *dz0 = reinterpret_cast<float *>(base + w.dz0);
   float *zdot = reinterpret_cast<float *>(base + w.zdot);
   float *partials = reinterpret_cast<float *>(base + w.partials);
   float *carryB = reinterpret_cast<float *>(base + w.carryB);
@@ -478,10 +488,10 @@ static int v2x2ssd_bwd_impl(const slx_scan_shape *s, const void *U, const float 
   cudaStream_t st = as_stream(stream);
 
   if (!dz0_ready) {
-    rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, d_inc, stream);
+    rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, dz0, stream);
     if (rc) return rc;
   }
-  rc = launch_state_bwd(d.BH, d.NC, d.P, d.N, d_inc, m_chunk, chunk_starts, starts_dtype_of(d, s->dtype), final_state,
+  rc = launch_state_bwd(d.BH, d.NC, d.P, d.N, dz0, m_chunk, chunk_starts, starts_dtype_of(d, s->dtype), final_state,
                         d_final, d_inc, d_initial,
                         zdot, partials, st);
   if (rc) return rc;
@@ -512,12 +522,12 @@ int slx_v2x2ssd_bwd_begin(const slx_scan_shape *s, const float *M, const void *C
   int rc = check_shape(s, &d);
   if (rc) return rc;
   SLX_REQUIRE(M && C && m_chunk && dY && d_initial_zero_final, SLX_E_NULL, "v2x2ssd_bwd_begin: NULL tensor");
-  const BwdWs w = bwd_ws(d);
+  const BwdWs w = bwd_ws(d, s->dtype);
   SLX_REQUIRE(workspace != nullptr && workspace_bytes >= w.total, SLX_E_WORKSPACE,
               "v2x2ssd_bwd_begin: workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
   SLX_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, SLX_E_WORKSPACE,
               "v2x2ssd_bwd_begin: workspace must be 256-byte aligned");
-  float *dz0 = reinterpret_cast<float *>(static_cast<char *>(workspace) + w.d_inc);
+  float *dz0 = reinterpret_cast<float *>(static_cast<char *>(workspace) + w.dz0);
   rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, dz0, stream);
   if (rc) return rc;
   return launch_state_bwd(d.BH, d.NC, d.P, d.N, dz0, m_chunk, nullptr, SLX_F32, nullptr, nullptr, nullptr,

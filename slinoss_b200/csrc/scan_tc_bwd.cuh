@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
   const int j = tid & 7, r0 = tid >> 3;  // r0 in [0,64)
   // on this path the chunk-start states are stored in the activation dtype (api: slx_scan_starts_dtype)
   const T *z0 = reinterpret_cast<const T *>(a.starts) + ((size_t)bh * d.NC + c) * P * d.D;
-  const float *lam = a.d_inc + ((size_t)bh * d.NC + c) * P * d.D;
+  const T *lam = reinterpret_cast<const T *>(a.d_inc) + ((size_t)bh * d.NC + c) * P * d.D;  // same dtype as z0
   float2 mreg[4];  // the prefix warp's multipliers, requested ahead of the bulk copies
   if (warp == 2) chunk_prefix_load4(a.M + tok0 * 2, valid, mreg);
   // U and dY land in their operand tiles by asynchronous copy (rows past the chunk end are
@@ -122,15 +122,12 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   prefetch_cb(0);
-  // Z0 / Lambda slab (fp32): one 8-float item per thread, prefetched into registers
+  // Z0 / Lambda slab: one 8-value (16-byte) item per thread, prefetched into registers
   const int zp = tid >> 3, zj = tid & 7;
-  uint4 zr;
-  float4 lr0, lr1;
+  uint4 zr, lr;
   auto prefetch_zl = [&](int sl) {
-    const float4 *ls = reinterpret_cast<const float4 *>(lam + (size_t)zp * d.D + sl * 64 + 8 * zj);
     zr = *reinterpret_cast<const uint4 *>(z0 + (size_t)zp * d.D + sl * 64 + 8 * zj);
-    lr0 = ls[0];
-    lr1 = ls[1];
+    lr = *reinterpret_cast<const uint4 *>(lam + (size_t)zp * d.D + sl * 64 + 8 * zj);
   };
   prefetch_zl(0);
 

@@ -112,14 +112,15 @@ __global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc
 // Reverse pass: g = d_final; for c = NC-1..0:
 //   zdot_partial[c] = sum conj(end_state_c) * g      (end_state_c = starts[c+1] or final)
 //   d_inc[c] = g;  g = dZ0[c] + conj(m_chunk[c]) * g
-// d_initial = g.  d_inc may alias dZ0.  With zdot_partials == NULL the dot products (and the reads
+// d_initial = g.  d_inc is stored as ST like the chunk-start states (the per-chunk backward rounds
+// it to the activation dtype for its products anyway); with ST = float it may alias dZ0.  With zdot_partials == NULL the dot products (and the reads
 // of starts / final_state) are skipped, with d_inc == NULL nothing but d_initial is written: that
 // is the reduce-only pass that gives a segment's d_initial for a zero d_final.
 template <int VEC, typename ST>
 __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0, const float *__restrict__ m_chunk,
                                                                 const ST *__restrict__ starts,
                                                                 const float *__restrict__ final_state,
-                                                                const float *__restrict__ d_final, float *d_inc,
+                                                                const float *__restrict__ d_final, ST *d_inc,
                                                                 float *__restrict__ d_initial,
                                                                 float *__restrict__ zdot_partials, int NC, int n_vec) {
   using V = typename VecT<VEC>::type;
@@ -130,7 +131,8 @@ __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0
   const int iv = live ? i : 0;
   const size_t per = (size_t)n_vec;
   const V *dzv = reinterpret_cast<const V *>(dZ0) + (size_t)bh * NC * per + iv;
-  V *div = d_inc ? reinterpret_cast<V *>(d_inc) + (size_t)bh * NC * per + iv : nullptr;
+  ST *div = d_inc ? d_inc + ((size_t)bh * NC * per + iv) * VEC : nullptr;  // + c * per * VEC per chunk
+  const size_t ds = per * VEC;
   if (zdot_partials == nullptr) {  // reduce-only / no dot products: a plain reverse recurrence
     const float2 *mc0 = reinterpret_cast<const float2 *>(m_chunk) + (size_t)bh * NC;
     V g0 = (d_final && live) ? reinterpret_cast<const V *>(d_final)[(size_t)bh * per + iv] : vzero(V());
@@ -139,18 +141,18 @@ __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0
       V d0 = dzv[(size_t)(c - 0) * per], d1 = dzv[(size_t)(c - 1) * per];
       V d2 = dzv[(size_t)(c - 2) * per], d3 = dzv[(size_t)(c - 3) * per];
       const float2 m0 = mc0[c], m1 = mc0[c - 1], m2 = mc0[c - 2], m3 = mc0[c - 3];
-      if (div && live) div[(size_t)(c - 0) * per] = g0;
+      if (div && live) st_store<ST>(div + (size_t)(c - 0) * ds, g0);
       g0 = axpy_c(cconj(m0), g0, d0);
-      if (div && live) div[(size_t)(c - 1) * per] = g0;
+      if (div && live) st_store<ST>(div + (size_t)(c - 1) * ds, g0);
       g0 = axpy_c(cconj(m1), g0, d1);
-      if (div && live) div[(size_t)(c - 2) * per] = g0;
+      if (div && live) st_store<ST>(div + (size_t)(c - 2) * ds, g0);
       g0 = axpy_c(cconj(m2), g0, d2);
-      if (div && live) div[(size_t)(c - 3) * per] = g0;
+      if (div && live) st_store<ST>(div + (size_t)(c - 3) * ds, g0);
       g0 = axpy_c(cconj(m3), g0, d3);
     }
     for (; c >= 0; --c) {
       V dz = dzv[(size_t)c * per];
-      if (div && live) div[(size_t)c * per] = g0;
+      if (div && live) st_store<ST>(div + (size_t)c * ds, g0);
       g0 = axpy_c(cconj(mc0[c]), g0, dz);
     }
     if (d_initial && live) reinterpret_cast<V *>(d_initial)[(size_t)bh * per + iv] = g0;
@@ -181,7 +183,7 @@ __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0
       reinterpret_cast<float2 *>(zdot_partials)[((size_t)bh * NC + c) * gridDim.x + blockIdx.x] = acc;
     }
     __syncthreads();
-    if (live && div) div[(size_t)c * per] = g;
+    if (live && div) st_store<ST>(div + (size_t)c * ds, g);
     g = axpy_c(cconj(m), g, dz);
     endst = st;
   }
