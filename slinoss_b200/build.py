@@ -60,7 +60,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         objs = list(ex.map(compile_one, sources))
     tmp = OUT_DIR / f"libslinoss_b200.{os.getpid()}.tmp.so"
     cmd = [_nvcc(), "-shared", "-o", str(tmp), *map(str, objs), "-gencode",
-           "arch=compute_100a,code=sm_100a", "-lcuda"]
+           "arch=compute_100a,code=sm_100a"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

@@ -167,13 +167,47 @@ static int launch_outer_tc(const ScanDims &d, const void *A, const void *X, cons
   return check_launch(MODE == 0 ? "chunk_increment_fwd_tc" : "chunk_scan_bwd_dz0_tc");
 }
 
+// Tensor map of a (BH, T, width) half tensor for boxes of [rows][64 columns], 128-byte swizzle.
+template <typename T>
+static int make_tile_map(CUtensorMap *map, const void *base, int BH, int T_, int width, int box_rows, const char *what) {
+  const cuuint64_t dims[3] = {(cuuint64_t)width, (cuuint64_t)T_, (cuuint64_t)BH};
+  const cuuint64_t strides[2] = {(cuuint64_t)width * sizeof(T), (cuuint64_t)T_ * width * sizeof(T)};
+  const cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 1u};
+  const cuuint32_t estr[3] = {1u, 1u, 1u};
+  const CUtensorMapDataType dt =
+      std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  // the driver entry point is looked up at run time so that the library loads on machines without a driver
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = nullptr;
+  if (encode == nullptr) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || fn == nullptr)
+      return fail(SLX_E_UNSUPPORTED, "%s: cuTensorMapEncodeTiled is not available from this driver", what);
+    encode = reinterpret_cast<EncodeFn>(fn);
+  }
+  CUresult r = encode(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SLX_E_UNSUPPORTED, "%s: tensor map could not be encoded (CUresult %d)", what, (int)r);
+  return SLX_OK;
+}
+
 template <typename T>
 static int launch_scan_bwd_tc(const ScanDims &d, const ScanBwdArgs<T> &a, cudaStream_t st) {
   auto kern = chunk_scan_bwd_tc_kernel<T>;
   size_t smem = scan_bwd_tc_smem_bytes();
   int rc = set_smem(kern, smem);
   if (rc) return rc;
-  kern<<<dim3(d.NC, d.BH), kTcBwdThreads, smem, st>>>(a);
+  ScanBwdMaps maps;
+  rc = make_tile_map<T>(&maps.C, a.C, d.BH, d.T, d.D, 128, "chunk_scan_bwd");
+  if (rc) return rc;
+  rc = make_tile_map<T>(&maps.B, a.B, d.BH, d.T, d.D, 128, "chunk_scan_bwd");
+  if (rc) return rc;
+  kern<<<dim3(d.NC, d.BH), kTcBwdThreads, smem, st>>>(a, maps);
   return check_launch("chunk_scan_bwd_tc");
 }
 

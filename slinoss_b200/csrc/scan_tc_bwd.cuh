@@ -24,15 +24,23 @@
 // wait on the preceding products, so that their latency overlaps the tensor work.
 #pragma once
 
+#include <cuda.h>
+
 #include "scan_tc.cuh"
 
 namespace slx {
+
+// tensor maps of the raw C and B operands: (D, T, BH) with boxes of 64 columns x 128 tokens
+struct alignas(64) ScanBwdMaps {
+  CUtensorMap C, B;
+};
 
 constexpr int kTcBwdThreads = 512;
 constexpr size_t scan_bwd_tc_smem_bytes() { return 1024 + 144 * 1024 + 28 * 1024 + 32 * 1024; }
 
 template <typename T>
-__global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(ScanBwdArgs<T> a) {
+__global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(ScanBwdArgs<T> a,
+                                                                              const __grid_constant__ ScanBwdMaps maps) {
   constexpr int L = kTcL, P = kTcP;
   extern __shared__ unsigned char smem_raw[];
   unsigned char *base =
@@ -64,7 +72,8 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
   float *ulf = xb + 256;                              // 256: u_{-1} . Lambda, all slabs
   unsigned char *sC = base + 147456 + 28672;          // raw C slab (swizzled tile), filled by cp.async
   unsigned char *sB = sC + 16384;                     // raw B slab
-  __shared__ uint64_t mbar;
+  __shared__ uint64_t mbar;   // completion of the tensor products
+  __shared__ uint64_t tbar;   // arrival of a raw (C, B) slab by TMA
   __shared__ uint32_t tmem_slot;
 
   const ScanDims d = a.d;
@@ -74,7 +83,7 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
   const int valid = min(L, d.T - t0);
   const size_t tok0 = (size_t)bh * d.T + t0;
   const int NB = d.D / 64;
-  const uint32_t mbar_s = umma::smem_u32(&mbar);
+  const uint32_t mbar_s = umma::smem_u32(&mbar), tbar_s = umma::smem_u32(&tbar);
   constexpr int fmt = umma::HalfFmt<T>::value;
 
   const bool stamp_on = (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0);
@@ -102,26 +111,25 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
                  : "memory");
   }
   asm volatile("cp.async.commit_group;" ::: "memory");
-  // asynchronous copy of one raw (C, B) slab into the staging tiles: every thread copies the
-  // chunks it will itself transform
+  // One raw (C, B) slab = two TMA boxes of [128 tokens][64 columns] into the swizzled staging tiles,
+  // issued by one thread; tokens past the end of the sequence arrive as zeros.
   auto prefetch_cb = [&](int sl) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int r = r0 + 64 * i;
-      const int rr = r < valid ? r : 0;
-      const uint32_t nbytes = r < valid ? 16u : 0u;
-      const size_t g = (tok0 + rr) * d.D + sl * 64 + 8 * j;
-      const uint32_t off = umma::swz_off(r, j);
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(umma::smem_u32(sC + off)), "l"(a.C + g),
-                   "r"(nbytes)
-                   : "memory");
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(umma::smem_u32(sB + off)), "l"(a.B + g),
-                   "r"(nbytes)
-                   : "memory");
+    if (tid == 32) {
+      umma::fence_smem_to_async();  // the tiles' earlier (generic) readers are behind a barrier
+      umma::mbar_expect_tx(tbar_s, 2u * 16384u);
+      umma::tma_load_3d(umma::smem_u32(sC), &maps.C, sl * 64, t0, bh, tbar_s);
+      umma::tma_load_3d(umma::smem_u32(sB), &maps.B, sl * 64, t0, bh, tbar_s);
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
   };
+  if (tid == 32) {
+    umma::mbar_init(mbar_s, 1);
+    umma::mbar_init(tbar_s, 1);
+    umma::fence_mbar_init();
+    umma::tma_prefetch_map(&maps.C);
+    umma::tma_prefetch_map(&maps.B);
+  }
   prefetch_cb(0);
+  uint32_t tphase = 0;
   // Z0 / Lambda slab: one 8-value (16-byte) item per thread, prefetched into registers
   const int zp = tid >> 3, zj = tid & 7;
   uint4 zr, lr;
@@ -132,10 +140,6 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
   prefetch_zl(0);
 
   if (warp == 0) umma::tmem_alloc(&tmem_slot, 512);
-  if (tid == 32) {
-    umma::mbar_init(mbar_s, 1);
-    umma::fence_mbar_init();
-  }
   if (warp == 2) chunk_prefix_fast128(mreg, lp, ph, mraw, &g_scan_bad);
   if (tid >= 128 && tid < 256) {
     int t = tid - 128;
@@ -161,7 +165,7 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
     else if (a.Bprev) bv = *reinterpret_cast<const float2 *>(a.Bprev + (size_t)bh * d.D + 2 * n);
     bm1[n] = bv;
   }
-  asm volatile("cp.async.wait_group 1;" ::: "memory");  // U, dY tiles (the slab group may still be in flight)
+  asm volatile("cp.async.wait_group 0;" ::: "memory");  // U, dY tiles
   umma::fence_smem_to_async();
   umma::fence_before_sync();
   __syncthreads();

@@ -95,6 +95,24 @@ __device__ __forceinline__ void mbar_init(uint32_t mbar_saddr, uint32_t count) {
 }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
+// ---- TMA (bulk tensor copies into swizzled shared-memory tiles) -----------------------------
+// The 128-byte swizzle of a tiled copy is the layout swz_off() describes, so a [rows][64 half]
+// box lands ready to be a tcgen05 operand.  Rows outside the tensor are filled with zeros.
+// The x coordinate times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar_saddr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar_saddr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_saddr, const void *tensor_map, int x, int y, int z,
+                                            uint32_t mbar_saddr) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst_saddr), "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(x), "r"(y), "r"(z), "r"(mbar_saddr)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_map(const void *tensor_map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensor_map)) : "memory");
+}
+
 // Bounded wait: gives up after about a second of SM clock and reports failure
 // instead of spinning forever (each try_wait poll blocks for a short
 // hardware-defined time by itself).
