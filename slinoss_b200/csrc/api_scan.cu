@@ -138,35 +138,6 @@ static bool tc_eligible(const ScanDims &d, int dtype) {
          d.D >= 64 && d.D <= 256;
 }
 
-// dtype of the chunk-start states between the stages: the activation dtype on the tensor-core
-// path (those kernels round Z0 to it anyway; half the bytes of fp32), fp32 otherwise
-static int starts_dtype_of(const ScanDims &d, int dtype) { return tc_eligible(d, dtype) ? dtype : (int)SLX_F32; }
-
-template <typename T>
-static int launch_scan_fwd_tc(const ScanDims &d, const void *U, const float *M, const float *K, const void *B,
-                              const void *C, const float *starts, const float *Bprev, const float *Uprev, void *Y,
-                              cudaStream_t st) {
-  ScanFwdArgs<T> a{(const T *)U, (const T *)B, (const T *)C, M, K, starts, Bprev, Uprev, (T *)Y, nullptr, d};
-  auto kern = chunk_scan_fwd_tc_kernel<T>;
-  size_t smem = scan_fwd_tc_smem_bytes();
-  int rc = set_smem(kern, smem);
-  if (rc) return rc;
-  kern<<<dim3(d.NC, d.BH), kTcThreads, smem, st>>>(a);
-  return check_launch("chunk_scan_fwd_tc");
-}
-
-template <typename T, int MODE>
-static int launch_outer_tc(const ScanDims &d, const void *A, const void *X, const float *M, const float *K,
-                           const float *Bprev, const float *Uprev, float *out, float *m_chunk, cudaStream_t st) {
-  OuterArgs<T> a{(const T *)A, (const T *)X, M, K, Bprev, Uprev, out, m_chunk, d};
-  auto kern = chunk_outer_tc_kernel<T, MODE>;
-  size_t smem = outer_tc_smem_bytes();
-  int rc = set_smem(kern, smem);
-  if (rc) return rc;
-  kern<<<dim3(d.NC, d.BH), kTcThreads, smem, st>>>(a);
-  return check_launch(MODE == 0 ? "chunk_increment_fwd_tc" : "chunk_scan_bwd_dz0_tc");
-}
-
 // Tensor map of a (BH, T, width) half tensor for boxes of [rows][64 columns], 128-byte swizzle.
 template <typename T>
 static int make_tile_map(CUtensorMap *map, const void *base, int BH, int T_, int width, int box_rows, const char *what) {
@@ -194,6 +165,35 @@ static int make_tile_map(CUtensorMap *map, const void *base, int BH, int T_, int
                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(SLX_E_UNSUPPORTED, "%s: tensor map could not be encoded (CUresult %d)", what, (int)r);
   return SLX_OK;
+}
+
+// dtype of the chunk-start states between the stages: the activation dtype on the tensor-core
+// path (those kernels round Z0 to it anyway; half the bytes of fp32), fp32 otherwise
+static int starts_dtype_of(const ScanDims &d, int dtype) { return tc_eligible(d, dtype) ? dtype : (int)SLX_F32; }
+
+template <typename T>
+static int launch_scan_fwd_tc(const ScanDims &d, const void *U, const float *M, const float *K, const void *B,
+                              const void *C, const float *starts, const float *Bprev, const float *Uprev, void *Y,
+                              cudaStream_t st) {
+  ScanFwdArgs<T> a{(const T *)U, (const T *)B, (const T *)C, M, K, starts, Bprev, Uprev, (T *)Y, nullptr, d};
+  auto kern = chunk_scan_fwd_tc_kernel<T>;
+  size_t smem = scan_fwd_tc_smem_bytes();
+  int rc = set_smem(kern, smem);
+  if (rc) return rc;
+  kern<<<dim3(d.NC, d.BH), kTcThreads, smem, st>>>(a);
+  return check_launch("chunk_scan_fwd_tc");
+}
+
+template <typename T, int MODE>
+static int launch_outer_tc(const ScanDims &d, const void *A, const void *X, const float *M, const float *K,
+                           const float *Bprev, const float *Uprev, float *out, float *m_chunk, cudaStream_t st) {
+  OuterArgs<T> a{(const T *)A, (const T *)X, M, K, Bprev, Uprev, out, m_chunk, d};
+  auto kern = chunk_outer_tc_kernel<T, MODE>;
+  size_t smem = outer_tc_smem_bytes();
+  int rc = set_smem(kern, smem);
+  if (rc) return rc;
+  kern<<<dim3(d.NC, d.BH), kTcThreads, smem, st>>>(a);
+  return check_launch(MODE == 0 ? "chunk_increment_fwd_tc" : "chunk_scan_bwd_dz0_tc");
 }
 
 template <typename T>

@@ -8,10 +8,17 @@
 // accumulators live in tensor memory and are read back once per tile.
 #pragma once
 
+#include <cuda.h>
+
 #include "scan_simt.cuh"
 #include "umma.cuh"
 
 namespace slx {
+
+// tensor maps of the raw C and B operands: (D, T, BH), boxes of 64 columns x 128 tokens, 128-byte swizzle
+struct alignas(64) ScanTileMaps {
+  CUtensorMap C, B;
+};
 
 __device__ int g_tc_status = 0;  // becomes non-zero when a bounded wait ran out
 __device__ long long g_phase_clock[128];  // clock64() stamps of CTA (0,0) of the last backward launch (diagnostic)

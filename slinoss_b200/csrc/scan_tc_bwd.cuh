@@ -24,16 +24,11 @@
 // wait on the preceding products, so that their latency overlaps the tensor work.
 #pragma once
 
-#include <cuda.h>
-
 #include "scan_tc.cuh"
 
 namespace slx {
 
-// tensor maps of the raw C and B operands: (D, T, BH) with boxes of 64 columns x 128 tokens
-struct alignas(64) ScanBwdMaps {
-  CUtensorMap C, B;
-};
+using ScanBwdMaps = ScanTileMaps;
 
 constexpr int kTcBwdThreads = 512;
 constexpr size_t scan_bwd_tc_smem_bytes() { return 1024 + 144 * 1024 + 28 * 1024 + 32 * 1024; }
