@@ -461,11 +461,11 @@ def main() -> int:
         k_ms = e0.elapsed_time(e1) / reps
     flops = dense_flops_bwd_chunk(L, P, D) * BH * NC
     achieved = flops / (k_ms * 1e-3) / 1e12
-    # DRAM bytes of one launch: ncu measured 356.5 MB for 1024 chunks of this kernel at P64 N128
+    # DRAM bytes of one launch: ncu measured 355.9 MB for 1024 chunks of this kernel at P64 N128
     # (the capture's summary is committed under profiles/); the kernel's traffic is per chunk
     traffic = None
     if L == 128 and P == 64 and N == 128:
-        traffic = 356.5e6 / 1024 * BH * NC
+        traffic = 355.9e6 / 1024 * BH * NC
     roofline = dict(kernel="chunk_scan_bwd_tc_kernel" if L == 128 else "chunk_scan_bwd_kernel", bound="tensor",
                     achieved=achieved, peak=peaks["tflops"], unit="TFLOP/s", frac=achieved / peaks["tflops"],
                     traffic=traffic, traffic_source="ncu capture of 1024 chunks scaled by the chunk count",
