@@ -218,12 +218,70 @@ __device__ __forceinline__ void apply_dyact(const ConvDims &d, int t, const floa
   }
 }
 
+// Gradient of the carried state (cat index i < W-1  <->  x index tau = i-(W-1)), a kernel of its own so
+// that it adds nothing to the register count of the walk: one thread per VEC channels of one batch row,
+// dyact[0..2] recomputed from the first three tokens.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_dstate_kernel(
+    const T *__restrict__ x, const T *__restrict__ weight, const T *__restrict__ bias, const T *__restrict__ state,
+    const T *__restrict__ dy, const T *__restrict__ d_next, float *__restrict__ dstate, ConvDims d) {
+  const int c0 = (blockIdx.x * kConvThreads + threadIdx.x) * VEC;
+  if (c0 >= d.C) return;
+  const int b = blockIdx.z;
+  float w4[4][VEC], bv[VEC];
+  load_taps<T, VEC>(weight, bias, d, c0, w4, bv);
+  float xa[VEC], xb[VEC], xc[VEC], xd[VEC], ga[3][VEC];
+  load_cat<T, VEC>(x, state, d, b, -3, c0, xa);
+  load_cat<T, VEC>(x, state, d, b, -2, c0, xb);
+  load_cat<T, VEC>(x, state, d, b, -1, c0, xc);
+#pragma unroll
+  for (int t = 0; t < 3; ++t) {
+    if (t < d.T) ldv<T, VEC>(x + (long long)b * d.xbs + (long long)t * d.xs + c0, xd);
+    load_dyact<T, VEC>(dy, d, b, t, c0, w4, bv, xa, xb, xc, xd, ga[t]);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      xa[e] = xb[e];
+      xb[e] = xc[e];
+      xc[e] = xd[e];
+    }
+  }
+  for (int i = 0; i < d.W - 1; ++i) {
+    const int tau = i - (d.W - 1);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+#pragma unroll
+        for (int s = 0; s < 3; ++s)
+          if (s == tau + 3 - k) acc = fmaf(w4[k][e], ga[s][e], acc);
+      }
+      int in = i - d.T;  // next_state index that aliases this state slot when T < W-1
+      if (d_next && in >= 0) acc += to_f(d_next[((long long)b * d.C + c0 + e) * (d.W - 1) + in]);
+      dstate[((long long)b * d.C + c0 + e) * (d.W - 1) + i] = acc;
+    }
+  }
+}
+
+// Writes this tile's partial sums part[(b*n_tiles + tile)][C][5] = (dw4[0..3], dbias)
+template <int VEC>
+__device__ __forceinline__ void conv_bwd_partials(float *part, int C, int b, int c0, const float (&dw)[4][VEC],
+                                                  const float (&db)[VEC]) {
+  float *pp = part + (((long long)b * gridDim.y + blockIdx.y) * C + c0) * 5;
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) pp[e * 5 + k] = dw[k][e];
+    pp[e * 5 + 4] = db[e];
+  }
+}
+
 // part[(b*n_tiles + tile)][C][5] = (dw4[0..3], dbias) partial sums of this tile
 template <typename T, int VEC>
 __global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_kernel(
     const T *__restrict__ x, const T *__restrict__ weight, const T *__restrict__ bias, const T *__restrict__ state,
-    const T *__restrict__ dy, const T *__restrict__ d_next, T *__restrict__ dx, float *__restrict__ dstate,
-    float *__restrict__ part, ConvDims d, int tile) {
+    const T *__restrict__ dy, const T *__restrict__ d_next, T *__restrict__ dx, float *__restrict__ part, ConvDims d,
+    int tile) {
   const int c0 = (blockIdx.x * kConvThreads + threadIdx.x) * VEC;
   if (c0 >= d.C) return;
   const int b = blockIdx.z;
@@ -302,65 +360,300 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_kernel(
     }
     }
   }
-  float *pp = part + (((long long)b * gridDim.y + blockIdx.y) * d.C + c0) * 5;
+  conv_bwd_partials<VEC>(part, d.C, b, c0, dw, db);
+}
+
+// ---- staged variants: rows travel global -> shared by cp.async, several groups ahead of the walk ----
+// Every thread copies exactly the slices it will read itself, so no barrier is needed: the copy groups
+// are tracked per thread (commit_group / wait_group).  The ring holds kConvRing groups of G rows; while
+// one group is consumed, kConvRing-1 groups are in flight, without holding registers for them.
+constexpr int kConvRing = 4;
+
+template <int BYTES>
+__device__ __forceinline__ void cp_async_slice(void *smem_dst, const void *gsrc, bool valid) {
+  static_assert(BYTES == 8 || BYTES == 16, "slice of 8 or 16 bytes");
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+  const int n = valid ? BYTES : 0;  // 0 source bytes: the slice is filled with zeros
+  if constexpr (BYTES == 16)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gsrc), "r"(n) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <typename T, int VEC>
+constexpr int conv_group_rows() { return sizeof(RowSlice<T, VEC>) == 8 ? 8 : 4; }
+template <typename T, int VEC>
+constexpr size_t conv_ring_bytes(int tensors) {
+  return (size_t)kConvRing * conv_group_rows<T, VEC>() * tensors * kConvThreads * sizeof(RowSlice<T, VEC>);
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_staged_kernel(
+    const T *__restrict__ x, const T *__restrict__ weight, const T *__restrict__ bias, const T *__restrict__ state,
+    const T *__restrict__ dy, const T *__restrict__ d_next, T *__restrict__ dx, float *__restrict__ part, ConvDims d,
+    int tile) {
+  using Slice = RowSlice<T, VEC>;
+  constexpr int G = conv_group_rows<T, VEC>();
+  extern __shared__ __align__(16) unsigned char conv_ring[];
+  const int c0 = (blockIdx.x * kConvThreads + threadIdx.x) * VEC;
+  if (c0 >= d.C) return;
+  Slice *ring = reinterpret_cast<Slice *>(conv_ring) + threadIdx.x;  // [kConvRing*G rows][x, dy][thread]
+  const int b = blockIdx.z;
+  const int t_lo = blockIdx.y * tile, t_hi = min(d.T, t_lo + tile);
+  const int t_end = min(d.T + 3, t_hi + 3);
+  const int n_grp = (t_end - t_lo + G - 1) / G;
+  const T *xb = x + (long long)b * d.xbs + c0;
+  const T *gb = dy + (long long)b * d.T * d.C + c0;
+  // requests the rows of group grp (rows past the tile or the sequence are filled with zeros) and closes
+  // the group; past the last group only the (empty) group is closed, which keeps the wait count uniform
+#define SLX_CONV_ISSUE(grp_)                                                                                     \
+  do {                                                                                                           \
+    const int gi_ = (grp_);                                                                                      \
+    if (gi_ < n_grp) {                                                                                           \
+      Slice *s_ = ring + (size_t)(gi_ % kConvRing) * G * 2 * kConvThreads;                                       \
+      _Pragma("unroll") for (int u_ = 0; u_ < G; ++u_) {                                                         \
+        const int t_ = t_lo + gi_ * G + u_;                                                                      \
+        const bool ok_ = t_ < t_end && t_ < d.T;                                                                 \
+        cp_async_slice<sizeof(Slice)>(s_ + (u_ * 2 + 0) * kConvThreads, ok_ ? xb + (long long)t_ * d.xs : x, ok_); \
+        cp_async_slice<sizeof(Slice)>(s_ + (u_ * 2 + 1) * kConvThreads, ok_ ? gb + (long long)t_ * d.C : dy, ok_); \
+      }                                                                                                          \
+    }                                                                                                            \
+    cp_async_commit();                                                                                           \
+  } while (0)
 #pragma unroll
-  for (int e = 0; e < VEC; ++e) {
+  for (int g = 0; g < kConvRing - 1; ++g) SLX_CONV_ISSUE(g);
+
+  // arithmetic on pairs of adjacent channels (fma.rn.f32x2: each half is the same IEEE fma as the scalar
+  // kernel's, so the results are identical)
+  constexpr int H = VEC / 2;
+  float2 w4[4][H], bv[H], x0[H], x1[H], x2[H], x3[H];
+  {
+    float wf[4][VEC], bf[VEC], xa[VEC], xb2[VEC], xc[VEC];
+    load_taps<T, VEC>(weight, bias, d, c0, wf, bf);
+    load_cat<T, VEC>(x, state, d, b, t_lo - 3, c0, xa);
+    load_cat<T, VEC>(x, state, d, b, t_lo - 2, c0, xb2);
+    load_cat<T, VEC>(x, state, d, b, t_lo - 1, c0, xc);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) pp[e * 5 + k] = dw[k][e];
-    pp[e * 5 + 4] = db[e];
+    for (int h = 0; h < H; ++h) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) w4[k][h] = make_float2(wf[k][2 * h], wf[k][2 * h + 1]);
+      bv[h] = make_float2(bf[2 * h], bf[2 * h + 1]);
+      x0[h] = make_float2(xa[2 * h], xa[2 * h + 1]);
+      x1[h] = make_float2(xb2[2 * h], xb2[2 * h + 1]);
+      x2[h] = make_float2(xc[2 * h], xc[2 * h + 1]);
+    }
   }
-  // gradient of the carried state: cat index i < W-1  <->  x index tau = i-(W-1)
-  if (dstate && blockIdx.y == 0) {
-    // dyact[0..2] recomputed from scratch (tile 0 owns them, but they have been shifted out)
-    float xa[VEC], xb[VEC], xc[VEC], xd[VEC], ga[3][VEC];
-    load_cat<T, VEC>(x, state, d, b, -3, c0, xa);
-    load_cat<T, VEC>(x, state, d, b, -2, c0, xb);
-    load_cat<T, VEC>(x, state, d, b, -1, c0, xc);
-    for (int t = 0; t < 3; ++t) {
-      if (t < d.T) ldv<T, VEC>(x + (long long)b * d.xbs + (long long)t * d.xs + c0, xd);
-      load_dyact<T, VEC>(dy, d, b, t, c0, w4, bv, xa, xb, xc, xd, ga[t]);
+  float2 g0[H], g1[H], g2[H], g3[H];  // dyact[t-3..t]
+  float2 dw[4][H], db[H];
+  const float2 zero2 = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) {
-        xa[e] = xb[e];
-        xb[e] = xc[e];
-        xc[e] = xd[e];
+  for (int h = 0; h < H; ++h) {
+    g0[h] = g1[h] = g2[h] = zero2;
+    x3[h] = zero2;
+    db[h] = zero2;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) dw[k][h] = zero2;
+  }
+  for (int grp = 0; grp < n_grp; ++grp) {
+    // the slot of group grp+R-1 is the one read in the previous iteration
+    SLX_CONV_ISSUE(grp + kConvRing - 1);
+    cp_async_wait<kConvRing - 1>();
+    const Slice *s = ring + (size_t)(grp % kConvRing) * G * 2 * kConvThreads;
+#pragma unroll
+    for (int u = 0; u < G; ++u) {
+      const int t = t_lo + grp * G + u;
+      if (t >= t_end) break;
+      Slice xr, gr;
+      ld_raw<T, VEC>(s[(u * 2 + 0) * kConvThreads].v, xr);
+      ld_raw<T, VEC>(s[(u * 2 + 1) * kConvThreads].v, gr);
+      if (t < d.T) {
+#pragma unroll
+        for (int h = 0; h < H; ++h) x3[h] = make_float2(to_f(xr.v[2 * h]), to_f(xr.v[2 * h + 1]));
+      }
+      // rows past the sequence arrive as zeros, so g3 = 0 there without a test
+#pragma unroll
+      for (int h = 0; h < H; ++h) g3[h] = make_float2(to_f(gr.v[2 * h]), to_f(gr.v[2 * h + 1]));
+      if (d.silu) {
+#pragma unroll
+        for (int h = 0; h < H; ++h) {
+          float2 pre = __ffma2_rn(w4[0][h], x0[h], bv[h]);
+          pre = __ffma2_rn(w4[1][h], x1[h], pre);
+          pre = __ffma2_rn(w4[2][h], x2[h], pre);
+          pre = __ffma2_rn(w4[3][h], x3[h], pre);
+          const float sx = 1.f / (1.f + expf(-pre.x)), sy = 1.f / (1.f + expf(-pre.y));
+          g3[h].x *= sx * (1.f + pre.x * (1.f - sx));
+          g3[h].y *= sy * (1.f + pre.y * (1.f - sy));
+        }
+      }
+      if (t < t_hi) {
+#pragma unroll
+        for (int h = 0; h < H; ++h) {
+          dw[0][h] = __ffma2_rn(g3[h], x0[h], dw[0][h]);
+          dw[1][h] = __ffma2_rn(g3[h], x1[h], dw[1][h]);
+          dw[2][h] = __ffma2_rn(g3[h], x2[h], dw[2][h]);
+          dw[3][h] = __ffma2_rn(g3[h], x3[h], dw[3][h]);
+          db[h] = __fadd2_rn(db[h], g3[h]);
+        }
+      }
+      const int tau = t - 3;  // dx[tau] = sum_k w4[k] dyact[tau+3-k]
+      if (tau >= t_lo && tau < t_hi) {
+        float o[VEC];
+#pragma unroll
+        for (int h = 0; h < H; ++h) {
+          float2 acc = __fmul2_rn(w4[0][h], g3[h]);
+          acc = __ffma2_rn(w4[1][h], g2[h], acc);
+          acc = __ffma2_rn(w4[2][h], g1[h], acc);
+          acc = __ffma2_rn(w4[3][h], g0[h], acc);
+          o[2 * h] = acc.x;
+          o[2 * h + 1] = acc.y;
+        }
+        const int i = tau - d.T + (d.W - 1);  // position inside next_state, if any
+        if (d_next && i >= 0) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) o[e] += to_f(d_next[((long long)b * d.C + c0 + e) * (d.W - 1) + i]);
+        }
+        stv<T, VEC>(dx + ((long long)b * d.T + tau) * d.C + c0, o);
+      }
+#pragma unroll
+      for (int h = 0; h < H; ++h) {
+        x0[h] = x1[h];
+        x1[h] = x2[h];
+        x2[h] = x3[h];
+        g0[h] = g1[h];
+        g1[h] = g2[h];
+        g2[h] = g3[h];
       }
     }
-    for (int i = 0; i < d.W - 1; ++i) {
-      const int tau = i - (d.W - 1);
+  }
+  float dwf[4][VEC], dbf[VEC];
+#pragma unroll
+  for (int h = 0; h < H; ++h) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      dwf[k][2 * h] = dw[k][h].x;
+      dwf[k][2 * h + 1] = dw[k][h].y;
+    }
+    dbf[2 * h] = db[h].x;
+    dbf[2 * h + 1] = db[h].y;
+  }
+  cp_async_wait<0>();
+#undef SLX_CONV_ISSUE
+  conv_bwd_partials<VEC>(part, d.C, b, c0, dwf, dbf);
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kConvThreads) cconv1d_fwd_staged_kernel(const T *__restrict__ x,
+                                                                          const T *__restrict__ weight,
+                                                                          const T *__restrict__ bias,
+                                                                          const T *__restrict__ state,
+                                                                          T *__restrict__ y, T *__restrict__ next_state,
+                                                                          ConvDims d, int tile) {
+  using Slice = RowSlice<T, VEC>;
+  constexpr int G = conv_group_rows<T, VEC>();
+  extern __shared__ __align__(16) unsigned char conv_ring[];
+  const int c0 = (blockIdx.x * kConvThreads + threadIdx.x) * VEC;
+  if (c0 >= d.C) return;
+  Slice *ring = reinterpret_cast<Slice *>(conv_ring) + threadIdx.x;  // [kConvRing*G rows][thread]
+  const int b = blockIdx.z;
+  const int t_lo = blockIdx.y * tile, t_hi = min(d.T, t_lo + tile);
+  const int n_grp = (t_hi - t_lo + G - 1) / G;
+  const T *xb = x + (long long)b * d.xbs + c0;
+#define SLX_CONV_ISSUE(grp_)                                                                        \
+  do {                                                                                              \
+    const int gi_ = (grp_);                                                                         \
+    if (gi_ < n_grp) {                                                                              \
+      Slice *s_ = ring + (size_t)(gi_ % kConvRing) * G * kConvThreads;                              \
+      _Pragma("unroll") for (int u_ = 0; u_ < G; ++u_) {                                            \
+        const int t_ = t_lo + gi_ * G + u_;                                                         \
+        const bool ok_ = t_ < t_hi;                                                                 \
+        cp_async_slice<sizeof(Slice)>(s_ + u_ * kConvThreads, ok_ ? xb + (long long)t_ * d.xs : x, ok_); \
+      }                                                                                             \
+    }                                                                                               \
+    cp_async_commit();                                                                              \
+  } while (0)
+#pragma unroll
+  for (int g = 0; g < kConvRing - 1; ++g) SLX_CONV_ISSUE(g);
+
+  float w4[4][VEC], bv[VEC];
+  load_taps<T, VEC>(weight, bias, d, c0, w4, bv);
+  float x0[VEC], x1[VEC], x2[VEC], x3[VEC];
+  load_cat<T, VEC>(x, state, d, b, t_lo - 3, c0, x0);
+  load_cat<T, VEC>(x, state, d, b, t_lo - 2, c0, x1);
+  load_cat<T, VEC>(x, state, d, b, t_lo - 1, c0, x2);
+  for (int grp = 0; grp < n_grp; ++grp) {
+    SLX_CONV_ISSUE(grp + kConvRing - 1);  // into the slot read in the previous iteration
+    cp_async_wait<kConvRing - 1>();
+    const Slice *s = ring + (size_t)(grp % kConvRing) * G * kConvThreads;
+#pragma unroll
+    for (int u = 0; u < G; ++u) {
+      const int t = t_lo + grp * G + u;
+      if (t >= t_hi) break;
+      Slice xr;
+      ld_raw<T, VEC>(s[u * kConvThreads].v, xr);
+      float o[VEC];
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        float acc = 0.f;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          int s = tau + 3 - k;
-          if (s >= 0 && s < 3) acc = fmaf(w4[k][e], ga[s][e], acc);
-        }
-        int in = i - d.T;  // next_state index that aliases this state slot when T < W-1
-        if (d_next && in >= 0) acc += to_f(d_next[((long long)b * d.C + c0 + e) * (d.W - 1) + in]);
-        dstate[((long long)b * d.C + c0 + e) * (d.W - 1) + i] = acc;
+        x3[e] = to_f(xr.v[e]);
+        float acc = bv[e];
+        acc = fmaf(w4[0][e], x0[e], acc);
+        acc = fmaf(w4[1][e], x1[e], acc);
+        acc = fmaf(w4[2][e], x2[e], acc);
+        acc = fmaf(w4[3][e], x3[e], acc);
+        if (d.silu) acc = acc / (1.f + expf(-acc));
+        o[e] = acc;
+        x0[e] = x1[e];
+        x1[e] = x2[e];
+        x2[e] = x3[e];
       }
+      stv<T, VEC>(y + ((long long)b * d.T + t) * d.C + c0, o);
+    }
+  }
+  cp_async_wait<0>();
+#undef SLX_CONV_ISSUE
+  if (next_state && t_hi == d.T) {
+    for (int i = 0; i < d.W - 1; ++i) {
+      float v[VEC];
+      load_cat<T, VEC>(x, state, d, b, d.T - (d.W - 1) + i, c0, v);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e)
+        next_state[((long long)b * d.C + c0 + e) * (d.W - 1) + i] = from_f<T>(v[e]);
     }
   }
 }
 
-// One thread per (channel, slot) of the partials, slots = (dw4[0..3], dbias); the parts are summed
-// in their fixed order, eight loads in flight.
-__global__ void cconv1d_reduce_kernel(const float *__restrict__ part, float *__restrict__ dweight,
-                                      float *__restrict__ dbias, int n_parts, int C, int W) {
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= C * 5) return;
+// Sums the per-tile partials: a block owns 32 adjacent (channel, slot) entries, slots = (dw4[0..3], dbias);
+// its eight rows of threads each sum a contiguous share of the parts (eight loads in flight), and row 0 adds
+// the eight shares.  The order of every sum is fixed, so the result does not vary from run to run.
+constexpr int kConvReduceRows = 8;
+__global__ void __launch_bounds__(32 * kConvReduceRows) cconv1d_reduce_kernel(const float *__restrict__ part,
+                                                                              float *__restrict__ dweight,
+                                                                              float *__restrict__ dbias, int n_parts,
+                                                                              int C, int W) {
+  __shared__ float share[kConvReduceRows][32];
+  const int e = blockIdx.x * 32 + threadIdx.x, row = threadIdx.y;
   const size_t stride = (size_t)C * 5;
   float acc = 0.f;
-  int p = 0;
-  for (; p + 8 <= n_parts; p += 8) {
-    float v[8];
+  if (e < C * 5) {
+    const int per = (n_parts + kConvReduceRows - 1) / kConvReduceRows;
+    int p = row * per;
+    const int p_end = min(n_parts, p + per);
+    for (; p + 8 <= p_end; p += 8) {
+      float v[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = part[(size_t)(p + i) * stride + e];
+      for (int i = 0; i < 8; ++i) v[i] = part[(size_t)(p + i) * stride + e];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc += v[i];
+      for (int i = 0; i < 8; ++i) acc += v[i];
+    }
+    for (; p < p_end; ++p) acc += part[(size_t)p * stride + e];
   }
-  for (; p < n_parts; ++p) acc += part[(size_t)p * stride + e];
+  share[row][threadIdx.x] = acc;
+  __syncthreads();
+  if (row != 0 || e >= C * 5) return;
+#pragma unroll
+  for (int r = 1; r < kConvReduceRows; ++r) acc += share[r][threadIdx.x];
   const int c = e / 5, k = e % 5;
   if (k == 4) {
     if (dbias) dbias[c] = acc;
@@ -382,9 +675,43 @@ static int check_conv(const slx_conv_shape *s, ConvDims *d) {
   return SLX_OK;
 }
 
+// Smallest tile of the token axis: the backward workspace is sized for it (one set of partial sums per tile).
+constexpr int kConvTileFwd = 64, kConvTileBwd = 128;
+
 static int conv_tile(int T, bool bwd) {
-  int tile = bwd ? 128 : 64;
+  int tile = bwd ? kConvTileBwd : kConvTileFwd;
   return tile < T ? tile : T;
+}
+
+// CTAs of `kernel` (kConvThreads threads, `smem` dynamic bytes) that the current device holds at once
+template <typename K>
+static long conv_slots(K kernel, size_t smem) {
+  int dev = 0, sms = 0, per_sm = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kConvThreads, smem) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return (long)sms * per_sm;
+}
+
+// Tile of the token axis for a grid of base_ctas x ceil(T / tile) CTAs.  With the smallest tile the grid
+// may come to a few waves plus a thin last one; then the tile is grown (up to 512 tokens) to the size at
+// which the grid is k full waves, for the smallest such k.
+static int conv_tile_balanced(int T, int min_tile, long base_ctas, long slots) {
+  if (T <= min_tile) return T;
+  const long n_min = (T + min_tile - 1) / min_tile;
+  if (slots <= 0 || base_ctas * n_min <= slots) return min_tile;
+  for (long k = 1; k <= 16; ++k) {
+    const long nt = k * slots / base_ctas;
+    if (nt < 1) continue;
+    long tile = (T + nt - 1) / nt;
+    tile = (tile + 7) / 8 * 8;
+    if (tile < min_tile) return min_tile;
+    if (tile <= 512) return (int)tile;
+  }
+  return min_tile;
 }
 
 template <typename T>
@@ -415,19 +742,25 @@ int slx_cconv1d_fwd(const slx_conv_shape *s, const void *x, const void *weight, 
   if (rc) return rc;
   SLX_REQUIRE(x && weight && y, SLX_E_NULL, "cconv1d_fwd: NULL tensor");
   cudaStream_t st = as_stream(stream);
-  const int tile = conv_tile(d.T, false);
-  const int n_tiles = (d.T + tile - 1) / tile;
   SLX_CONV_T(s->dtype, {
     constexpr int VFULL = kConvVec;
+    const T_ *xp = (const T_ *)x, *wp = (const T_ *)weight, *bp = (const T_ *)bias, *sp = (const T_ *)state;
     if (conv_vec_ok<T_>(s, {x, y})) {
-      int nvec = d.C / VFULL;
-      cconv1d_fwd_kernel<T_, VFULL><<<dim3((nvec + kConvThreads - 1) / kConvThreads, n_tiles, d.batch), kConvThreads, 0,
-                                      st>>>((const T_ *)x, (const T_ *)weight, (const T_ *)bias, (const T_ *)state,
-                                            (T_ *)y, (T_ *)next_state, d, tile);
+      const int nblk = (d.C / VFULL + kConvThreads - 1) / kConvThreads;
+      constexpr size_t ring = conv_ring_bytes<T_, VFULL>(1);
+      auto kern = cconv1d_fwd_staged_kernel<T_, VFULL>;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
+      SLX_REQUIRE(e == cudaSuccess, (int)e, "cconv1d_fwd: shared memory attribute: %s", cudaGetErrorString(e));
+      const int tile = conv_tile(d.T, false);  // growing the tile to whole waves measured no faster here
+      const int n_tiles = (d.T + tile - 1) / tile;
+      kern<<<dim3(nblk, n_tiles, d.batch), kConvThreads, ring, st>>>(xp, wp, bp, sp, (T_ *)y, (T_ *)next_state, d,
+                                                                     tile);
     } else {
-      cconv1d_fwd_kernel<T_, 1><<<dim3((d.C + kConvThreads - 1) / kConvThreads, n_tiles, d.batch), kConvThreads, 0,
-                                  st>>>((const T_ *)x, (const T_ *)weight, (const T_ *)bias, (const T_ *)state,
-                                        (T_ *)y, (T_ *)next_state, d, tile);
+      const int nblk = (d.C + kConvThreads - 1) / kConvThreads;
+      const int tile = conv_tile(d.T, false);
+      const int n_tiles = (d.T + tile - 1) / tile;
+      cconv1d_fwd_kernel<T_, 1><<<dim3(nblk, n_tiles, d.batch), kConvThreads, 0, st>>>(xp, wp, bp, sp, (T_ *)y,
+                                                                                     (T_ *)next_state, d, tile);
     }
   });
   return check_launch("cconv1d_fwd");
@@ -452,26 +785,39 @@ int slx_cconv1d_bwd(const slx_conv_shape *s, const void *x, const void *weight, 
   SLX_REQUIRE(workspace && workspace_bytes >= need, SLX_E_WORKSPACE, "cconv1d_bwd: workspace of %zu bytes needed",
               need);
   cudaStream_t st = as_stream(stream);
-  const int tile = conv_tile(d.T, true);
-  const int n_tiles = (d.T + tile - 1) / tile;
   float *part = static_cast<float *>(workspace);
+  int n_tiles = 0;  // at most ceil(T / kConvTileBwd), which the workspace is sized for
   SLX_CONV_T(s->dtype, {
     constexpr int VFULL = kConvVec;
+    const T_ *xp = (const T_ *)x, *wp = (const T_ *)weight, *bp = (const T_ *)bias, *sp = (const T_ *)state;
+    const T_ *gp = (const T_ *)dy, *np = (const T_ *)d_next_state;
     if (conv_vec_ok<T_>(s, {x, dy, dx})) {
-      int nvec = d.C / VFULL;
-      cconv1d_bwd_kernel<T_, VFULL><<<dim3((nvec + kConvThreads - 1) / kConvThreads, n_tiles, d.batch), kConvThreads, 0,
-                                      st>>>((const T_ *)x, (const T_ *)weight, (const T_ *)bias, (const T_ *)state,
-                                            (const T_ *)dy, (const T_ *)d_next_state, (T_ *)dx, dstate, part, d,
-                                            tile);
+      const int nblk = (d.C / VFULL + kConvThreads - 1) / kConvThreads;
+      constexpr size_t ring = conv_ring_bytes<T_, VFULL>(2);
+      auto kern = cconv1d_bwd_staged_kernel<T_, VFULL>;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
+      SLX_REQUIRE(e == cudaSuccess, (int)e, "cconv1d_bwd: shared memory attribute: %s", cudaGetErrorString(e));
+      const int tile = conv_tile_balanced(d.T, kConvTileBwd, (long)nblk * d.batch, conv_slots(kern, ring));
+      n_tiles = (d.T + tile - 1) / tile;
+      kern<<<dim3(nblk, n_tiles, d.batch), kConvThreads, ring, st>>>(xp, wp, bp, sp, gp, np, (T_ *)dx, part, d, tile);
+      if (dstate)
+        cconv1d_bwd_dstate_kernel<T_, VFULL><<<dim3(nblk, 1, d.batch), kConvThreads, 0, st>>>(xp, wp, bp, sp, gp, np,
+                                                                                            dstate, d);
     } else {
-      cconv1d_bwd_kernel<T_, 1><<<dim3((d.C + kConvThreads - 1) / kConvThreads, n_tiles, d.batch), kConvThreads, 0,
-                                  st>>>((const T_ *)x, (const T_ *)weight, (const T_ *)bias, (const T_ *)state,
-                                        (const T_ *)dy, (const T_ *)d_next_state, (T_ *)dx, dstate, part, d, tile);
+      const int nblk = (d.C + kConvThreads - 1) / kConvThreads;
+      const int tile = conv_tile(d.T, true);
+      n_tiles = (d.T + tile - 1) / tile;
+      cconv1d_bwd_kernel<T_, 1><<<dim3(nblk, n_tiles, d.batch), kConvThreads, 0, st>>>(xp, wp, bp, sp, gp, np,
+                                                                                     (T_ *)dx, part, d, tile);
+      if (dstate)
+        cconv1d_bwd_dstate_kernel<T_, 1><<<dim3(nblk, 1, d.batch), kConvThreads, 0, st>>>(xp, wp, bp, sp, gp, np,
+                                                                                        dstate, d);
     }
   });
   rc = check_launch("cconv1d_bwd");
   if (rc) return rc;
-  cconv1d_reduce_kernel<<<(d.C * 5 + 255) / 256, 256, 0, st>>>(part, dweight, dbias, d.batch * n_tiles, d.C, d.W);
+  cconv1d_reduce_kernel<<<(d.C * 5 + 31) / 32, dim3(32, kConvReduceRows), 0, st>>>(part, dweight, dbias,
+                                                                                   d.batch * n_tiles, d.C, d.W);
   return check_launch("cconv1d_reduce");
 }
 

@@ -149,6 +149,7 @@ def test_conv_golden(tag, silu):
     (torch.bfloat16, 1, 130, 1024, 4, False),
     (torch.float16, 2, 65, 96, 3, True),
     (torch.float32, 2, 77, 20, 4, True),        # scalar path
+    (torch.bfloat16, 4, 4100, 2048, 4, True),   # more CTAs than the GPU holds at once: tiles are grown to whole waves
 ])
 def test_conv_seeded_vs_oracle(dtype, b, T, C, W, with_state):
     import slinoss_b200 as sb
