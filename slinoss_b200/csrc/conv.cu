@@ -11,6 +11,7 @@
 // load and one vector store per channel-vector-token, i.e. the algorithmic
 // 4 bytes per channel-token forward and 6 backward for half types.
 #include <initializer_list>
+#include <type_traits>
 #include <mutex>
 
 #include "common.cuh"
@@ -457,74 +458,88 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_staged_kernel(
 #pragma unroll
     for (int k = 0; k < 4; ++k) dw[k][h] = zero2;
   }
-  for (int grp = 0; grp < n_grp; ++grp) {
-    // the slot of group grp+R-1 is the one read in the previous iteration
-    SLX_CONV_ISSUE(grp + kConvRing - 1);
-    cp_async_wait<kConvRing - 1>();
-    const Slice *s = ring + (size_t)(grp % kConvRing) * G * 2 * kConvThreads;
+  // One row of the walk.  INNER rows (three or more rows into the tile and before its end) need none of the
+  // edge tests: every row is inside the sequence, counts toward the sums, and its dx row lies in the tile
+  // and ahead of the last W-1 tokens, the only ones next_state's gradient reaches.
+  auto row_step = [&](auto inner_tag, const Slice *s, int u, int t) {
+    constexpr bool INNER = decltype(inner_tag)::value;
+    Slice xr, gr;
+    ld_raw<T, VEC>(s[(u * 2 + 0) * kConvThreads].v, xr);
+    ld_raw<T, VEC>(s[(u * 2 + 1) * kConvThreads].v, gr);
+    if (INNER || t < d.T) {
 #pragma unroll
-    for (int u = 0; u < G; ++u) {
-      const int t = t_lo + grp * G + u;
-      if (t >= t_end) break;
-      Slice xr, gr;
-      ld_raw<T, VEC>(s[(u * 2 + 0) * kConvThreads].v, xr);
-      ld_raw<T, VEC>(s[(u * 2 + 1) * kConvThreads].v, gr);
-      if (t < d.T) {
+      for (int h = 0; h < H; ++h) x3[h] = make_float2(to_f(xr.v[2 * h]), to_f(xr.v[2 * h + 1]));
+    }
+    // rows past the sequence arrive as zeros, so g3 = 0 there without a test
 #pragma unroll
-        for (int h = 0; h < H; ++h) x3[h] = make_float2(to_f(xr.v[2 * h]), to_f(xr.v[2 * h + 1]));
+    for (int h = 0; h < H; ++h) g3[h] = make_float2(to_f(gr.v[2 * h]), to_f(gr.v[2 * h + 1]));
+    if (d.silu) {
+#pragma unroll
+      for (int h = 0; h < H; ++h) {
+        float2 pre = __ffma2_rn(w4[0][h], x0[h], bv[h]);
+        pre = __ffma2_rn(w4[1][h], x1[h], pre);
+        pre = __ffma2_rn(w4[2][h], x2[h], pre);
+        pre = __ffma2_rn(w4[3][h], x3[h], pre);
+        const float sx = 1.f / (1.f + expf(-pre.x)), sy = 1.f / (1.f + expf(-pre.y));
+        g3[h].x *= sx * (1.f + pre.x * (1.f - sx));
+        g3[h].y *= sy * (1.f + pre.y * (1.f - sy));
       }
-      // rows past the sequence arrive as zeros, so g3 = 0 there without a test
+    }
+    if (INNER || t < t_hi) {
 #pragma unroll
-      for (int h = 0; h < H; ++h) g3[h] = make_float2(to_f(gr.v[2 * h]), to_f(gr.v[2 * h + 1]));
-      if (d.silu) {
-#pragma unroll
-        for (int h = 0; h < H; ++h) {
-          float2 pre = __ffma2_rn(w4[0][h], x0[h], bv[h]);
-          pre = __ffma2_rn(w4[1][h], x1[h], pre);
-          pre = __ffma2_rn(w4[2][h], x2[h], pre);
-          pre = __ffma2_rn(w4[3][h], x3[h], pre);
-          const float sx = 1.f / (1.f + expf(-pre.x)), sy = 1.f / (1.f + expf(-pre.y));
-          g3[h].x *= sx * (1.f + pre.x * (1.f - sx));
-          g3[h].y *= sy * (1.f + pre.y * (1.f - sy));
-        }
+      for (int h = 0; h < H; ++h) {
+        dw[0][h] = __ffma2_rn(g3[h], x0[h], dw[0][h]);
+        dw[1][h] = __ffma2_rn(g3[h], x1[h], dw[1][h]);
+        dw[2][h] = __ffma2_rn(g3[h], x2[h], dw[2][h]);
+        dw[3][h] = __ffma2_rn(g3[h], x3[h], dw[3][h]);
+        db[h] = __fadd2_rn(db[h], g3[h]);
       }
-      if (t < t_hi) {
+    }
+    const int tau = t - 3;  // dx[tau] = sum_k w4[k] dyact[tau+3-k]
+    if (INNER || (tau >= t_lo && tau < t_hi)) {
+      float o[VEC];
 #pragma unroll
-        for (int h = 0; h < H; ++h) {
-          dw[0][h] = __ffma2_rn(g3[h], x0[h], dw[0][h]);
-          dw[1][h] = __ffma2_rn(g3[h], x1[h], dw[1][h]);
-          dw[2][h] = __ffma2_rn(g3[h], x2[h], dw[2][h]);
-          dw[3][h] = __ffma2_rn(g3[h], x3[h], dw[3][h]);
-          db[h] = __fadd2_rn(db[h], g3[h]);
-        }
+      for (int h = 0; h < H; ++h) {
+        float2 acc = __fmul2_rn(w4[0][h], g3[h]);
+        acc = __ffma2_rn(w4[1][h], g2[h], acc);
+        acc = __ffma2_rn(w4[2][h], g1[h], acc);
+        acc = __ffma2_rn(w4[3][h], g0[h], acc);
+        o[2 * h] = acc.x;
+        o[2 * h + 1] = acc.y;
       }
-      const int tau = t - 3;  // dx[tau] = sum_k w4[k] dyact[tau+3-k]
-      if (tau >= t_lo && tau < t_hi) {
-        float o[VEC];
-#pragma unroll
-        for (int h = 0; h < H; ++h) {
-          float2 acc = __fmul2_rn(w4[0][h], g3[h]);
-          acc = __ffma2_rn(w4[1][h], g2[h], acc);
-          acc = __ffma2_rn(w4[2][h], g1[h], acc);
-          acc = __ffma2_rn(w4[3][h], g0[h], acc);
-          o[2 * h] = acc.x;
-          o[2 * h + 1] = acc.y;
-        }
+      if (!INNER) {
         const int i = tau - d.T + (d.W - 1);  // position inside next_state, if any
         if (d_next && i >= 0) {
 #pragma unroll
           for (int e = 0; e < VEC; ++e) o[e] += to_f(d_next[((long long)b * d.C + c0 + e) * (d.W - 1) + i]);
         }
-        stv<T, VEC>(dx + ((long long)b * d.T + tau) * d.C + c0, o);
       }
+      stv<T, VEC>(dx + ((long long)b * d.T + tau) * d.C + c0, o);
+    }
 #pragma unroll
-      for (int h = 0; h < H; ++h) {
-        x0[h] = x1[h];
-        x1[h] = x2[h];
-        x2[h] = x3[h];
-        g0[h] = g1[h];
-        g1[h] = g2[h];
-        g2[h] = g3[h];
+    for (int h = 0; h < H; ++h) {
+      x0[h] = x1[h];
+      x1[h] = x2[h];
+      x2[h] = x3[h];
+      g0[h] = g1[h];
+      g1[h] = g2[h];
+      g2[h] = g3[h];
+    }
+  };
+  for (int grp = 0; grp < n_grp; ++grp) {
+    // the slot of group grp+R-1 is the one read in the previous iteration
+    SLX_CONV_ISSUE(grp + kConvRing - 1);
+    cp_async_wait<kConvRing - 1>();
+    const Slice *s = ring + (size_t)(grp % kConvRing) * G * 2 * kConvThreads;
+    const int tg = t_lo + grp * G;
+    if (grp * G >= 3 && tg + G <= t_hi) {
+#pragma unroll
+      for (int u = 0; u < G; ++u) row_step(std::true_type(), s, u, tg + u);
+    } else {
+#pragma unroll
+      for (int u = 0; u < G; ++u) {
+        if (tg + u >= t_end) break;
+        row_step(std::false_type(), s, u, tg + u);
       }
     }
   }
