@@ -6,10 +6,15 @@
 // which is how the mixer hands over the value slice of its input projection, so
 // no contiguous copy or transpose is ever made.
 //
-// One thread owns VEC adjacent channels (one 16-byte vector for half types) and
-// walks a tile of tokens with the last three inputs in registers: one vector
-// load and one vector store per channel-vector-token, i.e. the algorithmic
-// 4 bytes per channel-token forward and 6 backward for half types.
+// One thread owns VEC adjacent channels and walks a tile of tokens with the last three
+// inputs in registers: one vector load and one vector store per channel-vector-token, i.e.
+// the algorithmic 4 bytes per channel-token forward and 6 backward for half types.
+// The aligned kernels (*_staged_kernel) bring their rows from global to shared memory with
+// per-thread cp.async rings (every thread copies exactly the slices it reads, so there is
+// no barrier), test nothing per row in the interior of a tile, and the backward does its
+// arithmetic on channel pairs (fma.rn.f32x2) and sizes its tiles so that the grid is a
+// whole number of waves.  The plain kernels (*_kernel, one channel per thread) serve
+// unaligned inputs.
 #include <initializer_list>
 #include <type_traits>
 #include <mutex>
@@ -19,9 +24,9 @@
 namespace slx {
 
 constexpr int kConvThreads = 128;
-constexpr int kConvAhead = 8;      // rows each thread requests ahead of its walk (backward: x and dy)
-constexpr int kConvAheadFwd = 8;   // forward: x only (16 measured slower)
-constexpr int kConvVec = 4;    // channels per thread: 8-byte vectors of half types, 16-byte of fp32
+constexpr int kConvAhead = 8;      // plain kernels: rows each thread requests ahead of its walk (backward: x and dy)
+constexpr int kConvAheadFwd = 8;   // plain forward: x only
+constexpr int kConvVec = 4;    // staged backward: channels per thread (8-byte slices of half types, 16-byte of fp32)
 
 template <typename T, int VEC>
 __device__ __forceinline__ void ldv(const T *p, float (&v)[VEC]) {
@@ -380,18 +385,27 @@ __device__ __forceinline__ void cp_async_slice(void *smem_dst, const void *gsrc,
   else
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(gsrc), "r"(n) : "memory");
 }
+template <int BYTES>
+__device__ __forceinline__ void cp_async_slice_full(void *smem_dst, const void *gsrc) {
+  static_assert(BYTES == 8 || BYTES == 16, "slice of 8 or 16 bytes");
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+  if constexpr (BYTES == 16)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gsrc) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(gsrc) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <typename T, int VEC>
 constexpr int conv_group_rows() { return sizeof(RowSlice<T, VEC>) == 8 ? 8 : 4; }
-template <typename T, int VEC>
+template <typename T, int VEC, int RING = kConvRing>
 constexpr size_t conv_ring_bytes(int tensors) {
-  return (size_t)kConvRing * conv_group_rows<T, VEC>() * tensors * kConvThreads * sizeof(RowSlice<T, VEC>);
+  return (size_t)RING * conv_group_rows<T, VEC>() * tensors * kConvThreads * sizeof(RowSlice<T, VEC>);
 }
 
-template <typename T, int VEC>
+template <typename T, int VEC, int RING>
 __global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_staged_kernel(
     const T *__restrict__ x, const T *__restrict__ weight, const T *__restrict__ bias, const T *__restrict__ state,
     const T *__restrict__ dy, const T *__restrict__ d_next, T *__restrict__ dx, float *__restrict__ part, ConvDims d,
@@ -401,7 +415,7 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_staged_kernel(
   extern __shared__ __align__(16) unsigned char conv_ring[];
   const int c0 = (blockIdx.x * kConvThreads + threadIdx.x) * VEC;
   if (c0 >= d.C) return;
-  Slice *ring = reinterpret_cast<Slice *>(conv_ring) + threadIdx.x;  // [kConvRing*G rows][x, dy][thread]
+  Slice *ring = reinterpret_cast<Slice *>(conv_ring) + threadIdx.x;  // [RING*G rows][x, dy][thread]
   const int b = blockIdx.z;
   const int t_lo = blockIdx.y * tile, t_hi = min(d.T, t_lo + tile);
   const int t_end = min(d.T + 3, t_hi + 3);
@@ -410,22 +424,31 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_staged_kernel(
   const T *gb = dy + (long long)b * d.T * d.C + c0;
   // requests the rows of group grp (rows past the tile or the sequence are filled with zeros) and closes
   // the group; past the last group only the (empty) group is closed, which keeps the wait count uniform
+  const int t_lim = min(t_end, d.T);  // rows at or past it are not read
 #define SLX_CONV_ISSUE(grp_)                                                                                     \
   do {                                                                                                           \
     const int gi_ = (grp_);                                                                                      \
     if (gi_ < n_grp) {                                                                                           \
-      Slice *s_ = ring + (size_t)(gi_ % kConvRing) * G * 2 * kConvThreads;                                       \
-      _Pragma("unroll") for (int u_ = 0; u_ < G; ++u_) {                                                         \
-        const int t_ = t_lo + gi_ * G + u_;                                                                      \
-        const bool ok_ = t_ < t_end && t_ < d.T;                                                                 \
-        cp_async_slice<sizeof(Slice)>(s_ + (u_ * 2 + 0) * kConvThreads, ok_ ? xb + (long long)t_ * d.xs : x, ok_); \
-        cp_async_slice<sizeof(Slice)>(s_ + (u_ * 2 + 1) * kConvThreads, ok_ ? gb + (long long)t_ * d.C : dy, ok_); \
+      Slice *s_ = ring + (size_t)(gi_ % RING) * G * 2 * kConvThreads;                                       \
+      const int t0_ = t_lo + gi_ * G;                                                                            \
+      const T *px_ = xb + (long long)t0_ * d.xs, *pg_ = gb + (long long)t0_ * d.C;                               \
+      if (t0_ + G <= t_lim) {                                                                                    \
+        _Pragma("unroll") for (int u_ = 0; u_ < G; ++u_) {                                                       \
+          cp_async_slice_full<sizeof(Slice)>(s_ + (u_ * 2 + 0) * kConvThreads, px_ + (long long)u_ * d.xs);      \
+          cp_async_slice_full<sizeof(Slice)>(s_ + (u_ * 2 + 1) * kConvThreads, pg_ + (long long)u_ * d.C);       \
+        }                                                                                                        \
+      } else {                                                                                                   \
+        _Pragma("unroll") for (int u_ = 0; u_ < G; ++u_) {                                                       \
+          const bool ok_ = t0_ + u_ < t_lim;                                                                     \
+          cp_async_slice<sizeof(Slice)>(s_ + (u_ * 2 + 0) * kConvThreads, ok_ ? px_ + (long long)u_ * d.xs : x, ok_); \
+          cp_async_slice<sizeof(Slice)>(s_ + (u_ * 2 + 1) * kConvThreads, ok_ ? pg_ + (long long)u_ * d.C : dy, ok_); \
+        }                                                                                                        \
       }                                                                                                          \
     }                                                                                                            \
     cp_async_commit();                                                                                           \
   } while (0)
 #pragma unroll
-  for (int g = 0; g < kConvRing - 1; ++g) SLX_CONV_ISSUE(g);
+  for (int g = 0; g < RING - 1; ++g) SLX_CONV_ISSUE(g);
 
   // arithmetic on pairs of adjacent channels (fma.rn.f32x2: each half is the same IEEE fma as the scalar
   // kernel's, so the results are identical)
@@ -528,9 +551,9 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_staged_kernel(
   };
   for (int grp = 0; grp < n_grp; ++grp) {
     // the slot of group grp+R-1 is the one read in the previous iteration
-    SLX_CONV_ISSUE(grp + kConvRing - 1);
-    cp_async_wait<kConvRing - 1>();
-    const Slice *s = ring + (size_t)(grp % kConvRing) * G * 2 * kConvThreads;
+    SLX_CONV_ISSUE(grp + RING - 1);
+    cp_async_wait<RING - 1>();
+    const Slice *s = ring + (size_t)(grp % RING) * G * 2 * kConvThreads;
     const int tg = t_lo + grp * G;
     if (grp * G >= 3 && tg + G <= t_hi) {
 #pragma unroll
@@ -576,18 +599,24 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_fwd_staged_kernel(const 
   const int t_lo = blockIdx.y * tile, t_hi = min(d.T, t_lo + tile);
   const int n_grp = (t_hi - t_lo + G - 1) / G;
   const T *xb = x + (long long)b * d.xbs + c0;
-#define SLX_CONV_ISSUE(grp_)                                                                        \
-  do {                                                                                              \
-    const int gi_ = (grp_);                                                                         \
-    if (gi_ < n_grp) {                                                                              \
-      Slice *s_ = ring + (size_t)(gi_ % kConvRing) * G * kConvThreads;                              \
-      _Pragma("unroll") for (int u_ = 0; u_ < G; ++u_) {                                            \
-        const int t_ = t_lo + gi_ * G + u_;                                                         \
-        const bool ok_ = t_ < t_hi;                                                                 \
-        cp_async_slice<sizeof(Slice)>(s_ + u_ * kConvThreads, ok_ ? xb + (long long)t_ * d.xs : x, ok_); \
-      }                                                                                             \
-    }                                                                                               \
-    cp_async_commit();                                                                              \
+#define SLX_CONV_ISSUE(grp_)                                                                                  \
+  do {                                                                                                        \
+    const int gi_ = (grp_);                                                                                   \
+    if (gi_ < n_grp) {                                                                                        \
+      Slice *s_ = ring + (size_t)(gi_ % kConvRing) * G * kConvThreads;                                        \
+      const int t0_ = t_lo + gi_ * G;                                                                         \
+      const T *px_ = xb + (long long)t0_ * d.xs;                                                              \
+      if (t0_ + G <= t_hi) {                                                                                  \
+        _Pragma("unroll") for (int u_ = 0; u_ < G; ++u_)                                                      \
+            cp_async_slice_full<sizeof(Slice)>(s_ + u_ * kConvThreads, px_ + (long long)u_ * d.xs);           \
+      } else {                                                                                                \
+        _Pragma("unroll") for (int u_ = 0; u_ < G; ++u_) {                                                    \
+          const bool ok_ = t0_ + u_ < t_hi;                                                                   \
+          cp_async_slice<sizeof(Slice)>(s_ + u_ * kConvThreads, ok_ ? px_ + (long long)u_ * d.xs : x, ok_);   \
+        }                                                                                                     \
+      }                                                                                                       \
+    }                                                                                                         \
+    cp_async_commit();                                                                                        \
   } while (0)
 #pragma unroll
   for (int g = 0; g < kConvRing - 1; ++g) SLX_CONV_ISSUE(g);
@@ -598,32 +627,41 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_fwd_staged_kernel(const 
   load_cat<T, VEC>(x, state, d, b, t_lo - 3, c0, x0);
   load_cat<T, VEC>(x, state, d, b, t_lo - 2, c0, x1);
   load_cat<T, VEC>(x, state, d, b, t_lo - 1, c0, x2);
+  auto row_step = [&](const Slice *s, int u, T *yrow) {
+    Slice xr;
+    ld_raw<T, VEC>(s[u * kConvThreads].v, xr);
+    float o[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      x3[e] = to_f(xr.v[e]);
+      float acc = bv[e];
+      acc = fmaf(w4[0][e], x0[e], acc);
+      acc = fmaf(w4[1][e], x1[e], acc);
+      acc = fmaf(w4[2][e], x2[e], acc);
+      acc = fmaf(w4[3][e], x3[e], acc);
+      if (d.silu) acc = acc / (1.f + expf(-acc));
+      o[e] = acc;
+      x0[e] = x1[e];
+      x1[e] = x2[e];
+      x2[e] = x3[e];
+    }
+    stv<T, VEC>(yrow, o);
+  };
+  T *yb = y + ((long long)b * d.T + t_lo) * d.C + c0;
   for (int grp = 0; grp < n_grp; ++grp) {
     SLX_CONV_ISSUE(grp + kConvRing - 1);  // into the slot read in the previous iteration
     cp_async_wait<kConvRing - 1>();
     const Slice *s = ring + (size_t)(grp % kConvRing) * G * kConvThreads;
+    T *yg = yb + (long long)grp * G * d.C;
+    if (t_lo + (grp + 1) * G <= t_hi) {  // whole group inside the tile: no per-row test
 #pragma unroll
-    for (int u = 0; u < G; ++u) {
-      const int t = t_lo + grp * G + u;
-      if (t >= t_hi) break;
-      Slice xr;
-      ld_raw<T, VEC>(s[u * kConvThreads].v, xr);
-      float o[VEC];
+      for (int u = 0; u < G; ++u) row_step(s, u, yg + (long long)u * d.C);
+    } else {
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) {
-        x3[e] = to_f(xr.v[e]);
-        float acc = bv[e];
-        acc = fmaf(w4[0][e], x0[e], acc);
-        acc = fmaf(w4[1][e], x1[e], acc);
-        acc = fmaf(w4[2][e], x2[e], acc);
-        acc = fmaf(w4[3][e], x3[e], acc);
-        if (d.silu) acc = acc / (1.f + expf(-acc));
-        o[e] = acc;
-        x0[e] = x1[e];
-        x1[e] = x2[e];
-        x2[e] = x3[e];
+      for (int u = 0; u < G; ++u) {
+        if (t_lo + grp * G + u >= t_hi) break;
+        row_step(s, u, yg + (long long)u * d.C);
       }
-      stv<T, VEC>(y + ((long long)b * d.T + t) * d.C + c0, o);
     }
   }
   cp_async_wait<0>();
@@ -761,9 +799,11 @@ int slx_cconv1d_fwd(const slx_conv_shape *s, const void *x, const void *weight, 
     constexpr int VFULL = kConvVec;
     const T_ *xp = (const T_ *)x, *wp = (const T_ *)weight, *bp = (const T_ *)bias, *sp = (const T_ *)state;
     if (conv_vec_ok<T_>(s, {x, y})) {
-      const int nblk = (d.C / VFULL + kConvThreads - 1) / kConvThreads;
-      constexpr size_t ring = conv_ring_bytes<T_, VFULL>(1);
-      auto kern = cconv1d_fwd_staged_kernel<T_, VFULL>;
+      // 16-byte slices (8 channels of a half type): fewer instructions per channel than the backward's 8-byte ones
+      constexpr int VW = 16 / (int)sizeof(T_);
+      const int nblk = (d.C / VW + kConvThreads - 1) / kConvThreads;
+      constexpr size_t ring = conv_ring_bytes<T_, VW>(1);
+      auto kern = cconv1d_fwd_staged_kernel<T_, VW>;
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
       SLX_REQUIRE(e == cudaSuccess, (int)e, "cconv1d_fwd: shared memory attribute: %s", cudaGetErrorString(e));
       const int tile = conv_tile(d.T, false);  // growing the tile to whole waves measured no faster here
@@ -809,7 +849,7 @@ int slx_cconv1d_bwd(const slx_conv_shape *s, const void *x, const void *weight, 
     if (conv_vec_ok<T_>(s, {x, dy, dx})) {
       const int nblk = (d.C / VFULL + kConvThreads - 1) / kConvThreads;
       constexpr size_t ring = conv_ring_bytes<T_, VFULL>(2);
-      auto kern = cconv1d_bwd_staged_kernel<T_, VFULL>;
+      auto kern = cconv1d_bwd_staged_kernel<T_, VFULL, kConvRing>;
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
       SLX_REQUIRE(e == cudaSuccess, (int)e, "cconv1d_bwd: shared memory attribute: %s", cudaGetErrorString(e));
       const int tile = conv_tile_balanced(d.T, kConvTileBwd, (long)nblk * d.batch, conv_slots(kern, ring));
