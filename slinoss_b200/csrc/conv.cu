@@ -374,6 +374,7 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_kernel(
 // are tracked per thread (commit_group / wait_group).  The ring holds kConvRing groups of G rows; while
 // one group is consumed, kConvRing-1 groups are in flight, without holding registers for them.
 constexpr int kConvRing = 4;
+constexpr int kConvRingFwd = 6;  // forward (one tensor in the ring): 4 measured 3 % slower, 8 slower than 4
 
 template <int BYTES>
 __device__ __forceinline__ void cp_async_slice(void *smem_dst, const void *gsrc, bool valid) {
@@ -582,7 +583,7 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_bwd_staged_kernel(
   conv_bwd_partials<VEC>(part, d.C, b, c0, dwf, dbf);
 }
 
-template <typename T, int VEC>
+template <typename T, int VEC, int RING>
 __global__ void __launch_bounds__(kConvThreads) cconv1d_fwd_staged_kernel(const T *__restrict__ x,
                                                                           const T *__restrict__ weight,
                                                                           const T *__restrict__ bias,
@@ -594,7 +595,7 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_fwd_staged_kernel(const 
   extern __shared__ __align__(16) unsigned char conv_ring[];
   const int c0 = (blockIdx.x * kConvThreads + threadIdx.x) * VEC;
   if (c0 >= d.C) return;
-  Slice *ring = reinterpret_cast<Slice *>(conv_ring) + threadIdx.x;  // [kConvRing*G rows][thread]
+  Slice *ring = reinterpret_cast<Slice *>(conv_ring) + threadIdx.x;  // [RING*G rows][thread]
   const int b = blockIdx.z;
   const int t_lo = blockIdx.y * tile, t_hi = min(d.T, t_lo + tile);
   const int n_grp = (t_hi - t_lo + G - 1) / G;
@@ -603,7 +604,7 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_fwd_staged_kernel(const 
   do {                                                                                                        \
     const int gi_ = (grp_);                                                                                   \
     if (gi_ < n_grp) {                                                                                        \
-      Slice *s_ = ring + (size_t)(gi_ % kConvRing) * G * kConvThreads;                                        \
+      Slice *s_ = ring + (size_t)(gi_ % RING) * G * kConvThreads;                                        \
       const int t0_ = t_lo + gi_ * G;                                                                         \
       const T *px_ = xb + (long long)t0_ * d.xs;                                                              \
       if (t0_ + G <= t_hi) {                                                                                  \
@@ -619,7 +620,7 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_fwd_staged_kernel(const 
     cp_async_commit();                                                                                        \
   } while (0)
 #pragma unroll
-  for (int g = 0; g < kConvRing - 1; ++g) SLX_CONV_ISSUE(g);
+  for (int g = 0; g < RING - 1; ++g) SLX_CONV_ISSUE(g);
 
   float w4[4][VEC], bv[VEC];
   load_taps<T, VEC>(weight, bias, d, c0, w4, bv);
@@ -649,9 +650,9 @@ __global__ void __launch_bounds__(kConvThreads) cconv1d_fwd_staged_kernel(const 
   };
   T *yb = y + ((long long)b * d.T + t_lo) * d.C + c0;
   for (int grp = 0; grp < n_grp; ++grp) {
-    SLX_CONV_ISSUE(grp + kConvRing - 1);  // into the slot read in the previous iteration
-    cp_async_wait<kConvRing - 1>();
-    const Slice *s = ring + (size_t)(grp % kConvRing) * G * kConvThreads;
+    SLX_CONV_ISSUE(grp + RING - 1);  // into the slot read in the previous iteration
+    cp_async_wait<RING - 1>();
+    const Slice *s = ring + (size_t)(grp % RING) * G * kConvThreads;
     T *yg = yb + (long long)grp * G * d.C;
     if (t_lo + (grp + 1) * G <= t_hi) {  // whole group inside the tile: no per-row test
 #pragma unroll
@@ -802,8 +803,8 @@ int slx_cconv1d_fwd(const slx_conv_shape *s, const void *x, const void *weight, 
       // 16-byte slices (8 channels of a half type): fewer instructions per channel than the backward's 8-byte ones
       constexpr int VW = 16 / (int)sizeof(T_);
       const int nblk = (d.C / VW + kConvThreads - 1) / kConvThreads;
-      constexpr size_t ring = conv_ring_bytes<T_, VW>(1);
-      auto kern = cconv1d_fwd_staged_kernel<T_, VW>;
+      constexpr size_t ring = conv_ring_bytes<T_, VW, kConvRingFwd>(1);
+      auto kern = cconv1d_fwd_staged_kernel<T_, VW, kConvRingFwd>;
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
       SLX_REQUIRE(e == cudaSuccess, (int)e, "cconv1d_fwd: shared memory attribute: %s", cudaGetErrorString(e));
       const int tile = conv_tile(d.T, false);  // growing the tile to whole waves measured no faster here
