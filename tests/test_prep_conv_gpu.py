@@ -181,6 +181,37 @@ def test_conv_seeded_vs_oracle(dtype, b, T, C, W, with_state):
         assert rel_err(_np(grads[3]), dso) < tol
 
 
+def test_conv_ragged_shapes_vs_oracle():
+    """Seeded sweep over short and odd sequence lengths (around the copy-group and tile edges), channel counts
+    that fill a block partly, every width, with and without state and SiLU, all three dtypes."""
+    import slinoss_b200 as sb
+
+    rng = np.random.default_rng(0)
+    lengths = [1, 2, 3, 4, 5, 7, 8, 9, 15, 16, 17, 31, 33, 63, 64, 65, 127, 129, 131, 200, 257]
+    for it in range(60):
+        dtype = [torch.bfloat16, torch.float16, torch.float32][it % 3]
+        b, T = int(rng.integers(1, 4)), int(rng.choice(lengths))
+        C, W = int(rng.choice([8, 16, 24, 40, 64, 520, 1032])), int(rng.integers(2, 5))
+        silu, with_state = bool(rng.integers(0, 2)), bool(rng.integers(0, 2))
+        gen = torch.Generator().manual_seed(it)
+        x = torch.randn(b, T, C, generator=gen).to(dtype).cuda().requires_grad_(True)
+        w = (0.5 * torch.randn(C, W, generator=gen)).to(dtype).cuda().requires_grad_(True)
+        bias = (0.5 * torch.randn(C, generator=gen)).to(dtype).cuda().requires_grad_(True)
+        st = torch.randn(b, C, W - 1, generator=gen).to(dtype).cuda().requires_grad_(True) if with_state else None
+        y, nxt = sb.cconv1d_b200(x, w, bias, st, activation="silu" if silu else None)
+        dy = torch.randn(b, T, C, generator=gen).to(dtype).cuda()
+        dn = torch.randn(b, C, W - 1, generator=gen).to(dtype).cuda()
+        leaves = [x, w, bias] + ([st] if st is not None else [])
+        grads = torch.autograd.grad([y, nxt], leaves, [dy, dn])
+        so = None if st is None else _np(st)
+        yo, nxo, _ = oprep.cconv1d_fwd(_np(x), _np(w), _np(bias), so, silu=silu)
+        outs = oprep.cconv1d_bwd(_np(x), _np(w), _np(bias), so, _np(dy), d_next_state=_np(dn), silu=silu)
+        tol = 6e-3 if dtype != torch.float32 else 5e-6
+        errs = [rel_err(_np(y), yo), rel_err(_np(nxt), nxo)]
+        errs += [rel_err(_np(g), o) for g, o in zip(grads, outs)]
+        assert max(errs) < tol, (it, dtype, b, T, C, W, silu, with_state, errs)
+
+
 def test_backends_on_a_fake_owner():
     """The backend objects read only attributes of their owner, like the
     reference's fakes in tests/test_mixer.py:18-74."""
