@@ -413,7 +413,7 @@ def main() -> int:
     b, h, T, P, N = cfg["batch"], cfg["heads"], cfg["T"], cfg["P"], cfg["N"]
     D, BH, NC = 2 * N, b * h, (T + L - 1) // L
     lib = _lib.lib()
-    shape = _lib.ScanShape(BH, T, P, N, L, _lib.dtype_code(dtype))
+    shape = _lib.scan_shape(BH, T, P, N, L, dtype)
     st = _lib.stream_ptr(dev)
     f32 = dict(device=dev, dtype=torch.float32)
     with torch.no_grad():

@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define SLX_ABI_VERSION 3
+#define SLX_ABI_VERSION 4
 
 typedef enum { SLX_F32 = 0, SLX_BF16 = 1, SLX_F16 = 2 } slx_dtype;
 
@@ -59,11 +59,19 @@ typedef struct {
   int32_t N;           /* complex state pairs; D = 2N                      */
   int32_t chunk;       /* chunk length L: multiple of 16, 16..128          */
   int32_t dtype;       /* slx_dtype of U, B, C, Y and their gradients      */
+  int32_t starts_dtype; /* slx_dtype of chunk_starts and d_inc.  It also names the
+                         * kernel family: the activation dtype = tcgen05 kernels
+                         * (half inputs, chunk 128, P 64, 2N in {64,..,256} only),
+                         * SLX_F32 = fp32-exact CUDA-core kernels.  Every call of
+                         * one forward/backward pair must pass the same value;
+                         * slx_scan_starts_dtype() gives the recommended one.   */
 } slx_scan_shape;
 
 int slx_abi_version(void);
 
-/* slx_dtype in which the stages of this shape exchange chunk_starts and d_inc. */
+/* Recommended starts_dtype for this shape (the field itself is not read): the
+ * activation dtype where the tensor-core kernels cover the shape, SLX_F32
+ * otherwise or after slx_set_tensor_path(0). */
 int slx_scan_starts_dtype(const slx_scan_shape *s);
 const char *slx_last_error_string(void);
 
@@ -187,6 +195,29 @@ int slx_v2x2ssd_bwd_finish(const slx_scan_shape *s, const void *U, const float *
                            float *dB_prev /*[opt]*/, float *dU_prev /*[opt]*/,
                            void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- segment chaining across devices (no counterpart in the reference) ------ */
+
+/* A segment of a sequence acts on the incoming scan state as z_out = m_seg * z_in + f
+ * (m_seg one complex number per batch*head, f one state).  When the segments live on
+ * different devices, every device gathers all (m_seg, f) pairs and folds the ones in
+ * front of it (forward) or behind it (backward, conj != 0 conjugates the transitions):
+ *   out = offsets[0];  for j = 1 .. count-1:  out = m[j] * out + offsets[j]
+ * offsets: `count` states (BH,P,2N) fp32, slice j at offsets + j*slice_stride elements;
+ * m: transitions (BH,2) fp32, slice j at m + j*m_stride elements (m[0] is not read).
+ * Strides may be negative (the backward chain walks the gathered buffer downwards). */
+int slx_segment_fold(int32_t batch_heads, int32_t P, int32_t N, int32_t count,
+                     const float *offsets, int64_t slice_stride, const float *m,
+                     int64_t m_stride, int32_t conj, float *out, void *stream);
+
+/* out = m * z + f (conj != 0: conj(m) * z + f) for one segment. */
+int slx_segment_axpy(int32_t batch_heads, int32_t P, int32_t N, const float *m,
+                     const float *z, const float *f, int32_t conj, float *out,
+                     void *stream);
+
+/* m_seg (BH,2) = product over the chunks of m_chunk (BH,NC,2). */
+int slx_segment_transition(int32_t batch_heads, int32_t n_chunks, const float *m_chunk,
+                           float *m_seg, void *stream);
+
 /* ---- scan preparation ---------------------------------------------------- */
 
 typedef struct {
@@ -267,6 +298,16 @@ int slx_cconv1d_fwd(const slx_conv_shape *s, const void *x, const void *weight,
                     const void *bias, const void *state, void *y,
                     void *next_state, void *stream);
 
+/* One decode token of the same convolution: replaces
+ * csrc/causal_conv1d/causal_conv1d_update.cu:25 causal_conv1d_update_kernel as the mixer
+ * uses it (slinoss/layers/mixer.py:614 _apply_causal_depthwise_conv_step).  s->T must be 1;
+ * x (b,C) with batch stride s->x_batch_stride, state (b,C,W-1) [opt = zeros] ->
+ * y (b,C) = act(bias + w . [state, x]), next_state (b,C,W-1) [opt] = [state[1:], x].
+ * next_state may be state (in-place rolling update). */
+int slx_cconv1d_update(const slx_conv_shape *s, const void *x, const void *weight,
+                       const void *bias, const void *state, void *y,
+                       void *next_state, void *stream);
+
 size_t slx_cconv1d_bwd_workspace_bytes(const slx_conv_shape *s);
 
 /* Replaces causal_conv1d.cpp:261 causal_conv1d_bwd.  dy (b,T,C) contiguous,
@@ -308,30 +349,20 @@ int slx_cconv1d_bwd_noalloc(const slx_conv_shape *s, const void *x,
  * previous setting.  (Process-wide switch for tests; no reference counterpart.) */
 int slx_set_tensor_path(int enable);
 
-/* Synchronising read-and-clear of the device status word of the tensor-core
- * kernels: *host_out != 0 means a bounded wait on an MMA completion barrier ran
- * out and the affected launch produced undefined values. */
+/* Synchronising read-and-clear (one atomic exchange on the device) of the status
+ * word of the tensor-core kernels on the CURRENT device: *host_out != 0 means a
+ * bounded wait on a completion barrier ran out in some launch since the last read;
+ * the outputs of the affected chunks were filled with NaN.  One word per device,
+ * shared by all streams and threads. */
 int slx_read_tc_status(int *host_out);
 
-/* Synchronising read-and-clear of the scan's input status word: *host_out != 0
+/* Synchronising read-and-clear (one atomic exchange, current device, one word per
+ * device) of the scan's input status word: *host_out != 0
  * means some launch since the last read met a transition M of magnitude exactly 0.
  * The reference raises for such input (reference.py:480-485: the log-magnitude /
  * phase split does not exist); these kernels cannot raise from the device, so they
  * set this word and fill the affected chunk and everything downstream with NaN. */
 int slx_read_scan_status(int *host_out);
-
-/* Diagnostic (synchronising): 64 clock64() stamps written by CTA (0,0) of the
- * last tensor-core backward launch at its phase boundaries. */
-int slx_read_phase_clock(long long *host_out64);
-
-/* Self-test of the tcgen05 tile engine (no counterpart in the reference): one
- * CTA computes a small bf16 product with fp32 accumulation in tensor memory.
- * mode 0: C[128x128] = A[128x64] B[128x64]^T;  mode 1: C[128x64] = A[128x128]
- * B[128x64];  mode 2: C[128x64] = A[128x128]^T B[128x64];  mode 3: C[128x64] =
- * A[128x64] B[64x64]^T.  A, B row-major bf16; *status (device int) becomes 1 if
- * a bounded wait ran out. */
-int slx_umma_selftest(int mode, const void *A, const void *B, float *C,
-                      int *status, void *stream);
 
 #ifdef __cplusplus
 }

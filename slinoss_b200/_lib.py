@@ -22,7 +22,7 @@ _DTYPE_CODE = {torch.float32: SLX_F32, torch.bfloat16: SLX_BF16, torch.float16: 
 
 class ScanShape(Structure):
     _fields_ = [("batch_heads", c_int32), ("T", c_int32), ("P", c_int32), ("N", c_int32),
-                ("chunk", c_int32), ("dtype", c_int32)]
+                ("chunk", c_int32), ("dtype", c_int32), ("starts_dtype", c_int32)]
 
 
 class PrepShape(Structure):
@@ -70,15 +70,39 @@ SIGNATURES = {
     "slx_set_tensor_path": (c_int32, [c_int32]),
     "slx_read_tc_status": (c_int32, [POINTER(c_int32)]),
     "slx_read_scan_status": (c_int32, [POINTER(c_int32)]),
-    "slx_read_phase_clock": (c_int32, [POINTER(c_int64)]),
-    "slx_umma_selftest": (c_int32, [c_int32] + [_P] * 5),
     "slx_decode_step": (c_int32, [POINTER(DecodeShape)] + [_P] * 15),
     "slx_cconv1d_fwd": (c_int32, [POINTER(ConvShape)] + [_P] * 7),
+    "slx_cconv1d_update": (c_int32, [POINTER(ConvShape)] + [_P] * 7),
+    "slx_segment_fold": (c_int32, [c_int32] * 4 + [_P, c_int64, _P, c_int64, c_int32, _P, _P]),
+    "slx_segment_axpy": (c_int32, [c_int32] * 3 + [_P] * 3 + [c_int32, _P, _P]),
+    "slx_segment_transition": (c_int32, [c_int32] * 2 + [_P] * 3),
     "slx_cconv1d_bwd_workspace_bytes": (c_size_t, [POINTER(ConvShape)]),
     "slx_cconv1d_bwd": (c_int32, [POINTER(ConvShape)] + [_P] * 11 + [c_size_t, _P]),
 }
 
+SELFTEST_LIB_PATH = LIB_PATH.with_name("libslinoss_b200_selftest.so")
+SELFTEST_SIGNATURES = {
+    "slx_umma_selftest": (c_int32, [c_int32] + [_P] * 5),
+    "slx_selftest_last_error_string": (c_char_p, []),
+}
+
 _lib: Optional[ctypes.CDLL] = None
+_selftest: Optional[ctypes.CDLL] = None
+
+
+def selftest_lib() -> ctypes.CDLL:
+    """The test-only library (tile-engine self-test); never loaded by the ops."""
+    global _selftest
+    if _selftest is None:
+        if not SELFTEST_LIB_PATH.exists():
+            raise RuntimeError(f"{SELFTEST_LIB_PATH} is missing: run slinoss_b200.build.build_selftest().")
+        handle = ctypes.CDLL(str(SELFTEST_LIB_PATH))
+        for name, (res, args) in SELFTEST_SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _selftest = handle
+    return _selftest
 
 
 def lib() -> ctypes.CDLL:
@@ -108,10 +132,20 @@ def dtype_code(dt: torch.dtype) -> int:
 _CODE_DTYPE = {v: k for k, v in _DTYPE_CODE.items()}
 
 
+def scan_shape(batch_heads: int, T: int, P: int, N: int, chunk: int, dtype: torch.dtype,
+               starts: Optional[torch.dtype] = None) -> "ScanShape":
+    """Shape struct of the scan entry points.  ``starts`` is the dtype of ``chunk_starts`` /
+    ``d_inc`` and with it the kernel family (activation dtype: tcgen05 kernels, fp32: exact
+    kernels); ``None`` takes the library's recommendation for the shape."""
+    s = ScanShape(batch_heads, T, P, N, chunk, dtype_code(dtype), SLX_F32)
+    s.starts_dtype = (int(lib().slx_scan_starts_dtype(ctypes.byref(s))) if starts is None
+                      else dtype_code(starts))
+    return s
+
+
 def starts_dtype(shape: "ScanShape") -> torch.dtype:
-    """dtype in which the stages of this shape exchange chunk_starts (the activation dtype where
-    the tensor-core kernels run, fp32 otherwise)."""
-    return _CODE_DTYPE[int(lib().slx_scan_starts_dtype(ctypes.byref(shape)))]
+    """dtype in which the stages of this shape exchange chunk_starts."""
+    return _CODE_DTYPE[int(shape.starts_dtype)]
 
 
 def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -120,6 +154,48 @@ def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 def stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
+
+
+class guard:
+    """Make ``device`` the current CUDA device around a library call.
+
+    The library launches on the current device of the calling thread, so every call is wrapped
+    in this guard with the device of the tensors it is given: a model that lives on ``cuda:1``
+    while ``cuda:0`` is current still launches on ``cuda:1``.  A no-op when the device is
+    already current."""
+
+    __slots__ = ("device", "ctx")
+
+    def __init__(self, device) -> None:
+        self.device = torch.device(device)
+        self.ctx = None
+
+    def __enter__(self):
+        d = self.device
+        if d.type != "cuda":
+            raise ValueError(f"slinoss_b200 kernels need CUDA tensors; got device {d}.")
+        idx = d.index
+        if idx is not None and idx != torch.cuda.current_device():
+            self.ctx = torch.cuda.device(idx)
+            self.ctx.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            ctx, self.ctx = self.ctx, None
+            return ctx.__exit__(*exc)
+        return False
+
+
+def same_device(*tensors) -> torch.device:
+    """Device shared by every given tensor (``None`` entries are skipped); raises the reference's
+    error when they differ (slinoss/ops/v2x2ssd/reference.py:133-137)."""
+    devs = [t.device for t in tensors if t is not None]
+    if not devs:
+        raise ValueError("no tensor given")
+    if any(d != devs[0] for d in devs):
+        raise ValueError(f"All inputs must be on the same device. Got {devs}.")
+    return devs[0]
 
 
 def check(status: int, what: str) -> None:
@@ -140,17 +216,27 @@ def set_tensor_path(enable: bool) -> bool:
     return bool(lib().slx_set_tensor_path(1 if enable else 0))
 
 
-def read_scan_status() -> int:
-    """Synchronising read-and-clear of the scan's input status word (non-zero: some launch
-    since the last read met a transition of magnitude exactly 0 and produced NaN)."""
+def _status_device(device) -> torch.device:
+    return torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+
+
+def read_scan_status(device=None) -> int:
+    """Synchronising read-and-clear (one atomic exchange on the device) of the scan's input
+    status word of ``device`` (default: the current device).  Non-zero: some launch on that
+    device since the last read met a transition of magnitude exactly 0 and produced NaN.
+    The word is one per device, shared by every stream and thread that uses the device."""
     out = c_int32(0)
-    check(lib().slx_read_scan_status(ctypes.byref(out)), "read_scan_status")
+    with guard(_status_device(device)):
+        check(lib().slx_read_scan_status(ctypes.byref(out)), "read_scan_status")
     return int(out.value)
 
 
-def read_tc_status() -> int:
-    """Synchronising read-and-clear of the tensor-core kernels' status word
-    (non-zero: a bounded completion wait ran out)."""
+def read_tc_status(device=None) -> int:
+    """Synchronising read-and-clear (one atomic exchange on the device) of the tensor-core
+    kernels' status word of ``device`` (default: the current device).  Non-zero: a bounded
+    completion wait ran out in some launch on that device since the last read; the outputs of
+    the affected chunks were filled with NaN."""
     out = c_int32(0)
-    check(lib().slx_read_tc_status(ctypes.byref(out)), "read_tc_status")
+    with guard(_status_device(device)):
+        check(lib().slx_read_tc_status(ctypes.byref(out)), "read_tc_status")
     return int(out.value)

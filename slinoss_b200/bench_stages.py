@@ -79,7 +79,7 @@ def scan_stages(b, h, T, P, N, L, dtype):
     C = (torch.randn((b, h, T, D), generator=g) / math.sqrt(N)).to(dtype).to(dev)
     dY = torch.randn((b, h, T, P), generator=g).to(dtype).to(dev)
     lib, st = _lib.lib(), _lib.stream_ptr(dev)
-    s = _lib.ScanShape(BH, T, P, N, L, _lib.dtype_code(dtype))
+    s = _lib.scan_shape(BH, T, P, N, L, dtype)
     f32 = dict(device=dev, dtype=torch.float32)
     inc = torch.empty((b, h, NC, P, D), **f32)
     starts = torch.empty(inc.shape, device=dev, dtype=_lib.starts_dtype(s))

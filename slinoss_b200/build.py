@@ -4,7 +4,8 @@
 with nvcc for ``sm_100a`` and links one C-ABI shared library,
 ``_C/libslinoss_b200.so``, whose exports are declared in
 ``include/slinoss_b200.h``.  There is no JIT and no fallback: importing the ops
-without this library raises.
+without this library raises.  ``build_selftest()`` builds ``csrc/selftest/*.cu`` into a
+second, test-only library (``include/slinoss_b200_selftest.h``) that the product never loads.
 """
 
 from __future__ import annotations
@@ -19,6 +20,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OUT_DIR = PKG / "_C"
 LIB = OUT_DIR / "libslinoss_b200.so"
+SELFTEST_LIB = OUT_DIR / "libslinoss_b200_selftest.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -31,17 +33,16 @@ def _nvcc() -> str:
     return cand if Path(cand).exists() else "nvcc"
 
 
-def _newest_source_mtime() -> float:
-    files = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.inc")) + [PKG.parent / "include" / "slinoss_b200.h"]
-    return max(f.stat().st_mtime for f in files)
+def _headers():
+    inc = PKG.parent / "include"
+    return (list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.inc")) + list(inc.glob("*.h")))
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def _compile_and_link(sources, lib: Path, force: bool, verbose: bool) -> Path:
     OUT_DIR.mkdir(exist_ok=True)
-    if not force and LIB.exists() and LIB.stat().st_mtime >= _newest_source_mtime():
-        return LIB
-    sources = sorted(CSRC.glob("*.cu"))
-    objs = []
+    newest = max(f.stat().st_mtime for f in list(sources) + _headers())
+    if not force and lib.exists() and lib.stat().st_mtime >= newest:
+        return lib
 
     def compile_one(src: Path) -> Path:
         obj = OUT_DIR / (src.stem + ".o")
@@ -58,15 +59,26 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, len(sources))) as ex:
         objs = list(ex.map(compile_one, sources))
-    tmp = OUT_DIR / f"libslinoss_b200.{os.getpid()}.tmp.so"
+    tmp = OUT_DIR / f"{lib.stem}.{os.getpid()}.tmp.so"
     cmd = [_nvcc(), "-shared", "-o", str(tmp), *map(str, objs), "-gencode",
            "arch=compute_100a,code=sm_100a"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    os.replace(tmp, LIB)
-    return LIB
+    os.replace(tmp, lib)
+    return lib
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """The product library: every ``csrc/*.cu``."""
+    return _compile_and_link(sorted(CSRC.glob("*.cu")), LIB, force, verbose)
+
+
+def build_selftest(force: bool = False, verbose: bool = False) -> Path:
+    """The test-only library: every ``csrc/selftest/*.cu``."""
+    return _compile_and_link(sorted((CSRC / "selftest").glob("*.cu")), SELFTEST_LIB, force, verbose)
 
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_selftest(force="--force" in sys.argv, verbose="-v" in sys.argv))

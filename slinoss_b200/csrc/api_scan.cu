@@ -5,6 +5,7 @@
 #include <type_traits>
 
 #include <initializer_list>
+#include <mutex>
 
 #include "scan_simt.cuh"
 #include "scan_tc.cuh"
@@ -13,30 +14,10 @@
 
 namespace slx {
 
-static thread_local char g_err[512] = "";
-
-void set_error(const char *fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_err, sizeof(g_err), fmt, ap);
-  va_end(ap);
-}
-
-int fail(int code, const char *fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_err, sizeof(g_err), fmt, ap);
-  va_end(ap);
-  return code;
-}
-
-int check_launch(const char *what) {
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) {
-    set_error("%s: %s", what, cudaGetErrorString(e));
-    return (int)e;
-  }
-  return SLX_OK;
+// shapes the tcgen05 kernels cover
+static bool tc_capable(const slx_scan_shape *s) {
+  return (s->dtype == SLX_BF16 || s->dtype == SLX_F16) && s->chunk == 128 && s->P == 64 && s->N % 32 == 0 &&
+         s->N >= 32 && s->N <= 128;
 }
 
 static int check_shape(const slx_scan_shape *s, ScanDims *d) {
@@ -50,6 +31,11 @@ static int check_shape(const slx_scan_shape *s, ScanDims *d) {
   SLX_REQUIRE(s->dtype == SLX_F32 || s->dtype == SLX_BF16 || s->dtype == SLX_F16, SLX_E_DTYPE, "bad dtype %d",
               s->dtype);
   SLX_REQUIRE(s->batch_heads <= 65535, SLX_E_UNSUPPORTED, "batch_heads=%d exceeds 65535", s->batch_heads);
+  SLX_REQUIRE(s->starts_dtype == SLX_F32 || s->starts_dtype == s->dtype, SLX_E_DTYPE,
+              "starts_dtype %d must be fp32 or the activation dtype %d", s->starts_dtype, s->dtype);
+  SLX_REQUIRE(s->starts_dtype == SLX_F32 || tc_capable(s), SLX_E_UNSUPPORTED,
+              "half-precision chunk_starts select the tensor-core kernels, which need half inputs, chunk 128, "
+              "P 64 and 2N in {64,128,192,256} (got chunk %d P %d N %d)", s->chunk, s->P, s->N);
   d->BH = s->batch_heads;
   d->T = s->T;
   d->P = s->P;
@@ -62,12 +48,7 @@ static int check_shape(const slx_scan_shape *s, ScanDims *d) {
 
 template <typename K>
 static int set_smem(K kernel, size_t bytes) {
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-  if (e != cudaSuccess) {
-    set_error("cudaFuncSetAttribute(%zu bytes): %s", bytes, cudaGetErrorString(e));
-    return (int)e;
-  }
-  return SLX_OK;
+  return ensure_dyn_smem(kernel, bytes);
 }
 
 #define SLX_DISPATCH_L(Lval, ...)            \
@@ -133,10 +114,10 @@ static bool all_aligned16(std::initializer_list<const void *> ptrs) {
 #define SLX_REQUIRE_ALIGNED(what, ...) \
   SLX_REQUIRE(all_aligned16({__VA_ARGS__}), SLX_E_UNSUPPORTED, what ": tensor pointers must be 16-byte aligned")
 
-static bool tc_eligible(const ScanDims &d, int dtype) {
-  return g_use_tc && (dtype == SLX_BF16 || dtype == SLX_F16) && d.L == kTcL && d.P == kTcP && d.D % 64 == 0 &&
-         d.D >= 64 && d.D <= 256;
-}
+// The kernel family follows from the shape alone: half-precision chunk_starts (s->starts_dtype)
+// mean the tensor-core kernels, fp32 chunk_starts the exact CUDA-core kernels.  check_shape has
+// verified that the combination exists.
+static bool use_tc(const slx_scan_shape *s) { return s->starts_dtype != SLX_F32; }
 
 // Tensor map of a (BH, T, width) half tensor for boxes of [rows][64 columns], 128-byte swizzle.
 template <typename T>
@@ -169,7 +150,6 @@ static int make_tile_map(CUtensorMap *map, const void *base, int BH, int T_, int
 
 // dtype of the chunk-start states between the stages: the activation dtype on the tensor-core
 // path (those kernels round Z0 to it anyway; half the bytes of fp32), fp32 otherwise
-static int starts_dtype_of(const ScanDims &d, int dtype) { return tc_eligible(d, dtype) ? dtype : (int)SLX_F32; }
 
 template <typename T>
 static int launch_scan_fwd_tc(const ScanDims &d, const void *U, const float *M, const float *K, const void *B,
@@ -278,13 +258,13 @@ struct BwdWs {
   size_t d_inc, dz0, zdot, partials, carryB, carryU, total;  // dz0 == d_inc where the reverse pass runs in place
 };
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
-static BwdWs bwd_ws(const ScanDims &d, int dtype) {
+static BwdWs bwd_ws(const ScanDims &d, int starts_dtype) {
   BwdWs w;
   size_t off = 0;
   const size_t n_state = (size_t)d.BH * d.NC * d.P * d.D;
   w.dz0 = off;
   off += align256(sizeof(float) * n_state);
-  if (starts_dtype_of(d, dtype) == SLX_F32) {
+  if (starts_dtype == SLX_F32) {
     w.d_inc = w.dz0;  // fp32 d_inc overwrites dZ0 chunk by chunk
   } else {
     w.d_inc = off;  // d_inc in the activation dtype next to the fp32 dZ0
@@ -302,6 +282,25 @@ static BwdWs bwd_ws(const ScanDims &d, int dtype) {
   return w;
 }
 
+// Read-and-clear of a device status word as ONE atomic exchange on the device (a flag raised by a
+// kernel that is still running is either returned by this read or kept for the next one, never
+// lost).  The exchanged value travels through a second device word; the host mutex keeps two
+// host threads from interleaving their kernel + copy pairs.  Runs on the legacy default stream
+// of the current device and synchronises.
+__device__ int g_status_mailbox = 0;
+__global__ void status_exchange_kernel(int which) {
+  g_status_mailbox = atomicExch(which == 0 ? &g_tc_status : &g_scan_bad, 0);
+}
+static std::mutex g_status_mutex;
+static int exchange_status(int which, int *host_out, const char *what) {
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  status_exchange_kernel<<<1, 1>>>(which);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(host_out, g_status_mailbox, sizeof(int));
+  if (e != cudaSuccess) return fail((int)e, "%s: %s", what, cudaGetErrorString(e));
+  return SLX_OK;
+}
+
 }  // namespace slx
 
 using namespace slx;
@@ -316,34 +315,27 @@ int slx_set_tensor_path(int enable) {
   return old;
 }
 
+#ifdef SLX_DIAG
 int slx_read_phase_clock(long long *host_out64) {
   SLX_REQUIRE(host_out64 != nullptr, SLX_E_NULL, "read_phase_clock: NULL pointer");
   cudaError_t e = cudaMemcpyFromSymbol(host_out64, g_phase_clock, sizeof(long long) * 128);
   if (e != cudaSuccess) return fail((int)e, "read_phase_clock: %s", cudaGetErrorString(e));
   return SLX_OK;
 }
+#endif
 
 int slx_read_tc_status(int *host_out) {
   SLX_REQUIRE(host_out != nullptr, SLX_E_NULL, "read_tc_status: NULL pointer");
-  int zero = 0;
-  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_tc_status, sizeof(int));
-  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
-  if (e != cudaSuccess) return fail((int)e, "read_tc_status: %s", cudaGetErrorString(e));
-  return SLX_OK;
+  return exchange_status(0, host_out, "read_tc_status");
 }
 int slx_scan_starts_dtype(const slx_scan_shape *s) {
-  ScanDims d;
-  if (check_shape(s, &d)) return SLX_F32;
-  return starts_dtype_of(d, s->dtype);
+  if (s == nullptr) return SLX_F32;
+  return (g_use_tc && tc_capable(s)) ? s->dtype : (int)SLX_F32;
 }
 
 int slx_read_scan_status(int *host_out) {
   SLX_REQUIRE(host_out != nullptr, SLX_E_NULL, "read_scan_status: NULL pointer");
-  int zero = 0;
-  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_scan_bad, sizeof(int));
-  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_scan_bad, &zero, sizeof(int));
-  if (e != cudaSuccess) return fail((int)e, "read_scan_status: %s", cudaGetErrorString(e));
-  return SLX_OK;
+  return exchange_status(1, host_out, "read_scan_status");
 }
 const char *slx_last_error_string(void) { return g_err; }
 
@@ -355,7 +347,7 @@ int slx_chunk_increment_fwd(const slx_scan_shape *s, const void *U, const float 
   SLX_REQUIRE(U && M && K && B && inc && m_chunk, SLX_E_NULL, "chunk_increment_fwd: NULL tensor");
   SLX_REQUIRE_ALIGNED("chunk_increment_fwd", U, M, K, B, B_prev, U_prev, inc, m_chunk);
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
-  if (tc_eligible(d, s->dtype)) {
+  if (use_tc(s)) {
     if (s->dtype == SLX_BF16)
       return launch_outer_tc<__nv_bfloat16, 0>(d, U, B, M, K, B_prev, U_prev, inc, m_chunk, as_stream(stream));
     return launch_outer_tc<__half, 0>(d, U, B, M, K, B_prev, U_prev, inc, m_chunk, as_stream(stream));
@@ -389,7 +381,7 @@ int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M, c
   SLX_REQUIRE(U && M && K && B && C && chunk_starts && Y, SLX_E_NULL, "chunk_scan_fwd: NULL tensor");
   SLX_REQUIRE_ALIGNED("chunk_scan_fwd", U, M, K, B, C, chunk_starts, B_prev, U_prev, Y);
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
-  if (tc_eligible(d, s->dtype)) {
+  if (use_tc(s)) {
     if (s->dtype == SLX_BF16)
       return launch_scan_fwd_tc<__nv_bfloat16>(d, U, M, K, B, C, (const float *)chunk_starts, B_prev, U_prev, Y,
                                                as_stream(stream));
@@ -409,7 +401,7 @@ int slx_v2x2ssd_fwd(const slx_scan_shape *s, const void *U, const float *M, cons
     int rc0 = check_shape(s, &d0);
     if (rc0) return rc0;
   }
-  const int sdt = starts_dtype_of(d0, s->dtype);
+  const int sdt = s->starts_dtype;
   SLX_REQUIRE(increments != nullptr || sdt == SLX_F32, SLX_E_NULL,
               "v2x2ssd_fwd: this shape keeps chunk_starts in the activation dtype and needs the increments buffer");
   float *inc = increments ? increments : (float *)chunk_starts;
@@ -426,7 +418,7 @@ int slx_v2x2ssd_fwd(const slx_scan_shape *s, const void *U, const float *M, cons
 size_t slx_v2x2ssd_bwd_workspace_bytes(const slx_scan_shape *s) {
   ScanDims d;
   if (check_shape(s, &d)) return 0;
-  return bwd_ws(d, s->dtype).total;
+  return bwd_ws(d, s->starts_dtype).total;
 }
 
 int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *C, const void *dY, float *dZ0,
@@ -436,7 +428,7 @@ int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *
   if (rc) return rc;
   SLX_REQUIRE(M && C && dY && dZ0, SLX_E_NULL, "chunk_scan_bwd_dz0: NULL tensor");
   SLX_REQUIRE_ALIGNED("chunk_scan_bwd_dz0", M, C, dY, dZ0);
-  if (tc_eligible(d, s->dtype)) {
+  if (use_tc(s)) {
     if (s->dtype == SLX_BF16)
       return launch_outer_tc<__nv_bfloat16, 1>(d, dY, C, M, nullptr, nullptr, nullptr, dZ0, nullptr,
                                                as_stream(stream));
@@ -482,7 +474,7 @@ int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M, c
   SLX_REQUIRE_ALIGNED("chunk_scan_bwd", U, M, K, B, C, B_prev, U_prev, chunk_starts, d_inc, dY, dU, dM, dK, dB, dC,
                       carryB, carryU);
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
-  const bool tc = tc_eligible(d, s->dtype);
+  const bool tc = use_tc(s);
   SLX_DISPATCH_T(s->dtype, {
     ScanBwdArgs<T_> a{(const T_ *)U, (const T_ *)B, (const T_ *)C, (const T_ *)dY, M, K, (const float *)chunk_starts,
                       (const float *)d_inc, zdot,
@@ -507,7 +499,7 @@ static int v2x2ssd_bwd_impl(const slx_scan_shape *s, const void *U, const float 
               SLX_E_NULL, "v2x2ssd_bwd: NULL tensor");
   SLX_REQUIRE_ALIGNED("v2x2ssd_bwd", final_state, d_final, d_initial, dB_prev, dU_prev);
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
-  const BwdWs w = bwd_ws(d, s->dtype);
+  const BwdWs w = bwd_ws(d, s->starts_dtype);
   SLX_REQUIRE(workspace != nullptr && workspace_bytes >= w.total, SLX_E_WORKSPACE,
               "v2x2ssd_bwd: workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
   SLX_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, SLX_E_WORKSPACE,
@@ -525,7 +517,7 @@ static int v2x2ssd_bwd_impl(const slx_scan_shape *s, const void *U, const float 
     rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, dz0, stream);
     if (rc) return rc;
   }
-  rc = launch_state_bwd(d.BH, d.NC, d.P, d.N, dz0, m_chunk, chunk_starts, starts_dtype_of(d, s->dtype), final_state,
+  rc = launch_state_bwd(d.BH, d.NC, d.P, d.N, dz0, m_chunk, chunk_starts, s->starts_dtype, final_state,
                         d_final, d_inc, d_initial,
                         zdot, partials, st);
   if (rc) return rc;
@@ -556,7 +548,7 @@ int slx_v2x2ssd_bwd_begin(const slx_scan_shape *s, const float *M, const void *C
   int rc = check_shape(s, &d);
   if (rc) return rc;
   SLX_REQUIRE(M && C && m_chunk && dY && d_initial_zero_final, SLX_E_NULL, "v2x2ssd_bwd_begin: NULL tensor");
-  const BwdWs w = bwd_ws(d, s->dtype);
+  const BwdWs w = bwd_ws(d, s->starts_dtype);
   SLX_REQUIRE(workspace != nullptr && workspace_bytes >= w.total, SLX_E_WORKSPACE,
               "v2x2ssd_bwd_begin: workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
   SLX_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, SLX_E_WORKSPACE,

@@ -6,14 +6,41 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdarg>
+#include <cstdio>
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "../../include/slinoss_b200.h"
 
 namespace slx {
 
 // ---- host-side status plumbing --------------------------------------------
-void set_error(const char *fmt, ...);
-int fail(int code, const char *fmt, ...);
-int check_launch(const char *what);  // cudaGetLastError -> status
+// one thread-local message buffer per shared library that includes this header
+inline thread_local char g_err[512] = "";
+
+inline void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+inline int fail(int code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+inline int check_launch(const char *what) {  // cudaGetLastError -> status
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return (int)e;
+  }
+  return SLX_OK;
+}
 
 #define SLX_REQUIRE(cond, code, ...)            \
   do {                                          \
@@ -21,6 +48,55 @@ int check_launch(const char *what);  // cudaGetLastError -> status
   } while (0)
 
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// Per-kernel set-up that the driver keeps per device is done once per (kernel, device) and
+// remembered, so that a launch costs no driver call beyond the launch itself.
+struct KernelSetup {
+  size_t smem = 0;   // largest dynamic shared-memory size granted so far
+  long slots = -1;   // CTAs the device holds at once (occupancy query), -1 = not asked yet
+};
+inline std::mutex &kernel_setup_mutex() {
+  static std::mutex mu;
+  return mu;
+}
+inline std::map<std::pair<const void *, int>, KernelSetup> &kernel_setup_table() {
+  static std::map<std::pair<const void *, int>, KernelSetup> table;
+  return table;
+}
+// cudaFuncAttributeMaxDynamicSharedMemorySize >= bytes for `kernel` on the current device.
+template <typename K>
+inline int ensure_dyn_smem(K kernel, size_t bytes) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail((int)e, "cudaGetDevice: %s", cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(kernel_setup_mutex());
+  KernelSetup &ks = kernel_setup_table()[{reinterpret_cast<const void *>(kernel), dev}];
+  if (ks.smem >= bytes) return SLX_OK;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess) return fail((int)e, "cudaFuncSetAttribute(%zu bytes): %s", bytes, cudaGetErrorString(e));
+  ks.smem = bytes;
+  return SLX_OK;
+}
+// CTAs of `kernel` (threads per CTA, dynamic bytes) the current device holds at once; 0 if unknown.
+template <typename K>
+inline long resident_ctas(K kernel, int threads, size_t smem) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  std::lock_guard<std::mutex> lock(kernel_setup_mutex());
+  KernelSetup &ks = kernel_setup_table()[{reinterpret_cast<const void *>(kernel), dev}];
+  if (ks.slots >= 0) return ks.slots;
+  int sms = 0, per_sm = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  ks.slots = (long)sms * per_sm;
+  return ks.slots;
+}
 
 // ---- element access in the activation dtype ---------------------------------
 template <typename T> __device__ __forceinline__ float to_f(T v);

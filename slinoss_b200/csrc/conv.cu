@@ -717,6 +717,35 @@ __global__ void __launch_bounds__(32 * kConvReduceRows) cconv1d_reduce_kernel(co
   }
 }
 
+// One decode token: y[b,c] = act(bias[c] + sum_k w[c,k] * cat[k]),  cat = [state[b,c,0..W-2], x[b,c]];
+// next_state[b,c,:] = cat[1:].  One thread per channel; state and next_state may be the same buffer
+// (a thread reads its channel's W-1 values before it writes them).
+template <typename T>
+__global__ void __launch_bounds__(128) cconv1d_update_kernel(const T *__restrict__ x, long long x_stride,
+                                                             const T *__restrict__ weight, const T *__restrict__ bias,
+                                                             const T *state, T *__restrict__ y, T *next_state, int C,
+                                                             int W, int silu) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  if (c >= C) return;
+  float cat[4];
+  const long long so = ((long long)b * C + c) * (W - 1);
+#pragma unroll
+  for (int k = 0; k < 3; ++k) cat[k] = (k < W - 1 && state) ? to_f(state[so + k]) : 0.f;
+  cat[W - 1] = to_f(x[(long long)b * x_stride + c]);
+  float acc = bias ? to_f(bias[c]) : 0.f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    if (k < W) acc = fmaf(to_f(weight[(long long)c * W + k]), cat[k], acc);
+  if (silu) acc = acc / (1.f + __expf(-acc));
+  y[(long long)b * C + c] = from_f<T>(acc);
+  if (next_state) {
+#pragma unroll
+    for (int k = 0; k < 3; ++k)
+      if (k < W - 1) next_state[so + k] = from_f<T>(cat[k + 1]);
+  }
+}
+
 static int check_conv(const slx_conv_shape *s, ConvDims *d) {
   SLX_REQUIRE(s != nullptr, SLX_E_NULL, "shape is NULL");
   SLX_REQUIRE(s->batch > 0 && s->T > 0 && s->channels > 0, SLX_E_SHAPE, "cconv1d: sizes must be positive");
@@ -740,14 +769,7 @@ static int conv_tile(int T, bool bwd) {
 // CTAs of `kernel` (kConvThreads threads, `smem` dynamic bytes) that the current device holds at once
 template <typename K>
 static long conv_slots(K kernel, size_t smem) {
-  int dev = 0, sms = 0, per_sm = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess ||
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kConvThreads, smem) != cudaSuccess) {
-    cudaGetLastError();
-    return 0;
-  }
-  return (long)sms * per_sm;
+  return resident_ctas(kernel, kConvThreads, smem);
 }
 
 // Tile of the token axis for a grid of base_ctas x ceil(T / tile) CTAs.  With the smallest tile the grid
@@ -805,8 +827,8 @@ int slx_cconv1d_fwd(const slx_conv_shape *s, const void *x, const void *weight, 
       const int nblk = (d.C / VW + kConvThreads - 1) / kConvThreads;
       constexpr size_t ring = conv_ring_bytes<T_, VW, kConvRingFwd>(1);
       auto kern = cconv1d_fwd_staged_kernel<T_, VW, kConvRingFwd>;
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
-      SLX_REQUIRE(e == cudaSuccess, (int)e, "cconv1d_fwd: shared memory attribute: %s", cudaGetErrorString(e));
+      rc = ensure_dyn_smem(kern, ring);
+      if (rc) return rc;
       const int tile = conv_tile(d.T, false);  // growing the tile to whole waves measured no faster here
       const int n_tiles = (d.T + tile - 1) / tile;
       kern<<<dim3(nblk, n_tiles, d.batch), kConvThreads, ring, st>>>(xp, wp, bp, sp, (T_ *)y, (T_ *)next_state, d,
@@ -820,6 +842,22 @@ int slx_cconv1d_fwd(const slx_conv_shape *s, const void *x, const void *weight, 
     }
   });
   return check_launch("cconv1d_fwd");
+}
+
+int slx_cconv1d_update(const slx_conv_shape *s, const void *x, const void *weight, const void *bias,
+                       const void *state, void *y, void *next_state, void *stream) {
+  ConvDims d;
+  int rc = check_conv(s, &d);
+  if (rc) return rc;
+  SLX_REQUIRE(s->T == 1, SLX_E_SHAPE, "cconv1d_update: one token per call (T must be 1, got %d)", s->T);
+  SLX_REQUIRE(x && weight && y, SLX_E_NULL, "cconv1d_update: NULL tensor");
+  cudaStream_t st = as_stream(stream);
+  SLX_CONV_T(s->dtype, {
+    cconv1d_update_kernel<T_><<<dim3((d.C + 127) / 128, d.batch), 128, 0, st>>>(
+        (const T_ *)x, s->x_batch_stride, (const T_ *)weight, (const T_ *)bias, (const T_ *)state, (T_ *)y,
+        (T_ *)next_state, d.C, d.W, d.silu);
+  });
+  return check_launch("cconv1d_update");
 }
 
 size_t slx_cconv1d_bwd_workspace_bytes(const slx_conv_shape *s) {
@@ -851,8 +889,8 @@ int slx_cconv1d_bwd(const slx_conv_shape *s, const void *x, const void *weight, 
       const int nblk = (d.C / VFULL + kConvThreads - 1) / kConvThreads;
       constexpr size_t ring = conv_ring_bytes<T_, VFULL>(2);
       auto kern = cconv1d_bwd_staged_kernel<T_, VFULL, kConvRing>;
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
-      SLX_REQUIRE(e == cudaSuccess, (int)e, "cconv1d_bwd: shared memory attribute: %s", cudaGetErrorString(e));
+      rc = ensure_dyn_smem(kern, ring);
+      if (rc) return rc;
       const int tile = conv_tile_balanced(d.T, kConvTileBwd, (long)nblk * d.batch, conv_slots(kern, ring));
       n_tiles = (d.T + tile - 1) / tile;
       kern<<<dim3(nblk, n_tiles, d.batch), kConvThreads, ring, st>>>(xp, wp, bp, sp, gp, np, (T_ *)dx, part, d, tile);

@@ -850,8 +850,8 @@ static int launch_prep_bwd(const slx_prep_shape *s, const PrepDims &d, const voi
 #define SLX_PREP_BWD(KM)                                                                                      \
   {                                                                                                           \
     auto kern = scanprep_bwd_kernel<T, VEC, G, KM>;                                                           \
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);    \
-    if (e != cudaSuccess) return fail((int)e, "scanprep_bwd smem attribute: %s", cudaGetErrorString(e));      \
+    int rc_smem = ensure_dyn_smem(kern, pl.smem);                                                             \
+    if (rc_smem) return rc_smem;                                                                              \
     kern<<<dim3(2 * pl.n_tiles, d.batch * d.H), 256, pl.smem, st>>>(                                          \
         (const T *)params, (const T *)bc, bias, scale, (const T *)dU, dM, dK, (const T *)dB, (const T *)dC,   \
         (T *)d_value, (T *)d_params, (T *)d_bc, part, d, hp, pl.rows_per_tile, pl.n_tiles);                   \

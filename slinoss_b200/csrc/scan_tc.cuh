@@ -21,7 +21,14 @@ struct alignas(64) ScanTileMaps {
 };
 
 __device__ int g_tc_status = 0;  // becomes non-zero when a bounded wait ran out
-__device__ long long g_phase_clock[128];  // clock64() stamps of CTA (0,0) of the last backward launch (diagnostic)
+// Phase-clock stamps (clock64() of CTA (0,0) at the phase boundaries) exist only in builds with
+// -DSLX_DIAG; the shipped library carries none.
+#ifdef SLX_DIAG
+__device__ long long g_phase_clock[128];
+#define SLX_DIAG_STAMP(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_phase_clock[i] = clock64(); } while (0)
+#else
+#define SLX_DIAG_STAMP(i) do { } while (0)
+#endif
 
 constexpr int kTcL = 128;
 constexpr int kTcP = 64;
@@ -179,8 +186,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   prefetch_cb(0);
   prefetch_z(0);
 
-  const bool stamp_on = (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0);
-#define SLX_FSTAMP(i) do { if (stamp_on) g_phase_clock[64 + (i)] = clock64(); } while (0)
+#define SLX_FSTAMP(i) SLX_DIAG_STAMP(64 + (i))
   SLX_FSTAMP(0);
   if (warp == 0) umma::tmem_alloc(&tmem_slot, 256);
   if (tid == 32) {

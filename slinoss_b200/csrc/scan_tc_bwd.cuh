@@ -81,8 +81,7 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
   const uint32_t mbar_s = umma::smem_u32(&mbar), tbar_s = umma::smem_u32(&tbar);
   constexpr int fmt = umma::HalfFmt<T>::value;
 
-  const bool stamp_on = (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0);
-#define SLX_STAMP(i) do { if (stamp_on) g_phase_clock[i] = clock64(); } while (0)
+#define SLX_STAMP(i) SLX_DIAG_STAMP(i)
   SLX_STAMP(0);
   const int j = tid & 7, r0 = tid >> 3;  // r0 in [0,64)
   // on this path the chunk-start states are stored in the activation dtype (api: slx_scan_starts_dtype)

@@ -1,8 +1,8 @@
 // Self-test of the tcgen05 tile engine (umma.cuh): small single-CTA products in
 // every operand arrangement the scan kernels use, checked by the tests against a
 // plain matrix product.  Diagnostic entry point; not on any hot path.
-#include "common.cuh"
-#include "umma.cuh"
+#include "../common.cuh"
+#include "../umma.cuh"
 
 namespace slx {
 
@@ -96,3 +96,5 @@ extern "C" int slx_umma_selftest(int mode, const void *A, const void *B, float *
                                                            status);
   return check_launch("umma_selftest");
 }
+
+extern "C" const char *slx_selftest_last_error_string(void) { return slx::g_err; }

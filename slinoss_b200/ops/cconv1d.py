@@ -42,9 +42,10 @@ class _CConv1dFn(torch.autograd.Function):
         y = torch.empty((b, T, C), device=dev, dtype=x.dtype)
         nxt = torch.empty((b, C, W - 1), device=dev, dtype=x.dtype)
         s = _conv_shape(xd, C, W, silu)
-        _lib.check(_lib.lib().slx_cconv1d_fwd(byref(s), xd.data_ptr(), w.data_ptr(), _lib.ptr(bs),
-                                              _lib.ptr(st), y.data_ptr(), nxt.data_ptr(),
-                                              _lib.stream_ptr(dev)), "cconv1d forward")
+        with _lib.guard(dev):
+            _lib.check(_lib.lib().slx_cconv1d_fwd(byref(s), xd.data_ptr(), w.data_ptr(), _lib.ptr(bs),
+                                                  _lib.ptr(st), y.data_ptr(), nxt.data_ptr(),
+                                                  _lib.stream_ptr(dev)), "cconv1d forward")
         ctx.silu = silu
         ctx.has_bias = bias is not None
         ctx.has_state = conv_state is not None
@@ -75,10 +76,11 @@ class _CConv1dFn(torch.autograd.Function):
         L_ = _lib.lib()
         nbytes = int(L_.slx_cconv1d_bwd_workspace_bytes(byref(s)))
         ws = torch.empty((max(nbytes, 16),), device=dev, dtype=torch.uint8)
-        _lib.check(L_.slx_cconv1d_bwd(byref(s), xd.data_ptr(), w.data_ptr(), _lib.ptr(bs), _lib.ptr(st),
-                                      dyc.data_ptr(), _lib.ptr(dn), dx.data_ptr(), dw.data_ptr(),
-                                      db.data_ptr(), _lib.ptr(dst), ws.data_ptr(), nbytes,
-                                      _lib.stream_ptr(dev)), "cconv1d backward")
+        with _lib.guard(dev):
+            _lib.check(L_.slx_cconv1d_bwd(byref(s), xd.data_ptr(), w.data_ptr(), _lib.ptr(bs), _lib.ptr(st),
+                                          dyc.data_ptr(), _lib.ptr(dn), dx.data_ptr(), dw.data_ptr(),
+                                          db.data_ptr(), _lib.ptr(dst), ws.data_ptr(), nbytes,
+                                          _lib.stream_ptr(dev)), "cconv1d backward")
         return (dx, dw.to(ctx.w_dtype), db.to(ctx.b_dtype) if ctx.has_bias else None,
                 dst.to(ctx.s_dtype) if ctx.has_state else None, None)
 

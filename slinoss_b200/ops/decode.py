@@ -93,11 +93,12 @@ def mixer_decode_step_b200(value, params, bc, gate, skip, *, initial_states=None
     s = _lib.DecodeShape(b, H, P, N, _lib.dtype_code(dt), 1 if normalize_bc else 0, float(dt_min),
                          float(dt_max), float(r_min), float(r_max), float(theta_bound), float(k_max),
                          float(eps))
-    _lib.check(_lib.lib().slx_decode_step(
-        byref(s), value.data_ptr(), params.data_ptr(), bc.data_ptr(), gate.data_ptr(), skip.data_ptr(),
-        bias.data_ptr(), _lib.ptr(scale), _lib.ptr(state_in), _lib.ptr(B_prev), _lib.ptr(U_prev),
-        out.data_ptr(), state_out.data_ptr(), b_last.data_ptr(), u_last.data_ptr(),
-        _lib.stream_ptr(dev)), "decode step")
+    with _lib.guard(dev):
+        _lib.check(_lib.lib().slx_decode_step(
+            byref(s), value.data_ptr(), params.data_ptr(), bc.data_ptr(), gate.data_ptr(), skip.data_ptr(),
+            bias.data_ptr(), _lib.ptr(scale), _lib.ptr(state_in), _lib.ptr(B_prev), _lib.ptr(U_prev),
+            out.data_ptr(), state_out.data_ptr(), b_last.data_ptr(), u_last.data_ptr(),
+            _lib.stream_ptr(dev)), "decode step")
     return out, state_out, b_last, u_last
 
 

@@ -66,10 +66,11 @@ class _ScanPrepFn(torch.autograd.Function):
         Co = torch.empty_like(Bo)
         M = torch.empty((b, n_heads, T, 2), device=dev, dtype=torch.float32)
         K = torch.empty((b, n_heads, T, 2, 2), device=dev, dtype=torch.float32)
-        _lib.check(_lib.lib().slx_scanprep_fwd(
-            byref(s), v.data_ptr(), p.data_ptr(), c.data_ptr(), bias.data_ptr(), _lib.ptr(scale),
-            U.data_ptr(), M.data_ptr(), K.data_ptr(), Bo.data_ptr(), Co.data_ptr(),
-            _lib.stream_ptr(dev)), "scanprep forward")
+        with _lib.guard(dev):
+            _lib.check(_lib.lib().slx_scanprep_fwd(
+                byref(s), v.data_ptr(), p.data_ptr(), c.data_ptr(), bias.data_ptr(), _lib.ptr(scale),
+                U.data_ptr(), M.data_ptr(), K.data_ptr(), Bo.data_ptr(), Co.data_ptr(),
+                _lib.stream_ptr(dev)), "scanprep forward")
         ctx.meta = meta
         ctx.has_scale = scale is not None
         ctx.bias_dtypes = [t.dtype for t in (dt_bias, gamma_bias, omega_bias, mix_r_bias,
@@ -110,11 +111,12 @@ class _ScanPrepFn(torch.autograd.Function):
         L_ = _lib.lib()
         nbytes = int(L_.slx_scanprep_bwd_workspace_bytes(byref(s)))
         ws = torch.empty((max(nbytes, 16),), device=dev, dtype=torch.uint8)
-        _lib.check(L_.slx_scanprep_bwd(
-            byref(s), p.data_ptr(), c.data_ptr(), bias.data_ptr(), _lib.ptr(scale), dU.data_ptr(),
-            dM.data_ptr(), dK.data_ptr(), dB.data_ptr(), dC.data_ptr(), d_value.data_ptr(),
-            d_params.data_ptr(), d_bc.data_ptr(), d_bias.data_ptr(), _lib.ptr(d_scale),
-            ws.data_ptr(), nbytes, _lib.stream_ptr(dev)), "scanprep backward")
+        with _lib.guard(dev):
+            _lib.check(L_.slx_scanprep_bwd(
+                byref(s), p.data_ptr(), c.data_ptr(), bias.data_ptr(), _lib.ptr(scale), dU.data_ptr(),
+                dM.data_ptr(), dK.data_ptr(), dB.data_ptr(), dC.data_ptr(), d_value.data_ptr(),
+                d_params.data_ptr(), d_bc.data_ptr(), d_bias.data_ptr(), _lib.ptr(d_scale),
+                ws.data_ptr(), nbytes, _lib.stream_ptr(dev)), "scanprep backward")
         gb = [d_bias[:, slot].to(dtp) for slot, dtp in zip(BIAS_SLOTS, ctx.bias_dtypes)]
         gbs = gcs = None
         if d_scale is not None:

@@ -128,27 +128,47 @@ def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
 def _shape(b, h, T, P, N, L, dtype) -> _lib.ScanShape:
     if L not in _CHUNKS:
         raise ValueError(f"chunk_size must be one of {_CHUNKS} for the sm_100a kernels. Got {L}.")
-    return _lib.ScanShape(b * h, T, P, N, L, _lib.dtype_code(dtype))
+    return _lib.scan_shape(b * h, T, P, N, L, dtype)
 
 
 # --------------------------------------------------------------------------- #
 # stage-level entry points
 # --------------------------------------------------------------------------- #
 
+def _stage_inputs(U, M, K, B, C, B_prev, U_prev):
+    """Validation and dtype handling shared by the stage-level entry points: the checks of
+    ``_validate_inputs`` (same messages as the reference), then M and K as fp32, U/B/C in one
+    activation dtype, everything 16-byte aligned -- what ``v2x2ssd_b200`` does for the fused op."""
+    _validate_inputs(U, M, K, B, B if C is None else C, None, B_prev, U_prev)
+    _require_cuda(U, M, K, B, C, B_prev, U_prev)
+    act = torch.promote_types(U.dtype, B.dtype)
+    if C is not None:
+        act = torch.promote_types(act, C.dtype)
+    if act not in _ACT_DTYPES:
+        raise TypeError(f"U/B/C must be float32, bfloat16 or float16. Got {act}.")
+    cast = lambda t: None if t is None else _aligned(t if t.dtype == act else t.to(act))
+    f32 = lambda t: _aligned(t if t.dtype == torch.float32 else t.to(torch.float32))
+    return cast(U), f32(M), f32(K), cast(B), cast(C)
+
+
 def chunk_increment_b200(U, M, K, B, *, B_prev=None, U_prev=None, chunk_size: int):
-    """Stage 1 -> ``(inc (b,h,C,P,2N) fp32, m_chunk (b,h,C,2) fp32)``."""
-    _require_cuda(U, M, K, B)
+    """Stage 1 -> ``(inc (b,h,C,P,2N) fp32, m_chunk (b,h,C,2) fp32)``.  Inputs are checked as
+    the reference checks them (contiguous, matching shapes, one device)."""
+    U, M, K, B, _ = _stage_inputs(U, M, K, B, None, B_prev, U_prev)
     b, h, T, P = map(int, U.shape)
     D = int(B.shape[-1])
     L = int(chunk_size)
+    if L <= 0:
+        raise ValueError(f"chunk_size must be positive. Got {chunk_size}.")
     NC = (T + L - 1) // L
     s = _shape(b, h, T, P, D // 2, L, U.dtype)
     inc = torch.empty((b, h, NC, P, D), device=U.device, dtype=torch.float32)
     mch = torch.empty((b, h, NC, 2), device=U.device, dtype=torch.float32)
     bp, up = _f32(B_prev), _f32(U_prev)
-    _lib.check(_lib.lib().slx_chunk_increment_fwd(
-        byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), _lib.ptr(bp), _lib.ptr(up),
-        inc.data_ptr(), mch.data_ptr(), _lib.stream_ptr(U.device)), "chunk_increment")
+    with _lib.guard(U.device):
+        _lib.check(_lib.lib().slx_chunk_increment_fwd(
+            byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), _lib.ptr(bp), _lib.ptr(up),
+            inc.data_ptr(), mch.data_ptr(), _lib.stream_ptr(U.device)), "chunk_increment")
     return inc, mch
 
 
@@ -159,29 +179,53 @@ def state_passing_b200(inc, m_chunk, *, initial_states=None, want_starts: bool =
     op uses the activation dtype where the tensor-core kernels run).  ``want_starts=False``
     returns ``(None, final_state)`` and writes nothing but the final state (half the traffic)."""
     _require_cuda(inc, m_chunk, initial_states)
+    if inc.ndim != 5:
+        raise ValueError(f"inc must be (batch,heads,chunks,P,2N). Got {tuple(inc.shape)}.")
     b, h, NC, P, D = map(int, inc.shape)
+    if D % 2 != 0:
+        raise ValueError(f"inc 2N dim must be divisible by 2. Got {D}.")
+    if tuple(m_chunk.shape) != (b, h, NC, 2):
+        raise ValueError(f"m_chunk must be (batch,heads,chunks,2)={(b, h, NC, 2)}. Got {tuple(m_chunk.shape)}.")
+    if initial_states is not None and tuple(initial_states.shape) != (b, h, P, D):
+        raise ValueError(f"initial_states must be (batch,heads,P,2N)={(b, h, P, D)}. "
+                         f"Got {tuple(initial_states.shape)}.")
+    if starts_dtype not in _ACT_DTYPES:
+        raise TypeError(f"starts_dtype must be float32, bfloat16 or float16. Got {starts_dtype}.")
+    dev = _lib.same_device(inc, m_chunk, initial_states)
+    inc, m_chunk = _f32(inc), _f32(m_chunk)
     init = _f32(initial_states)
-    starts = torch.empty(inc.shape, device=inc.device, dtype=starts_dtype) if want_starts else None
-    final = torch.empty((b, h, P, D), device=inc.device, dtype=torch.float32)
-    _lib.check(_lib.lib().slx_state_passing_fwd(
-        b * h, NC, P, D // 2, inc.data_ptr(), m_chunk.data_ptr(), _lib.ptr(init), _lib.ptr(starts),
-        _lib.dtype_code(starts_dtype), final.data_ptr(), _lib.stream_ptr(inc.device)), "state_passing")
+    starts = torch.empty(inc.shape, device=dev, dtype=starts_dtype) if want_starts else None
+    final = torch.empty((b, h, P, D), device=dev, dtype=torch.float32)
+    with _lib.guard(dev):
+        _lib.check(_lib.lib().slx_state_passing_fwd(
+            b * h, NC, P, D // 2, inc.data_ptr(), m_chunk.data_ptr(), _lib.ptr(init), _lib.ptr(starts),
+            _lib.dtype_code(starts_dtype), final.data_ptr(), _lib.stream_ptr(dev)), "state_passing")
     return starts, final
 
 
 def chunk_scan_b200(U, M, K, B, C, chunk_starts, *, B_prev=None, U_prev=None, chunk_size: int):
-    """Stage 3 -> ``Y (b,h,T,P)`` in ``U.dtype``."""
-    _require_cuda(U, M, K, B, C, chunk_starts)
+    """Stage 3 -> ``Y (b,h,T,P)`` in the activation dtype.  Inputs are checked as the reference
+    checks them; ``chunk_starts`` must be ``(b,h,chunks,P,2N)`` for this ``chunk_size``."""
+    U, M, K, B, C = _stage_inputs(U, M, K, B, C, B_prev, U_prev)
     b, h, T, P = map(int, U.shape)
     D = int(B.shape[-1])
-    s = _shape(b, h, T, P, D // 2, int(chunk_size), U.dtype)
-    chunk_starts = _as_starts(chunk_starts, s)
+    L = int(chunk_size)
+    if L <= 0:
+        raise ValueError(f"chunk_size must be positive. Got {chunk_size}.")
+    NC = (T + L - 1) // L
+    if tuple(chunk_starts.shape) != (b, h, NC, P, D):
+        raise ValueError(f"chunk_starts must be (batch,heads,chunks,P,2N)={(b, h, NC, P, D)}. "
+                         f"Got {tuple(chunk_starts.shape)}.")
+    _lib.same_device(U, chunk_starts)
+    s = _shape(b, h, T, P, D // 2, L, U.dtype)
+    chunk_starts = _aligned(_as_starts(chunk_starts, s).contiguous())
     Y = torch.empty_like(U)
     bp, up = _f32(B_prev), _f32(U_prev)
-    _lib.check(_lib.lib().slx_chunk_scan_fwd(
-        byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
-        chunk_starts.data_ptr(), _lib.ptr(bp), _lib.ptr(up), Y.data_ptr(), _lib.stream_ptr(U.device)),
-        "chunk_scan")
+    with _lib.guard(U.device):
+        _lib.check(_lib.lib().slx_chunk_scan_fwd(
+            byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
+            chunk_starts.data_ptr(), _lib.ptr(bp), _lib.ptr(up), Y.data_ptr(), _lib.stream_ptr(U.device)),
+            "chunk_scan")
     return Y
 
 
@@ -205,10 +249,11 @@ def _fwd_impl(U, M, K, B, C, init32, bp32, up32, L):
     mch = torch.empty((b, h, NC, 2), device=dev, dtype=torch.float32)
     # separate fp32 increment buffer: the two-buffer state pass is ~2.5x faster than the in-place one
     inc = torch.empty((b, h, NC, P, D), device=dev, dtype=torch.float32)
-    _lib.check(_lib.lib().slx_v2x2ssd_fwd(
-        byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
-        _lib.ptr(init32), _lib.ptr(bp32), _lib.ptr(up32), Y.data_ptr(), final.data_ptr(),
-        starts.data_ptr(), mch.data_ptr(), inc.data_ptr(), _lib.stream_ptr(dev)), "v2x2ssd forward")
+    with _lib.guard(dev):
+        _lib.check(_lib.lib().slx_v2x2ssd_fwd(
+            byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
+            _lib.ptr(init32), _lib.ptr(bp32), _lib.ptr(up32), Y.data_ptr(), final.data_ptr(),
+            starts.data_ptr(), mch.data_ptr(), inc.data_ptr(), _lib.stream_ptr(dev)), "v2x2ssd forward")
     return Y, final, starts, mch
 
 
@@ -223,9 +268,10 @@ def _bwd_begin(M, C, mch, dY, L, P):
     nbytes = int(L_.slx_v2x2ssd_bwd_workspace_bytes(byref(s)))
     ws = torch.empty((nbytes,), device=dev, dtype=torch.uint8)
     g0 = torch.empty((b, h, P, D), device=dev, dtype=torch.float32)
-    _lib.check(L_.slx_v2x2ssd_bwd_begin(byref(s), M.data_ptr(), C.data_ptr(), mch.data_ptr(), dY.data_ptr(),
-                                        g0.data_ptr(), ws.data_ptr(), nbytes, _lib.stream_ptr(dev)),
-               "v2x2ssd backward (begin)")
+    with _lib.guard(dev):
+        _lib.check(L_.slx_v2x2ssd_bwd_begin(byref(s), M.data_ptr(), C.data_ptr(), mch.data_ptr(), dY.data_ptr(),
+                                            g0.data_ptr(), ws.data_ptr(), nbytes, _lib.stream_ptr(dev)),
+                   "v2x2ssd backward (begin)")
     return g0, ws
 
 
@@ -246,12 +292,13 @@ def _bwd_impl(U, M, K, B, C, bp32, up32, starts, mch, final32, dY, d_final32, L,
     starts = _as_starts(starts, s)
     ws = torch.empty((nbytes,), device=dev, dtype=torch.uint8) if workspace is None else workspace
     entry = L_.slx_v2x2ssd_bwd if workspace is None else L_.slx_v2x2ssd_bwd_finish  # dZ0 already there
-    _lib.check(entry(
-        byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
-        _lib.ptr(bp32), _lib.ptr(up32), starts.data_ptr(), mch.data_ptr(), final32.data_ptr(),
-        dY.data_ptr(), _lib.ptr(d_final32), dU.data_ptr(), dM.data_ptr(), dK.data_ptr(),
-        dB.data_ptr(), dC.data_ptr(), _lib.ptr(d_init), _lib.ptr(dBp), _lib.ptr(dUp),
-        ws.data_ptr(), nbytes, _lib.stream_ptr(dev)), "v2x2ssd backward")
+    with _lib.guard(dev):
+        _lib.check(entry(
+            byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
+            _lib.ptr(bp32), _lib.ptr(up32), starts.data_ptr(), mch.data_ptr(), final32.data_ptr(),
+            dY.data_ptr(), _lib.ptr(d_final32), dU.data_ptr(), dM.data_ptr(), dK.data_ptr(),
+            dB.data_ptr(), dC.data_ptr(), _lib.ptr(d_init), _lib.ptr(dBp), _lib.ptr(dUp),
+            ws.data_ptr(), nbytes, _lib.stream_ptr(dev)), "v2x2ssd backward")
     return dU, dM, dK, dB, dC, d_init, dBp, dUp
 
 
@@ -344,7 +391,10 @@ def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=
     A transition ``M`` of magnitude exactly 0 makes the reference raise ``ValueError``
     (reference.py:480-485).  The kernels cannot raise: they fill the affected outputs with NaN
     and set a status word (``read_scan_status``).  ``strict=True`` reads that word after the
-    forward (one device synchronisation per call) and raises like the reference.
+    forward (one device synchronisation per call) and raises like the reference; it also reads
+    the tensor-core kernels' status word (a completion wait that ran out) and raises
+    ``RuntimeError`` for it.  The status words are one per device, shared by every stream and
+    thread using that device: ``strict`` is meant for one caller at a time per device.
 
     ``residual`` chooses what autograd keeps of the chunk-start states, the largest residual
     ((batch, heads, chunks, P, 2N); the reference saves it in fp32, cute/autograd.py:98):
@@ -383,11 +433,16 @@ def v2x2ssd_b200(U, M, K, B, C, *, chunk_size: int, initial_states=None, B_prev=
     needs_grad = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (U, M, K, B, C, initial_states, B_prev, U_prev))
     if strict:
-        _lib.read_scan_status()  # clear what earlier calls may have left
+        _lib.read_scan_status(U.device)  # clear what earlier calls on this device may have left
+        _lib.read_tc_status(U.device)
 
     def _checked(out):
-        if strict and _lib.read_scan_status():
-            raise ValueError("M has an entry of magnitude exactly 0: the chunked scan needs abs(M) > 0.")
+        if strict:
+            if _lib.read_scan_status(U.device):
+                raise ValueError("M has an entry of magnitude exactly 0: the chunked scan needs abs(M) > 0.")
+            if _lib.read_tc_status(U.device):
+                raise RuntimeError("v2x2ssd: a bounded wait inside a tensor-core kernel ran out; the outputs "
+                                   "of the affected chunks are NaN.")
         return out
 
     if needs_grad:

@@ -1,6 +1,7 @@
-"""Context-parallel scan on real GPUs (NCCL, one process per GPU): split the
-sequence over the ranks, compare with the single-GPU op on the whole sequence.
-Skipped unless at least two GPUs are visible."""
+"""Context-parallel scan on real GPUs (NCCL, one process per GPU, all visible GPUs): split the
+sequence over the ranks; every rank compares its slice with the float64 oracle run over the
+whole sequence (relative L2 <= 2e-2, the bound for bf16 inputs with fp32 state) and with the
+single-GPU op on the whole sequence.  Skipped unless at least two GPUs are visible."""
 
 from __future__ import annotations
 
@@ -58,6 +59,18 @@ def _worker(rank, world, port, out_dir):
             errs["final"] = rel(fin, finf)
         if rank == 0:
             errs["d_init"] = rel(grads[5], gf[5])
+        # the float64 oracle over the whole sequence (CPU), this rank's slice of it
+        from gpu_util import oracle_fwd_bwd, to_np
+        from util import rel_err
+
+        Yo, fino, go = oracle_fwd_bwd({**inp, "B_prev": None, "U_prev": None})
+        errs["oracle:Y"] = rel_err(to_np(Y), Yo[:, :, lo:hi])
+        for n, g in zip(names, grads):
+            errs["oracle:d" + n] = rel_err(to_np(g), go["d" + n][:, :, lo:hi])
+        if rank == world - 1:
+            errs["oracle:final"] = rel_err(to_np(fin), fino)
+        if rank == 0:
+            errs["oracle:d_init"] = rel_err(to_np(grads[5]), go["d_initial"])
         torch.cuda.synchronize()
         (Path(out_dir) / f"r{rank}.txt").write_text(repr(errs))
     finally:
@@ -74,9 +87,10 @@ def _free_port():
 def test_context_parallel_on_gpus(tmp_path):
     import torch.multiprocessing as mp
 
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), 8)
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         errs = eval((tmp_path / f"r{r}.txt").read_text())
-        # both sides are the same half-precision kernels; segment boundaries move chunk boundaries only
-        assert all(v < 1e-2 for v in errs.values()), (r, errs)
+        # against the single-GPU op both sides are the same half-precision kernels (segment boundaries
+        # only move chunk boundaries): 1e-2; against the float64 oracle the bf16 contract: 2e-2
+        assert all(v < (2e-2 if k.startswith("oracle:") else 1e-2) for k, v in errs.items()), (r, errs)

@@ -11,10 +11,11 @@ import pytest
 
 ROOT = Path(__file__).resolve().parents[1]
 HEADER = ROOT / "include" / "slinoss_b200.h"
+SELFTEST_HEADER = ROOT / "include" / "slinoss_b200_selftest.h"
 
 
-def _declared():
-    text = HEADER.read_text()
+def _declared(header=HEADER):
+    text = header.read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(slx_[a-z0-9_]+)\s*\(", text)))
 
@@ -37,8 +38,22 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
     assert sorted(_lib.SIGNATURES) == names, "ctypes table and header disagree"
 
 
+def test_selftest_library_exports_its_header():
+    from slinoss_b200 import _lib, build
+
+    build.build_selftest()
+    names = _declared(SELFTEST_HEADER)
+    handle = _lib.selftest_lib()
+    for n in names:
+        assert hasattr(handle, n), f"{n} declared in the self-test header but not exported"
+    assert sorted(_lib.SELFTEST_SIGNATURES) == names
+    # the product library carries no diagnostics
+    assert not hasattr(_lib.lib(), "slx_umma_selftest")
+    assert not hasattr(_lib.lib(), "slx_read_phase_clock")
+
+
 def test_abi_version(lib):
-    assert lib.slx_abi_version() == 3
+    assert lib.slx_abi_version() == 4
 
 
 def test_argument_errors_are_reported_without_touching_the_gpu(lib):

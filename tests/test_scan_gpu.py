@@ -223,7 +223,7 @@ def test_views_at_odd_storage_offsets_are_handled():
     assert any(t.data_ptr() % 16 for t in sh)
     assert torch.equal(sb.v2x2ssd_b200(*sh, chunk_size=128), y_ref)
     U, M, K, B, C = sh
-    s = _lib.ScanShape(2, 128, 64, 64, 128, _lib.dtype_code(torch.bfloat16))
+    s = _lib.scan_shape(2, 128, 64, 64, 128, torch.bfloat16)
     inc = torch.empty(1, 2, 1, 64, 128, device="cuda")
     mch = torch.empty(1, 2, 1, 2, device="cuda")
     rc = _lib.lib().slx_chunk_increment_fwd(ctypes.byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(),

@@ -20,8 +20,9 @@ def test_umma_selftest(mode):
     B = torch.randn(shapes[1], generator=g).to(torch.bfloat16).cuda()
     C = torch.full(shapes[2], float("nan"), device="cuda", dtype=torch.float32)
     status = torch.zeros(1, device="cuda", dtype=torch.int32)
-    _lib.check(_lib.lib().slx_umma_selftest(mode, A.data_ptr(), B.data_ptr(), C.data_ptr(), status.data_ptr(),
-                                            _lib.stream_ptr(A.device)), "umma selftest")
+    rc = _lib.selftest_lib().slx_umma_selftest(mode, A.data_ptr(), B.data_ptr(), C.data_ptr(), status.data_ptr(),
+                                               _lib.stream_ptr(A.device))
+    assert rc == 0, _lib.selftest_lib().slx_selftest_last_error_string()
     torch.cuda.synchronize()
     assert int(status.item()) == 0, "bounded mbarrier wait ran out"
     a, b = A.float(), B.float()
