@@ -8,6 +8,7 @@ framework fallback.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, Structure, c_char_p, c_float, c_int32, c_int64, c_size_t, c_void_p
 from pathlib import Path
 from typing import Optional
@@ -119,6 +120,10 @@ def lib() -> ctypes.CDLL:
             fn.restype = res
             fn.argtypes = args
         _lib = handle
+        # SLX_SCAN_KERNELS=0|1|2 picks the kernel family at load time (see set_tensor_path)
+        env = os.environ.get("SLX_SCAN_KERNELS")
+        if env is not None:
+            handle.slx_set_tensor_path(int(env))
     return _lib
 
 
@@ -210,10 +215,13 @@ def check(status: int, what: str) -> None:
     raise RuntimeError(f"{what}: CUDA error {status}: {msg}")
 
 
-def set_tensor_path(enable: bool) -> bool:
-    """Process-wide switch between the tcgen05 kernels (default, where a shape is
-    eligible) and the fp32-exact CUDA-core kernels.  Returns the previous value."""
-    return bool(lib().slx_set_tensor_path(1 if enable else 0))
+def set_tensor_path(enable) -> int:
+    """Process-wide choice of the kernel family for shapes the tcgen05 kernels cover:
+    ``False``/0 = fp32-exact CUDA-core kernels, 1 = one-chunk-per-CTA tcgen05 kernels,
+    ``True``/2 = persistent warp-specialised tcgen05 kernels (default).  Returns the previous
+    value (0, 1 or 2)."""
+    code = 2 if enable is True else (0 if enable is False else int(enable))
+    return int(lib().slx_set_tensor_path(code))
 
 
 def _status_device(device) -> torch.device:

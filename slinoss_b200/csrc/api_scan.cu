@@ -4,12 +4,14 @@
 #include <cstdio>
 #include <type_traits>
 
+#include <atomic>
 #include <initializer_list>
 #include <mutex>
 
 #include "scan_simt.cuh"
 #include "scan_tc.cuh"
 #include "scan_tc_bwd.cuh"
+#include "scan_ws_bwd.cuh"
 #include "state_passing.cuh"
 
 namespace slx {
@@ -103,7 +105,7 @@ static int launch_scan_bwd(const ScanDims &d, const ScanBwdArgs<T> &a, cudaStrea
 }
 
 // ---- tensor-core path selection ----------------------------------------------------
-static int g_use_tc = 1;  // 0 forces the fp32-exact CUDA-core kernels for every dtype
+static int g_use_tc = 1;  // 0: fp32-exact CUDA-core kernels for every dtype; 1: per-chunk tcgen05 kernels; 2: persistent ones
 
 // every kernel of this file reads and writes its tensors with 8- and 16-byte accesses
 static bool all_aligned16(std::initializer_list<const void *> ptrs) {
@@ -132,7 +134,8 @@ static int make_tile_map(CUtensorMap *map, const void *base, int BH, int T_, int
   typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-  static EncodeFn encode = nullptr;
+  static std::atomic<EncodeFn> encode_fn{nullptr};
+  EncodeFn encode = encode_fn.load(std::memory_order_acquire);
   if (encode == nullptr) {
     void *fn = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -140,6 +143,7 @@ static int make_tile_map(CUtensorMap *map, const void *base, int BH, int T_, int
     if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || fn == nullptr)
       return fail(SLX_E_UNSUPPORTED, "%s: cuTensorMapEncodeTiled is not available from this driver", what);
     encode = reinterpret_cast<EncodeFn>(fn);
+    encode_fn.store(encode, std::memory_order_release);
   }
   CUresult r = encode(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr,
                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -162,6 +166,40 @@ static int launch_scan_fwd_tc(const ScanDims &d, const void *U, const float *M, 
   if (rc) return rc;
   kern<<<dim3(d.NC, d.BH), kTcThreads, smem, st>>>(a);
   return check_launch("chunk_scan_fwd_tc");
+}
+
+static int sm_count() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
+// Forward chunk scan, persistent warp-specialised kernel (scan_ws_fwd.cuh)
+template <typename T>
+static int launch_scan_fwd_ws(const ScanDims &d, const void *U, const float *M, const float *K, const void *B,
+                              const void *C, const void *starts, const float *Bprev, const float *Uprev, void *Y,
+                              cudaStream_t st) {
+  ScanFwdArgs<T> a{(const T *)U, (const T *)B, (const T *)C, M, K, (const float *)starts, Bprev, Uprev, (T *)Y, nullptr, d};
+  auto kern = chunk_scan_fwd_ws_kernel<T>;
+  const size_t smem = scan_ws_fwd_smem_bytes();
+  int rc = set_smem(kern, smem);
+  if (rc) return rc;
+  WsFwdMaps maps;
+  if ((rc = make_tile_map<T>(&maps.C, C, d.BH, d.T, d.D, 128, "chunk_scan_fwd"))) return rc;
+  if ((rc = make_tile_map<T>(&maps.B, B, d.BH, d.T, d.D, 128, "chunk_scan_fwd"))) return rc;
+  if ((rc = make_tile_map<T>(&maps.Z, starts, d.BH * d.NC, d.P, d.D, 64, "chunk_scan_fwd"))) return rc;
+  if ((rc = make_tile_map<T>(&maps.U, U, d.BH, d.T, d.P, 128, "chunk_scan_fwd"))) return rc;
+  if ((rc = make_tile_map<T>(&maps.Y, Y, d.BH, d.T, d.P, 128, "chunk_scan_fwd"))) return rc;
+  const int total = d.BH * d.NC;
+  const int grid = total < sm_count() ? total : sm_count();
+  kern<<<grid, kWsThreads, smem, st>>>(a, maps);
+  return check_launch("chunk_scan_fwd_ws");
 }
 
 template <typename T, int MODE>
@@ -189,6 +227,26 @@ static int launch_scan_bwd_tc(const ScanDims &d, const ScanBwdArgs<T> &a, cudaSt
   if (rc) return rc;
   kern<<<dim3(d.NC, d.BH), kTcBwdThreads, smem, st>>>(a, maps);
   return check_launch("chunk_scan_bwd_tc");
+}
+
+// Per-chunk backward, persistent warp-specialised kernel (scan_ws_bwd.cuh)
+template <typename T>
+static int launch_scan_bwd_ws(const ScanDims &d, const ScanBwdArgs<T> &a, cudaStream_t st) {
+  auto kern = chunk_scan_bwd_ws_kernel<T>;
+  const size_t smem = scan_ws_bwd_smem_bytes();
+  int rc = set_smem(kern, smem);
+  if (rc) return rc;
+  WsBwdMaps maps;
+  if ((rc = make_tile_map<T>(&maps.C, a.C, d.BH, d.T, d.D, 128, "chunk_scan_bwd"))) return rc;
+  if ((rc = make_tile_map<T>(&maps.B, a.B, d.BH, d.T, d.D, 128, "chunk_scan_bwd"))) return rc;
+  if ((rc = make_tile_map<T>(&maps.Z, a.starts, d.BH * d.NC, d.P, d.D, 64, "chunk_scan_bwd"))) return rc;
+  if ((rc = make_tile_map<T>(&maps.Lm, a.d_inc, d.BH * d.NC, d.P, d.D, 64, "chunk_scan_bwd"))) return rc;
+  if ((rc = make_tile_map<T>(&maps.U, a.U, d.BH, d.T, d.P, 128, "chunk_scan_bwd"))) return rc;
+  if ((rc = make_tile_map<T>(&maps.dY, a.dY, d.BH, d.T, d.P, 128, "chunk_scan_bwd"))) return rc;
+  const int total = d.BH * d.NC;
+  const int grid = total < sm_count() ? total : sm_count();
+  kern<<<grid, kWsThreads, smem, st>>>(a, maps);
+  return check_launch("chunk_scan_bwd_ws");
 }
 
 template <typename ST>
@@ -311,7 +369,7 @@ int slx_abi_version(void) { return SLX_ABI_VERSION; }
 
 int slx_set_tensor_path(int enable) {
   int old = g_use_tc;
-  g_use_tc = enable ? 1 : 0;
+  g_use_tc = enable < 0 ? 0 : (enable > 2 ? 2 : enable);
   return old;
 }
 
@@ -381,6 +439,11 @@ int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M, c
   SLX_REQUIRE(U && M && K && B && C && chunk_starts && Y, SLX_E_NULL, "chunk_scan_fwd: NULL tensor");
   SLX_REQUIRE_ALIGNED("chunk_scan_fwd", U, M, K, B, C, chunk_starts, B_prev, U_prev, Y);
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
+  if (use_tc(s) && g_use_tc == 2) {
+    if (s->dtype == SLX_BF16)
+      return launch_scan_fwd_ws<__nv_bfloat16>(d, U, M, K, B, C, chunk_starts, B_prev, U_prev, Y, as_stream(stream));
+    return launch_scan_fwd_ws<__half>(d, U, M, K, B, C, chunk_starts, B_prev, U_prev, Y, as_stream(stream));
+  }
   if (use_tc(s)) {
     if (s->dtype == SLX_BF16)
       return launch_scan_fwd_tc<__nv_bfloat16>(d, U, M, K, B, C, (const float *)chunk_starts, B_prev, U_prev, Y,
@@ -480,6 +543,7 @@ int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M, c
                       (const float *)d_inc, zdot,
                       B_prev, U_prev, (T_ *)dU, (T_ *)dB, (T_ *)dC, dM, dK, carryB, carryU, d};
     if constexpr (!std::is_same<T_, float>::value) {
+      if (tc && g_use_tc == 2) return launch_scan_bwd_ws<T_>(d, a, as_stream(stream));
       if (tc) return launch_scan_bwd_tc<T_>(d, a, as_stream(stream));
     }
     SLX_DISPATCH_L(d.L, rc = (launch_scan_bwd<T_, L_>(d, a, as_stream(stream))));

@@ -113,6 +113,60 @@ __device__ __forceinline__ void tma_prefetch_map(const void *tensor_map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensor_map)) : "memory");
 }
 
+// ---- pieces of the warp-specialised (producer / issuer / worker) kernels ---------------------------
+__device__ __forceinline__ void mbar_arrive(uint32_t mbar_saddr) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar_saddr) : "memory");
+}
+// Bulk tensor store of a swizzled shared-memory tile (rows outside the tensor are not written).
+// Never give it a negative coordinate.
+__device__ __forceinline__ void tma_store_3d(const void *tensor_map, int x, int y, int z, uint32_t src_saddr) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(
+                   reinterpret_cast<uint64_t>(tensor_map)),
+               "r"(x), "r"(y), "r"(z), "r"(src_saddr)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the issuing thread's earlier bulk stores have finished READING shared memory
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// Wait on an mbarrier phase inside a kernel whose warps play different roles.  Gives up after
+// `limit` clocks (about 0.2 s by default), and at once when another role has already given up:
+// *abort_flag (shared memory) is set by the first wait that runs out and read by all others, so
+// that a fault in one role ends the whole CTA within one timeout instead of one per wait.
+__device__ __forceinline__ bool mbar_wait_abortable(uint32_t mbar_saddr, uint32_t parity, volatile int *abort_flag,
+                                                    long long limit = 400000000LL) {
+  long long t0 = 0;
+  for (int spin = 0;; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(mbar_saddr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (*abort_flag) return false;
+    if (spin == 0) t0 = clock64();
+    else if ((spin & 15) == 0 && clock64() - t0 > limit) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+// i * v on a packed pair (re, im) of halfs: (re, im) -> (-im, re).  One byte permute and one xor;
+// works for bf16 and fp16 alike (sign in the top bit).
+__device__ __forceinline__ uint32_t jword(uint32_t w) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %1, 0x1032;" : "=r"(r) : "r"(w));
+  return r ^ 0x00008000u;
+}
+__device__ __forceinline__ uint4 jchunk(uint4 v) { return make_uint4(jword(v.x), jword(v.y), jword(v.z), jword(v.w)); }
+
 // Bounded wait: gives up after about a second of SM clock and reports failure
 // instead of spinning forever (each try_wait poll blocks for a short
 // hardware-defined time by itself).
@@ -194,6 +248,19 @@ __device__ __forceinline__ void tmem_ld16_wait(uint32_t (&r)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;"
                : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
                  "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
+// 8-column variants
+__device__ __forceinline__ void tmem_ld8_issue(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld8_wait(uint32_t (&r)[8]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
                :
                : "memory");
 }

@@ -13,14 +13,20 @@ from util import rel_err
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True)
-def _tensor_path_on():
+TC = 2  # tensor-core kernel family under test (set per test by the fixture)
+
+
+@pytest.fixture(autouse=True, params=[1, 2], ids=["per-chunk", "persistent"])
+def _tensor_path_on(request):
+    """Every test of this file runs with both tcgen05 kernel families."""
     import slinoss_b200 as sb
 
-    sb.set_tensor_path(True)
+    global TC
+    TC = request.param
+    prev = sb.set_tensor_path(TC)
     yield
-    sb.set_tensor_path(True)
-    assert sb.read_tc_status() == 0, "a bounded MMA-completion wait ran out"
+    sb.set_tensor_path(prev)
+    assert sb.read_tc_status() == 0, "a bounded completion wait ran out"
 
 
 @pytest.mark.parametrize("N,T,dtype,streaming", [
@@ -40,7 +46,7 @@ def test_chunk_scan_stage_tc_vs_exact(N, T, dtype, streaming):
     y_tc = sb.chunk_scan_b200(inp["U"], inp["M"], inp["K"], inp["B"], inp["C"], starts, **kw)
     sb.set_tensor_path(False)
     y_ex = sb.chunk_scan_b200(inp["U"], inp["M"], inp["K"], inp["B"], inp["C"], starts, **kw)
-    sb.set_tensor_path(True)
+    sb.set_tensor_path(TC)
     # both round Y to the half dtype; the tensor path also rounds its operands
     assert rel_err(to_np(y_tc), to_np(y_ex)) < 1e-2
     Yo, _, _ = oracle_fwd_bwd(inp)
@@ -66,7 +72,7 @@ def test_increment_stage_tc_vs_exact(N, T, dtype):
     inc_tc, m_tc = sb.chunk_increment_b200(inp["U"], inp["M"], inp["K"], inp["B"], **kw)
     sb.set_tensor_path(False)
     inc_ex, m_ex = sb.chunk_increment_b200(inp["U"], inp["M"], inp["K"], inp["B"], **kw)
-    sb.set_tensor_path(True)
+    sb.set_tensor_path(TC)
     assert rel_err(to_np(m_tc), to_np(m_ex)) < 1e-6
     assert rel_err(to_np(inc_tc), to_np(inc_ex)) < 5e-3
 
@@ -86,7 +92,7 @@ def test_backward_tc_vs_exact_and_oracle(N, T, dtype, streaming):
     Y, fin, g_tc = run_b200_fwd_bwd(inp, 128)
     sb.set_tensor_path(False)
     Y2, fin2, g_ex = run_b200_fwd_bwd(inp, 128)
-    sb.set_tensor_path(True)
+    sb.set_tensor_path(TC)
     Yo, fino, go = oracle_fwd_bwd(inp)
     errs_ex, errs_or = {}, {}
     for k in SCAN_GRADS:
