@@ -344,10 +344,17 @@ int slx_cconv1d_bwd_noalloc(const slx_conv_shape *s, const void *x,
 /* ---- diagnostics ----------------------------------------------------------- */
 
 /* Half inputs with chunk 128, P 64 and 2N in {64,128,192,256} run on the
- * tcgen05 tensor-core kernels; everything else, and everything after
+ * tcgen05 tensor-core kernels: enable = 2 the persistent warp-specialised ones,
+ * enable = 1 the one-chunk-per-CTA ones; everything else, and everything after
  * slx_set_tensor_path(0), runs on the fp32-exact CUDA-core kernels.  Returns the
  * previous setting.  (Process-wide switch for tests; no reference counterpart.) */
 int slx_set_tensor_path(int enable);
+
+/* The persistent tensor-core kernels launch one CTA per SM, each walking several
+ * chunks.  max_ctas > 0 caps the number of CTAs (a tuning and test knob: a small cap
+ * makes small inputs walk the multi-chunk loop); 0 restores one per SM.  Returns the
+ * previous cap.  Process-wide; no reference counterpart. */
+int slx_set_persistent_ctas(int max_ctas);
 
 /* Synchronising read-and-clear (one atomic exchange on the device) of the status
  * word of the tensor-core kernels on the CURRENT device: *host_out != 0 means a

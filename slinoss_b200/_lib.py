@@ -69,6 +69,7 @@ SIGNATURES = {
     "slx_scanprep_bwd": (c_int32, [POINTER(PrepShape)] + [_P] * 15 + [c_size_t, _P]),
     "slx_cconv1d_bwd_noalloc": (c_int32, [POINTER(ConvShape)] + [_P] * 11),
     "slx_set_tensor_path": (c_int32, [c_int32]),
+    "slx_set_persistent_ctas": (c_int32, [c_int32]),
     "slx_read_tc_status": (c_int32, [POINTER(c_int32)]),
     "slx_read_scan_status": (c_int32, [POINTER(c_int32)]),
     "slx_decode_step": (c_int32, [POINTER(DecodeShape)] + [_P] * 15),
@@ -222,6 +223,12 @@ def set_tensor_path(enable) -> int:
     value (0, 1 or 2)."""
     code = 2 if enable is True else (0 if enable is False else int(enable))
     return int(lib().slx_set_tensor_path(code))
+
+
+def set_persistent_ctas(max_ctas: int) -> int:
+    """Cap on the CTAs of the persistent tensor-core kernels (0 = one per SM, the default).
+    Returns the previous cap."""
+    return int(lib().slx_set_persistent_ctas(int(max_ctas)))
 
 
 def _status_device(device) -> torch.device:

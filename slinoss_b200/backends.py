@@ -126,4 +126,31 @@ class B200MixerDecodeBackend:
         return gated, self.state_cls(state=fin, b_prev=b_last, u_prev=u_last)
 
 
-__all__ = ["B200ScanBackend", "B200ScanPrepBackend", "B200CConv1dBackend", "B200MixerDecodeBackend"]
+def use_b200_backends(model) -> int:
+    """Point every ``SLinOSSMixer`` inside ``model`` (a mixer, a block, a whole ``NextCharLM``) at
+    the four B200 backends, the way the reference's own workload builder swaps backends
+    (scripts/perf/_nextchar.py:101-127: ``module.backend``, ``module.scanprep.backend``,
+    ``module.cconv_backend``, ``module.decode_backend``).  The reference package must be
+    importable; its own ``ScanInputs`` / ``ScanState`` classes are used for the values handed
+    back to the mixer.  Returns the number of mixers switched."""
+    from slinoss.layers import SLinOSSMixer
+    from slinoss.layers.backend import ScanInputs as RefScanInputs
+    from slinoss.layers.state import ScanState as RefScanState
+
+    scan = B200ScanBackend(state_cls=RefScanState)
+    prep = B200ScanPrepBackend(inputs_cls=RefScanInputs)
+    conv = B200CConv1dBackend()
+    dec = B200MixerDecodeBackend(state_cls=RefScanState)
+    n = 0
+    for module in model.modules():
+        if isinstance(module, SLinOSSMixer):
+            module.backend = scan
+            module.scanprep.backend = prep
+            module.cconv_backend = conv
+            module.decode_backend = dec
+            n += 1
+    return n
+
+
+__all__ = ["B200ScanBackend", "B200ScanPrepBackend", "B200CConv1dBackend", "B200MixerDecodeBackend",
+           "use_b200_backends"]

@@ -168,6 +168,10 @@ static int launch_scan_fwd_tc(const ScanDims &d, const void *U, const float *M, 
   return check_launch("chunk_scan_fwd_tc");
 }
 
+// CTAs of the persistent kernels: one per SM unless a smaller number was asked for
+// (slx_set_persistent_ctas; the tests use it to walk the multi-chunk loop on small inputs)
+static std::atomic<int> g_max_ctas{0};
+
 static int sm_count() {
   static std::atomic<int> cached[64];
   int dev = 0;
@@ -178,6 +182,13 @@ static int sm_count() {
     cached[dev].store(n, std::memory_order_relaxed);
   }
   return n;
+}
+
+static int persistent_grid(int total) {
+  int g = sm_count();
+  const int cap = g_max_ctas.load(std::memory_order_relaxed);
+  if (cap > 0 && cap < g) g = cap;
+  return total < g ? total : g;
 }
 
 // Forward chunk scan, persistent warp-specialised kernel (scan_ws_fwd.cuh)
@@ -196,8 +207,7 @@ static int launch_scan_fwd_ws(const ScanDims &d, const void *U, const float *M, 
   if ((rc = make_tile_map<T>(&maps.Z, starts, d.BH * d.NC, d.P, d.D, 64, "chunk_scan_fwd"))) return rc;
   if ((rc = make_tile_map<T>(&maps.U, U, d.BH, d.T, d.P, 128, "chunk_scan_fwd"))) return rc;
   if ((rc = make_tile_map<T>(&maps.Y, Y, d.BH, d.T, d.P, 128, "chunk_scan_fwd"))) return rc;
-  const int total = d.BH * d.NC;
-  const int grid = total < sm_count() ? total : sm_count();
+  const int grid = persistent_grid(d.BH * d.NC);
   kern<<<grid, kWsThreads, smem, st>>>(a, maps);
   return check_launch("chunk_scan_fwd_ws");
 }
@@ -243,8 +253,7 @@ static int launch_scan_bwd_ws(const ScanDims &d, const ScanBwdArgs<T> &a, cudaSt
   if ((rc = make_tile_map<T>(&maps.Lm, a.d_inc, d.BH * d.NC, d.P, d.D, 64, "chunk_scan_bwd"))) return rc;
   if ((rc = make_tile_map<T>(&maps.U, a.U, d.BH, d.T, d.P, 128, "chunk_scan_bwd"))) return rc;
   if ((rc = make_tile_map<T>(&maps.dY, a.dY, d.BH, d.T, d.P, 128, "chunk_scan_bwd"))) return rc;
-  const int total = d.BH * d.NC;
-  const int grid = total < sm_count() ? total : sm_count();
+  const int grid = persistent_grid(d.BH * d.NC);
   kern<<<grid, kWsThreads, smem, st>>>(a, maps);
   return check_launch("chunk_scan_bwd_ws");
 }
@@ -381,6 +390,10 @@ int slx_read_phase_clock(long long *host_out64) {
   return SLX_OK;
 }
 #endif
+
+int slx_set_persistent_ctas(int max_ctas) {
+  return g_max_ctas.exchange(max_ctas > 0 ? max_ctas : 0, std::memory_order_relaxed);
+}
 
 int slx_read_tc_status(int *host_out) {
   SLX_REQUIRE(host_out != nullptr, SLX_E_NULL, "read_tc_status: NULL pointer");

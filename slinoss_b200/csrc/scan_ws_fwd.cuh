@@ -36,7 +36,8 @@ struct alignas(64) WsFwdMaps {
 constexpr int kWsWorkers = 512;
 constexpr int kWsThreads = kWsWorkers + 64;
 constexpr int kWsStageBytes = 57344;  // C 16K | B 16K + Z0 8K | JC 16K
-constexpr size_t scan_ws_fwd_smem_bytes() { return 1024 + 2 * kWsStageBytes + 16384 + 32768 + 12288; }
+constexpr int kWsFwdScal = 13312;     // per-chunk scalars and the staged rows (12,544 bytes used)
+constexpr size_t scan_ws_fwd_smem_bytes() { return 1024 + 2 * kWsStageBytes + 16384 + 32768 + kWsFwdScal; }
 
 template <typename T>
 __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFwdArgs<T> a,
@@ -47,7 +48,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
       reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char *tU = base + 2 * kWsStageBytes;  // [128][64] U (row 127 <- u_{-1})
   unsigned char *tS = tU + 16384;                // 2 x [128][64] S'; block 0 doubles as the Y staging tile
-  unsigned char *sc = tS + 32768;                // scalars, 12 KB
+  unsigned char *sc = tS + 32768;                // scalars (kWsFwdScal bytes)
   float *lp = reinterpret_cast<float *>(sc);                 // 128
   float2 *ph = reinterpret_cast<float2 *>(lp + L);           // 128
   float2 *mraw = ph + L;                                     // 128
@@ -59,6 +60,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
   float4 *Kst = reinterpret_cast<float4 *>(Mst + 2 * L);     // 2 x 128 staged K rows
   T *bpst = reinterpret_cast<T *>(Kst + 2 * L);              // 2 x 256 staged b_{-1}
   T *upst = bpst + 2 * 256;                                  // 2 x 64 staged u_{-1}
+  static_assert(512 + 4 * 1024 + 256 + 256 + 2048 + 4096 + 2 * 256 * 2 + 2 * 64 * 2 <= kWsFwdScal, "scalar area too small");
   __shared__ uint64_t bars[12];  // full[2] jready[2] empty[2] accfull sready ydone ufull tmemfree wbar
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag, slow_flag;

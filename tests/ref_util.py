@@ -29,28 +29,10 @@ def import_reference():
 
 
 def use_b200_backends(model) -> int:
-    """Point every ``SLinOSSMixer`` inside ``model`` at the four B200 backends, the way the
-    reference's own workload builder swaps backends (scripts/perf/_nextchar.py:101-127).
-    Returns the number of mixers switched."""
-    from slinoss.layers import SLinOSSMixer
-    from slinoss.layers.backend import ScanInputs
-    from slinoss.layers.state import ScanState
-
+    """The package's own helper (every ``SLinOSSMixer`` inside ``model`` -> the four B200 backends)."""
     import slinoss_b200 as sb
 
-    scan = sb.B200ScanBackend(state_cls=ScanState)
-    prep = sb.B200ScanPrepBackend(inputs_cls=ScanInputs)
-    conv = sb.B200CConv1dBackend()
-    dec = sb.B200MixerDecodeBackend(state_cls=ScanState)
-    n = 0
-    for module in model.modules():
-        if isinstance(module, SLinOSSMixer):
-            module.backend = scan
-            module.scanprep.backend = prep
-            module.cconv_backend = conv
-            module.decode_backend = dec
-            n += 1
-    return n
+    return sb.use_b200_backends(model)
 
 
 def use_reference_backends(model) -> int:

@@ -16,16 +16,21 @@ pytestmark = pytest.mark.gpu
 TC = 2  # tensor-core kernel family under test (set per test by the fixture)
 
 
-@pytest.fixture(autouse=True, params=[1, 2], ids=["per-chunk", "persistent"])
+@pytest.fixture(autouse=True, params=[(1, 0), (2, 0), (2, 3)], ids=["per-chunk", "persistent", "persistent-3-ctas"])
 def _tensor_path_on(request):
-    """Every test of this file runs with both tcgen05 kernel families."""
+    """Every test of this file runs with both tcgen05 kernel families; the persistent one also with
+    three CTAs only, so that every CTA walks several chunks (ring and barrier phases wrap around,
+    the staging buffers alternate) on these small inputs."""
     import slinoss_b200 as sb
+    from slinoss_b200 import _lib
 
     global TC
-    TC = request.param
+    TC, ctas = request.param
     prev = sb.set_tensor_path(TC)
+    prev_ctas = _lib.set_persistent_ctas(ctas)
     yield
     sb.set_tensor_path(prev)
+    _lib.set_persistent_ctas(prev_ctas)
     assert sb.read_tc_status() == 0, "a bounded completion wait ran out"
 
 
