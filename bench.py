@@ -392,9 +392,11 @@ def scan_stage_timings(inp, b, h, T, P, N, L, dtype, reps=10, warm=3, only=None)
     out = []
     for name, fn, nbytes, flops, bound in plan:
         if only is not None and name != only:
-            fn()  # keeps the inputs of the later stages defined
+            fn()  # the stages before the chosen one produce its inputs
             continue
         out.append(_stage(name, _time_kernel(fn, reps, warm), nbytes, flops, peaks, bound))
+        if only is not None:
+            break
     torch.cuda.synchronize()
     return out
 

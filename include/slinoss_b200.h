@@ -341,6 +341,32 @@ int slx_cconv1d_bwd_noalloc(const slx_conv_shape *s, const void *x,
                             float *dweight, float *dbias, float *dstate,
                             void *stream);
 
+/* ---- mixer glue: skip, re-layout and gate in one pass ---------------------------- */
+
+typedef struct {
+  int32_t batch, T, heads, P; /* P a multiple of 8 */
+  int32_t dtype;              /* slx_dtype of y, u, gate, out and their gradients */
+  int64_t gate_stride;        /* elements between tokens of gate (a column slice of a wider row is fine) */
+  int64_t gate_batch_stride;  /* elements between batches of gate */
+} slx_glue_shape;
+
+/* Replaces SLinOSSMixer._apply_gate_skip (slinoss/layers/mixer.py:585-599) without its
+ * output norm: out (b,T,H*P) = (y + skip * u) re-laid from (b,H,T,P), times silu(gate).
+ * y, u (b,H,T,P); gate (b,T,H*P) with the given strides; skip (H*P) fp32; out contiguous.
+ * All pointers 16-byte aligned. */
+int slx_gate_skip_fwd(const slx_glue_shape *s, const void *y, const void *u,
+                      const void *gate, const float *skip, void *out, void *stream);
+
+size_t slx_gate_skip_bwd_workspace_bytes(const slx_glue_shape *s);
+
+/* VJP of slx_gate_skip_fwd: d_out (b,T,H*P) contiguous -> dy, du (b,H,T,P), d_gate
+ * (b,T,H*P) contiguous, d_skip (H*P) fp32 (overwritten; two-level fixed-order sum
+ * through the workspace, no atomics). */
+int slx_gate_skip_bwd(const slx_glue_shape *s, const void *y, const void *u,
+                      const void *gate, const float *skip, const void *d_out, void *dy,
+                      void *du, void *d_gate, float *d_skip, void *workspace,
+                      size_t workspace_bytes, void *stream);
+
 /* ---- diagnostics ----------------------------------------------------------- */
 
 /* Half inputs with chunk 128, P 64 and 2N in {64,128,192,256} run on the

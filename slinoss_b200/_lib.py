@@ -41,6 +41,11 @@ class DecodeShape(Structure):
                 ("theta_bound", c_float), ("k_max", c_float), ("eps", c_float)]
 
 
+class GlueShape(Structure):
+    _fields_ = [("batch", c_int32), ("T", c_int32), ("heads", c_int32), ("P", c_int32), ("dtype", c_int32),
+                ("gate_stride", c_int64), ("gate_batch_stride", c_int64)]
+
+
 class ConvShape(Structure):
     _fields_ = [("batch", c_int32), ("T", c_int32), ("channels", c_int32), ("width", c_int32),
                 ("dtype", c_int32), ("silu", c_int32), ("x_stride", c_int64),
@@ -68,6 +73,9 @@ SIGNATURES = {
     "slx_scanprep_bwd_workspace_bytes": (c_size_t, [POINTER(PrepShape)]),
     "slx_scanprep_bwd": (c_int32, [POINTER(PrepShape)] + [_P] * 15 + [c_size_t, _P]),
     "slx_cconv1d_bwd_noalloc": (c_int32, [POINTER(ConvShape)] + [_P] * 11),
+    "slx_gate_skip_fwd": (c_int32, [POINTER(GlueShape)] + [_P] * 6),
+    "slx_gate_skip_bwd_workspace_bytes": (c_size_t, [POINTER(GlueShape)]),
+    "slx_gate_skip_bwd": (c_int32, [POINTER(GlueShape)] + [_P] * 10 + [c_size_t, _P]),
     "slx_set_tensor_path": (c_int32, [c_int32]),
     "slx_set_persistent_ctas": (c_int32, [c_int32]),
     "slx_read_tc_status": (c_int32, [POINTER(c_int32)]),

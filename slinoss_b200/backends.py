@@ -14,12 +14,14 @@ mirror types, which expose the same attributes.
 
 from __future__ import annotations
 
+import types
 from typing import Optional, Tuple, Union
 
 import torch
 
-from .ops.cconv1d import cconv1d_b200
+from .ops.cconv1d import cconv1d_b200, cconv1d_update_b200
 from .ops.decode import mixer_decode_step_b200
+from .ops.glue import gate_skip_b200
 from .ops.scanprep import scanprep_b200
 from .ops.v2x2ssd import v2x2ssd_b200
 from .types import ScanInputs, ScanState
@@ -126,13 +128,70 @@ class B200MixerDecodeBackend:
         return gated, self.state_cls(state=fin, b_prev=b_last, u_prev=u_last)
 
 
-def use_b200_backends(model) -> int:
+def _conv_step_b200(self, value_raw: torch.Tensor, conv_state: Optional[torch.Tensor]):
+    """Replacement for ``SLinOSSMixer._apply_causal_depthwise_conv_step`` (mixer.py:614-676): the
+    conv half of a decode token (conv + SiLU, rolling state) in one ``slx_cconv1d_update`` launch.
+    The reference reaches its vendored ``causal_conv1d_update`` directly there, not through a
+    backend object, so the method itself is replaced on the instance."""
+    if value_raw.ndim != 2 or value_raw.shape[-1] != self.d_inner:
+        raise ValueError(f"Expected value_raw shape (batch, {self.d_inner}), got {tuple(value_raw.shape)}.")
+    state_len = max(int(self.d_conv) - 1, 0)
+    if state_len == 0 or value_raw.device.type != "cuda":
+        return type(self)._apply_causal_depthwise_conv_step(self, value_raw, conv_state)
+    init = self._validate_conv_state(conv_state, batch=int(value_raw.shape[0]), state_len=state_len,
+                                     device=value_raw.device, dtype=value_raw.dtype)
+    return cconv1d_update_b200(value_raw, self.dw_weight, self.dw_bias, init, activation="silu")
+
+
+def _mixer_forward_fused(self, x: torch.Tensor, *, state=None, return_state: bool = False):
+    """``SLinOSSMixer.forward`` (mixer.py:534-583) with the elementwise glue folded into the kernels on
+    either side of it: the SiLU after the conv (mixer.py:562) runs in the conv kernel's epilogue
+    (``activation="silu"``), and skip, re-layout and gate (``_apply_gate_skip``, mixer.py:585-599) run
+    as one pass (``gate_skip_b200``).  Same arguments, results and state handling as the original;
+    installed on a mixer instance by ``use_b200_backends(..., fuse_glue=True)``."""
+    if x.ndim != 3 or x.shape[-1] != self.d_model:
+        raise ValueError(f"Expected x shape (batch, T, {self.d_model}), got {tuple(x.shape)}.")
+    batch, T, _ = map(int, x.shape)
+    if T == 0 or x.device.type != "cuda" or int(self.d_conv) < 2 or int(self.d_head) % 8 != 0:
+        return type(self).forward(self, x, state=state, return_state=return_state)
+    proj = self.in_proj(x)
+    gate, value_raw, params, bc_flat = torch.split(
+        proj, [self.d_inner, self.d_inner, self.param_proj_dim, self.bc_proj_dim], dim=-1)
+    conv_state_in = None if state is None else state.conv
+    if conv_state_in is not None:
+        conv_state_in = self._validate_conv_state(conv_state_in, batch=batch, state_len=int(self.d_conv) - 1,
+                                                  device=x.device, dtype=value_raw.dtype)
+    value, conv_state = cconv1d_b200(value_raw, self.dw_weight, self.dw_bias, conv_state_in, activation="silu")
+    bc = self._reshape_bc(bc_flat, batch, T)
+    scan_inputs = self._build_scan_inputs(value=value, params=params, bc=bc)
+    scan_state_in = None if state is None else state.scan
+    scan_result = self._run_scan_backend(scan_inputs, scan_state_in, return_state)
+    scan_y, scan_state = scan_result if return_state else (scan_result, None)
+    gated = gate_skip_b200(scan_y, scan_inputs.U, gate, self.skip)
+    if self.output_norm is not None:
+        gated = self.output_norm(gated)
+    out = self.out_proj(gated)
+    if not return_state:
+        return out
+    return out, _mixer_state(conv_state, scan_state)
+
+
+def _mixer_state(conv_state, scan_state):
+    from slinoss.layers.state import SLinOSSMixerState
+
+    return SLinOSSMixerState(conv=conv_state, scan=scan_state)
+
+
+def use_b200_backends(model, *, decode_conv: bool = True, fuse_glue: bool = False) -> int:
     """Point every ``SLinOSSMixer`` inside ``model`` (a mixer, a block, a whole ``NextCharLM``) at
     the four B200 backends, the way the reference's own workload builder swaps backends
     (scripts/perf/_nextchar.py:101-127: ``module.backend``, ``module.scanprep.backend``,
-    ``module.cconv_backend``, ``module.decode_backend``).  The reference package must be
-    importable; its own ``ScanInputs`` / ``ScanState`` classes are used for the values handed
-    back to the mixer.  Returns the number of mixers switched."""
+    ``module.cconv_backend``, ``module.decode_backend``).  With ``decode_conv`` the one-token conv
+    step of each mixer (not behind a backend object in the reference) is replaced as well; with
+    ``fuse_glue`` each mixer's ``forward`` is replaced by ``_mixer_forward_fused`` (same results; the
+    SiLU after the conv and the skip / re-layout / gate pass run inside kernels).  The
+    reference package must be importable; its own ``ScanInputs`` / ``ScanState`` classes are used
+    for the values handed back to the mixer.  Returns the number of mixers switched."""
     from slinoss.layers import SLinOSSMixer
     from slinoss.layers.backend import ScanInputs as RefScanInputs
     from slinoss.layers.state import ScanState as RefScanState
@@ -148,6 +207,10 @@ def use_b200_backends(model) -> int:
             module.scanprep.backend = prep
             module.cconv_backend = conv
             module.decode_backend = dec
+            if decode_conv:
+                module._apply_causal_depthwise_conv_step = types.MethodType(_conv_step_b200, module)
+            if fuse_glue:
+                module.forward = types.MethodType(_mixer_forward_fused, module)
             n += 1
     return n
 

@@ -41,12 +41,18 @@ def _headers():
 def _compile_and_link(sources, lib: Path, force: bool, verbose: bool) -> Path:
     OUT_DIR.mkdir(exist_ok=True)
     newest = max(f.stat().st_mtime for f in list(sources) + _headers())
-    if not force and lib.exists() and lib.stat().st_mtime >= newest:
+    diag = os.environ.get("SLX_DIAG") == "1"
+    marker = OUT_DIR / (lib.stem + ".flags")
+    flags = "diag" if diag else "release"
+    same_flags = marker.exists() and marker.read_text().strip() == flags
+    if not force and same_flags and lib.exists() and lib.stat().st_mtime >= newest:
         return lib
 
     def compile_one(src: Path) -> Path:
         obj = OUT_DIR / (src.stem + ".o")
         cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        if diag:  # SLX_DIAG=1: phase-clock stamps in the tensor-core kernels (never the shipped build)
+            cmd.insert(1, "-DSLX_DIAG")
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -66,6 +72,7 @@ def _compile_and_link(sources, lib: Path, force: bool, verbose: bool) -> Path:
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     os.replace(tmp, lib)
+    marker.write_text(flags + "\n")
     return lib
 
 

@@ -28,14 +28,9 @@ __device__ __forceinline__ void coef_backward(const CoefCtx &c, const PrepHyper 
   float ddt = rdot(c.k2, dkps) + rdot(csub(c.k1, c.k2), dkcs);
   float2 k1p, k2p;
   const float2 z = c.z;
-  if (c.small) {
-    float2 z2 = cmul(z, z);
-    k1p = make_float2(0.5f + z.x / 3.f + z2.x / 8.f, z.y / 3.f + z2.y / 8.f);
-    k2p = make_float2(1.f / 3.f + z.x / 4.f + z2.x / 10.f, z.y / 4.f + z2.y / 10.f);
-  } else {
-    k1p = c.k2;                                              // d/dz (e^z-1)/z
-    k2p = cdiv(csub(c.rho, cscale(c.k2, 2.f)), z);           // d/dz (e^z(z-1)+1)/z^2
-  }
+  k1p = c.k2;  // d/dz (e^z-1)/z = kappa2, in both branches
+  if (c.small) k2p = c.k2p;                                      // series (prep_coef.cuh)
+  else k2p = cdiv(csub(c.rho, cscale(c.k2, 2.f)), z);            // d/dz (e^z(z-1)+1)/z^2 = (e^z - 2 kappa2)/z
   // dz = conj(k1') dk1 + conj(k2') dk2 + conj(rho) dM
   float2 dz = cadd(cadd(cmul(cconj(k1p), dk1), cmul(cconj(k2p), dk2)), cmul(cconj(c.rho), dm));
   float dr = dz.x / c.r;

@@ -20,7 +20,7 @@ struct CoefOut {
 struct CoefCtx {
   float dt_u, dt, gamma, omega, e_gdt, r_struct, th_struct, r_dir_u, r_direct, th_t, th_direct;
   float mix_r, mix_th, mix_kp, mix_kc, tk[4], r, sig_p1;
-  float2 rho, z, k1, k2, kps, kcs, kpl, kcl;
+  float2 rho, z, k1, k2, k2p, kps, kcs, kpl, kcl;  // k2p = d kappa2 / dz where the series branch ran
   bool small;
 };
 
@@ -34,6 +34,39 @@ __device__ __forceinline__ float lerpf_(float a, float b, float w) {
 __device__ __forceinline__ float2 cdiv(float2 a, float2 b) {
   float inv = 1.f / (b.x * b.x + b.y * b.y);
   return make_float2((a.x * b.x + a.y * b.y) * inv, (a.y * b.x - a.x * b.y) * inv);
+}
+
+// FOH tap factors as power series (complex Horner, 11 terms: exact to fp32 for |z| <= 1/2):
+//   kappa1 = (e^z - 1)/z           = sum_k z^k / (k+1)!
+//   kappa2 = (e^z (z-1) + 1)/z^2   = sum_k (k+1) z^k / (k+2)!
+//   d kappa2/dz                    = sum_k (k+1)(k+2) z^k / (k+3)!        (d kappa1/dz = kappa2)
+// The closed forms cancel in fp32 (relative error ~6e-8 / |z|^2 for kappa2: 6e-4 at |z| = 0.01, which is where
+// the reference's own fp32 evaluation is that far from its float64 value); the series do not, so they are used
+// for every |z|^2 < 1/4 and the closed forms only beyond, where the cancellation is harmless.
+__device__ __forceinline__ void kappa_series(float2 z, float2 &k1, float2 &k2, float2 &k2p) {
+  constexpr int NT = 11;
+  float c1[NT], c2[NT], c3[NT];
+  float f = 1.f;  // (k+1)!
+#pragma unroll
+  for (int k = 0; k < NT; ++k) {
+    f *= (float)(k + 1);
+    c1[k] = 1.f / f;
+    c2[k] = (float)(k + 1) / (f * (float)(k + 2));
+    c3[k] = (float)(k + 1) * (float)(k + 2) / (f * (float)(k + 2) * (float)(k + 3));
+  }
+  float2 a1 = make_float2(c1[NT - 1], 0.f), a2 = make_float2(c2[NT - 1], 0.f), a3 = make_float2(c3[NT - 1], 0.f);
+#pragma unroll
+  for (int k = NT - 2; k >= 0; --k) {
+    a1 = cmul(a1, z);
+    a1.x += c1[k];
+    a2 = cmul(a2, z);
+    a2.x += c2[k];
+    a3 = cmul(a3, z);
+    a3.x += c3[k];
+  }
+  k1 = a1;
+  k2 = a2;
+  k2p = a3;
 }
 
 __device__ __forceinline__ CoefOut coef_forward(const float *p, const PrepHyper &h, CoefCtx *ctx) {
@@ -66,12 +99,12 @@ __device__ __forceinline__ CoefOut coef_forward(const float *p, const PrepHyper 
   sincosf(theta, &sn, &cs);
   float2 rho = make_float2(r * cs, r * sn);
   float2 z = make_float2(log_r, theta);
-  bool small = (log_r * log_r + theta * theta) < h.z_thr2;
-  float2 k1, k2;
+  // (the reference switches to a 3rd-order series below |z|^2 = z_thr2, layers/scanprep.py:255-268; the longer
+  // series used here agrees with it there to fp32 and stays exact up to the wider bound)
+  bool small = (log_r * log_r + theta * theta) < fmaxf(h.z_thr2, 0.25f);
+  float2 k1, k2, k2p = make_float2(0.f, 0.f);
   if (small) {
-    float2 z2 = cmul(z, z), z3 = cmul(z2, z);
-    k1 = make_float2(1.f + 0.5f * z.x + z2.x / 6.f + z3.x / 24.f, 0.5f * z.y + z2.y / 6.f + z3.y / 24.f);
-    k2 = make_float2(0.5f + z.x / 3.f + z2.x / 8.f + z3.x / 30.f, z.y / 3.f + z2.y / 8.f + z3.y / 30.f);
+    kappa_series(z, k1, k2, k2p);
   } else {
     k1 = cdiv(make_float2(rho.x - 1.f, rho.y), z);
     float2 num = cmul(rho, make_float2(z.x - 1.f, z.y));
@@ -90,7 +123,7 @@ __device__ __forceinline__ CoefOut coef_forward(const float *p, const PrepHyper 
     ctx->th_t = th_t; ctx->th_direct = th_direct; ctx->mix_r = mix_r; ctx->mix_th = mix_th;
     ctx->mix_kp = mix_kp; ctx->mix_kc = mix_kc; ctx->tk[0] = tk0; ctx->tk[1] = tk1; ctx->tk[2] = tk2;
     ctx->tk[3] = tk3; ctx->r = r; ctx->sig_p1 = sigmoidf_(p[1]); ctx->rho = rho; ctx->z = z; ctx->k1 = k1;
-    ctx->k2 = k2; ctx->kps = kps; ctx->kcs = kcs; ctx->kpl = kpl; ctx->kcl = kcl; ctx->small = small;
+    ctx->k2 = k2; ctx->k2p = k2p; ctx->kps = kps; ctx->kcs = kcs; ctx->kpl = kpl; ctx->kcl = kcl; ctx->small = small;
   }
   return o;
 }

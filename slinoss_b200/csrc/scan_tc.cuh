@@ -384,7 +384,13 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
       *reinterpret_cast<uint4 *>(a.Y + (tok0 + r) * P + 8 * j) = *reinterpret_cast<const uint4 *>(tQ + umma::swz_off(r, j));
   }
   SLX_FSTAMP(6);
-  if (!ok && tid == 0) atomicExch(&g_tc_status, 1);
+  if (__syncthreads_or(!ok)) {
+    // a bounded wait ran out: the rows just written came from unfinished products; overwrite them with NaN
+    // so that the failure shows in the data as well as in the status word
+    const T nanv = from_f<T>(__int_as_float(0x7fc00000));
+    for (int e = tid; e < valid * P; e += kTcThreads) a.Y[tok0 * P + e] = nanv;
+    if (tid == 0) atomicExch(&g_tc_status, 1);
+  }
   if (warp == 0) umma::tmem_dealloc(tmem, 256);
 #undef SLX_FSTAMP
 }
@@ -545,8 +551,11 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_outer_tc_kernel(OuterArgs
     }
   }
   umma::fence_before_sync();
-  __syncthreads();
-  if (!ok && tid == 0) atomicExch(&g_tc_status, 1);
+  if (__syncthreads_or(!ok)) {  // a bounded wait ran out: NaN instead of values from an unfinished product
+    const float nanf_ = __int_as_float(0x7fc00000);
+    for (int e = tid; e < P * d.D; e += kTcThreads) outc[e] = nanf_;
+    if (tid == 0) atomicExch(&g_tc_status, 1);
+  }
   if (warp == 0) umma::tmem_dealloc(tmem, 128);
 }
 

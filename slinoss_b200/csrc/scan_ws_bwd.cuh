@@ -46,8 +46,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_bwd_ws_kernel(ScanBw
   unsigned char *base =
       reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char *X = base, *Y = base + kBwX;
-  // pass 1: stage s at X + 49152 s: C | B~ | Z0 | Lambda; transform area JC | JLambda
-  unsigned char *tJC = X + 98304, *tJL = X + 114688;
+  // pass 1: stage s at X + 49152 s: C | B~ | Z0 | Lambda; two transform buffers JC | JLambda (the second one
+  // borrows the S' tile, which nothing else touches before phase S)
   // phase S / pass 2
   unsigned char *tWr = X, *tWi = X + 32768, *tYr = X + 65536, *tYi = X + 81920, *tUr = X + 98304, *tUi = X + 114688;
   unsigned char *tU = Y, *tdY = Y + 16384, *tS = Y + 32768;
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_bwd_ws_kernel(ScanBw
   T *rowst = reinterpret_cast<T *>(Kst + L);                   // 3 x 256 + 3 x 64: b_{-1} b_127 c_127 u_{-1} u_127 dy_127
   static_assert(512 * 2 + 1024 * 4 + 4096 + 1024 * 3 + 512 + 1024 * 3 + 576 + 1024 + 2048 + (3 * 256 + 3 * 64) * 2 <= kBwScal,
                 "scalar area too small");
-  __shared__ uint64_t bars[26];
+  __shared__ uint64_t bars[27];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag, slow_flag;
 
@@ -92,14 +92,14 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_bwd_ws_kernel(ScanBw
   enum {
     UDYFULL = 0, UPATCH = 1, ADONE = 2, AREAD = 3, P1FULL = 4, P1JREADY = 6, P1EMPTY = 7, ACC1FULL = 9, SREADY = 10,
     DUDONE = 11, WREADY = 12, DUREAD = 13, H2FULL = 14, H2EMPTY = 17, ACC2FULL = 20, ACC2FREE = 22, WBAR = 24,
-    REDREAD = 25
+    REDREAD = 25, P1JREADY2 = 26
   };
   constexpr int fmt = umma::HalfFmt<T>::value;
 
   if (tid == 0) {
-    for (int i = 0; i < 26; ++i) {
+    for (int i = 0; i < 27; ++i) {
       const bool wb = (i == UPATCH || i == AREAD || i == P1JREADY || i == SREADY || i == WREADY || i == DUREAD ||
-                       i == ACC2FREE || i == ACC2FREE + 1 || i == WBAR || i == REDREAD);
+                       i == ACC2FREE || i == ACC2FREE + 1 || i == WBAR || i == REDREAD || i == P1JREADY2);
       umma::mbar_init(BAR(i), wb ? 16u : 1u);
     }
     umma::fence_mbar_init();
@@ -119,7 +119,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_bwd_ws_kernel(ScanBw
   umma::fence_after_sync();
   const uint32_t tmem = tmem_slot;
   volatile int *ab = &abort_flag;
-  auto WAIT = [&](int i, uint32_t parity) { return umma::mbar_wait_abortable(BAR(i), parity, ab); };
+  auto WAIT = [&](int i, uint32_t parity) { return umma::mbar_wait_abortable(BAR(i), parity, ab); };  // one thread
+  auto WAITW = [&](int i, uint32_t parity) { return umma::mbar_wait_warp(BAR(i), parity, ab); };        // a whole warp
 
   if (warp == 16) {
     // ------------------------------------------------------------------ producer
@@ -135,6 +136,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_bwd_ws_kernel(ScanBw
           if (ok && NB >= 2) ok = WAIT(ACC2FULL + (lb ^ 1), (use[lb ^ 1] - 1) & 1);
           if (!ok) break;
         }
+        WS_STAMP(it == 2, 48);
         umma::mbar_expect_tx(BAR(UDYFULL), 32768u);
         umma::tma_load_3d(umma::smem_u32(tU), &maps.U, 0, t0, bh, BAR(UDYFULL));
         umma::tma_load_3d(umma::smem_u32(tdY), &maps.dY, 0, t0, bh, BAR(UDYFULL));
@@ -151,8 +153,10 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_bwd_ws_kernel(ScanBw
         }
         if (!ok) break;
         // second pass: its ring lies over the U, dY and S' tiles
+        WS_STAMP(it == 2, 49);
         ok = WAIT(WREADY, it & 1) && WAIT(DUDONE, it & 1);
         if (!ok) break;
+        WS_STAMP(it == 2, 50);
         for (int hs = 0; hs < 2 * NB && ok; ++hs, ++q2) {
           const int slot = q2 % 3, sl = hs >> 1;
           if (hs >= 3) ok = WAIT(H2EMPTY + slot, ((q2 / 3) - 1) & 1);  // (three free slots at the start of a chunk)
@@ -182,7 +186,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_bwd_ws_kernel(ScanBw
       const uint32_t sU = umma::smem_u32(tU), sdY = umma::smem_u32(tdY), sS = umma::smem_u32(tS);
       const uint32_t sWr = umma::smem_u32(tWr), sWi = umma::smem_u32(tWi), sYr = umma::smem_u32(tYr),
                      sYi = umma::smem_u32(tYi), sUr = umma::smem_u32(tUr), sUi = umma::smem_u32(tUi);
-      const uint32_t sJC = umma::smem_u32(tJC), sJL = umma::smem_u32(tJL);
       uint32_t g1 = 0, q2 = 0, it = 0, use[2] = {0, 0};
       bool ok = true;
       for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++it) {
@@ -191,9 +194,11 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_bwd_ws_kernel(ScanBw
           if (use[b] >= 1) ok = WAIT(ACC2FREE + b, (use[b] - 1) & 1);
         if (!ok) break;
         // ---- A = dY U~^T
+        WS_STAMP(it == 2, 32);
         ok = WAIT(UDYFULL, it & 1) && WAIT(UPATCH, it & 1);
         if (!ok) break;
         umma::fence_after_sync();
+        WS_STAMP(it == 2, 33);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma::mma_ss(tmem, umma::desc_kmajor(sdY, kk), umma::desc_kmajor(sU, kk), id_a, kk != 0);
@@ -204,13 +209,15 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_bwd_ws_kernel(ScanBw
         // ---- pass 1: [G | H] (re, im), T (re, im) over the state slabs
         for (int sl = 0; sl < NB && ok; ++sl, ++g1) {
           const int st = g1 & 1;
-          ok = WAIT(P1FULL + st, (g1 >> 1) & 1) && WAIT(P1JREADY, g1 & 1);
+          ok = WAIT(P1FULL + st, (g1 >> 1) & 1) && WAIT(st ? P1JREADY2 : P1JREADY, (g1 >> 1) & 1);
           if (!ok) break;
           umma::fence_after_sync();
+          WS_STAMP(it == 2, 34 + sl);
           const uint32_t sb = umma::smem_u32(X + st * 49152);
           const uint64_t dC = umma::desc_kmajor(sb, 0), dBZ = umma::desc_kmajor(sb + 16384, 0),
-                         dLm = umma::desc_kmajor(sb + 40960, 0), dJC = umma::desc_kmajor(sJC, 0),
-                         dJL = umma::desc_kmajor(sJL, 0);
+                         dLm = umma::desc_kmajor(sb + 40960, 0),
+                         dJC = umma::desc_kmajor(umma::smem_u32(st ? tS : X + 98304), 0),
+                         dJL = umma::desc_kmajor(umma::smem_u32(st ? tS + 16384 : X + 114688), 0);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const uint32_t adv = umma::kStepK * kk;
@@ -224,6 +231,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_bwd_ws_kernel(ScanBw
         }
         if (!ok) break;
         umma::commit(BAR(ACC1FULL));
+        WS_STAMP(it == 2, 38);
         // ---- dU~ (score path) = S'^T dY
         ok = WAIT(SREADY, it & 1);
         if (!ok) break;
@@ -243,9 +251,11 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_bwd_ws_kernel(ScanBw
           umma::fence_after_sync();
           {
             const int slot = q2 % 3;
+            WS_STAMP(it == 2, 40 + 2 * sl);
             ok = WAIT(H2FULL + slot, (q2 / 3) & 1);
             if (!ok) break;
             umma::fence_after_sync();
+            WS_STAMP(it == 2, 41 + 2 * sl);
             const uint32_t hb = umma::smem_u32(Y + slot * 24576);
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {

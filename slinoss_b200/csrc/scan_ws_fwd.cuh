@@ -18,7 +18,7 @@
 // (d = Re(k^c_127 <c_127, b_127>), Y_127 += d u_127).
 //
 // Roles (576 threads, one CTA per SM, chunks handed out round-robin):
-//   warp 16  producer: bulk tensor copies of the C, B, Z0 slabs (ring of two stages) and of U
+//   warp 16  producer: bulk tensor copies of the C, B, Z0 slabs (ring of three stages) and of U
 //   warp 17  issuer:   every tcgen05.mma, completion by tcgen05.commit on mbarriers
 //   warps 0-15 workers: JC transform of each slab, the score tile, the output rows
 // All waits are bounded and share one abort flag; a CTA that gave up fills its remaining output
@@ -33,11 +33,21 @@ struct alignas(64) WsFwdMaps {
   CUtensorMap C, B, Z, U, Y;
 };
 
+// clock64() stamps of CTA 0 while it works on its third chunk (builds with -DSLX_DIAG only)
+#ifdef SLX_DIAG
+#define WS_STAMP(cond, i) do { if ((cond) && blockIdx.x == 0) g_phase_clock[i] = clock64(); } while (0)
+#else
+#define WS_STAMP(cond, i) do { } while (0)
+#endif
+
 constexpr int kWsWorkers = 512;
 constexpr int kWsThreads = kWsWorkers + 64;
-constexpr int kWsStageBytes = 57344;  // C 16K | B 16K + Z0 8K | JC 16K
+constexpr int kWsStageBytes = 40960;  // one ring stage of bulk copies: C 16K | B 16K + Z0 8K
+constexpr int kWsStages = 3;
 constexpr int kWsFwdScal = 13312;     // per-chunk scalars and the staged rows (12,544 bytes used)
-constexpr size_t scan_ws_fwd_smem_bytes() { return 1024 + 2 * kWsStageBytes + 16384 + 32768 + kWsFwdScal; }
+constexpr size_t scan_ws_fwd_smem_bytes() {
+  return 1024 + kWsStages * kWsStageBytes + 2 * 16384 /* JC, two buffers */ + 16384 + 32768 + kWsFwdScal;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFwdArgs<T> a,
@@ -46,7 +56,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
   extern __shared__ unsigned char smem_raw[];
   unsigned char *base =
       reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char *tU = base + 2 * kWsStageBytes;  // [128][64] U (row 127 <- u_{-1})
+  unsigned char *tJ = base + kWsStages * kWsStageBytes;  // 2 x [128][64] JC (buffer = slab parity)
+  unsigned char *tU = tJ + 2 * 16384;                    // [128][64] U (row 127 <- u_{-1})
   unsigned char *tS = tU + 16384;                // 2 x [128][64] S'; block 0 doubles as the Y staging tile
   unsigned char *sc = tS + 32768;                // scalars (kWsFwdScal bytes)
   float *lp = reinterpret_cast<float *>(sc);                 // 128
@@ -61,7 +72,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
   T *bpst = reinterpret_cast<T *>(Kst + 2 * L);              // 2 x 256 staged b_{-1}
   T *upst = bpst + 2 * 256;                                  // 2 x 64 staged u_{-1}
   static_assert(512 + 4 * 1024 + 256 + 256 + 2048 + 4096 + 2 * 256 * 2 + 2 * 64 * 2 <= kWsFwdScal, "scalar area too small");
-  __shared__ uint64_t bars[12];  // full[2] jready[2] empty[2] accfull sready ydone ufull tmemfree wbar
+  __shared__ uint64_t bars[14];  // full[3] empty[3] jready[2] accfull sready ydone ufull tmemfree wbar
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag, slow_flag;
 
@@ -71,11 +82,11 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
   const int total = d.NC * d.BH;
   const uint32_t bar0 = umma::smem_u32(&bars[0]);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  enum { FULL = 0, JREADY = 2, EMPTY = 4, ACCFULL = 6, SREADY = 7, YDONE = 8, UFULL = 9, TMEMFREE = 10, WBAR = 11 };
+  enum { FULL = 0, EMPTY = 3, JREADY = 6, ACCFULL = 8, SREADY = 9, YDONE = 10, UFULL = 11, TMEMFREE = 12, WBAR = 13 };
   constexpr int fmt = umma::HalfFmt<T>::value;
 
   if (tid == 0) {
-    for (int i = 0; i < 12; ++i) {
+    for (int i = 0; i < 14; ++i) {
       const bool worker_bar = (i == JREADY || i == JREADY + 1 || i == SREADY || i == TMEMFREE || i == WBAR);
       umma::mbar_init(BAR(i), worker_bar ? 16u : 1u);
     }
@@ -94,7 +105,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
   umma::fence_after_sync();
   const uint32_t tmem = tmem_slot;
   volatile int *ab = &abort_flag;
-  auto WAIT = [&](int i, uint32_t parity) { return umma::mbar_wait_abortable(BAR(i), parity, ab); };
+  auto WAIT = [&](int i, uint32_t parity) { return umma::mbar_wait_abortable(BAR(i), parity, ab); };  // one thread
+  auto WAITW = [&](int i, uint32_t parity) { return umma::mbar_wait_warp(BAR(i), parity, ab); };        // a whole warp
 
   if (warp == 16) {
     // ------------------------------------------------------------------ producer
@@ -104,10 +116,11 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
       for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++it) {
         const int c = w % d.NC, bh = w / d.NC, t0 = c * L;
         for (int sl = 0; sl < NB && ok; ++sl, ++g) {
-          const int st = g & 1;
-          if (g >= 2) ok = WAIT(EMPTY + st, ((g >> 1) - 1) & 1);
+          const int st = g % kWsStages;
+          if (g >= kWsStages) ok = WAIT(EMPTY + st, ((g / kWsStages) - 1) & 1);
           if (!ok) break;
           unsigned char *sb = base + st * kWsStageBytes;
+          WS_STAMP(it == 2, 48 + sl);
           umma::mbar_expect_tx(BAR(FULL + st), 16384u + 16384u + 8192u);
           umma::tma_load_3d(umma::smem_u32(sb), &maps.C, sl * 64, t0, bh, BAR(FULL + st));
           umma::tma_load_3d(umma::smem_u32(sb + 16384), &maps.B, sl * 64, t0, bh, BAR(FULL + st));
@@ -131,14 +144,14 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
         if (it >= 1) ok = WAIT(TMEMFREE, (it - 1) & 1);  // the workers have read the previous chunk's accumulators
         umma::fence_after_sync();
         for (int sl = 0; sl < NB && ok; ++sl, ++g) {
-          const int st = g & 1;
-          const uint32_t par = (g >> 1) & 1;
-          ok = WAIT(FULL + st, par) && WAIT(JREADY + st, par);
+          const int st = g % kWsStages, jb = g & 1;
+          ok = WAIT(FULL + st, (g / kWsStages) & 1) && WAIT(JREADY + jb, (g >> 1) & 1);
           if (!ok) break;
           umma::fence_after_sync();
+          WS_STAMP(it == 2, 32 + sl);
           const uint32_t sb = umma::smem_u32(base + st * kWsStageBytes);
           const uint64_t dC = umma::desc_kmajor(sb, 0), dBZ = umma::desc_kmajor(sb + 16384, 0),
-                         dJ = umma::desc_kmajor(sb + 40960, 0);
+                         dJ = umma::desc_kmajor(umma::smem_u32(tJ + 16384 * jb), 0);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const uint64_t bz = umma::desc_advance(dBZ, umma::kStepK * kk);
@@ -149,9 +162,11 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
         }
         if (!ok) break;
         umma::commit(BAR(ACCFULL));
+        WS_STAMP(it == 2, 36);
         ok = WAIT(SREADY, it & 1) && WAIT(UFULL, it & 1);
         if (!ok) break;
         umma::fence_after_sync();
+        WS_STAMP(it == 2, 37);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma::mma_ss(tmem + 384, umma::desc_kmajor(sS + 16384u * (kk >> 2), kk & 3), umma::desc_mnmajor(sU, kk, 0),
@@ -199,23 +214,20 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
     };
     if ((int)blockIdx.x < total) prefetch_scalars(blockIdx.x, 0);
 
-    uint32_t g = 0, it = 0, wpar = 0;
+    uint32_t g = 0, it = 0;
     bool ok = true;
-    // Barrier among the 16 worker warps, built on an mbarrier so that it obeys the abort flag like
-    // every other wait (a plain bar.sync could not be left once some warps have given up).
-    auto WSYNC = [&]() {
-      __syncwarp();
-      if (lane == 0) umma::mbar_arrive(BAR(WBAR));
-      const bool r = WAIT(WBAR, wpar);
-      wpar ^= 1;
-      return r;
-    };
+    // Barrier among the 16 worker warps: the hardware barrier (an mbarrier-based one keeps 16 pollers on the
+    // shared-memory pipe and slowed the warp that computes the prefix several times over).  A hardware barrier
+    // cannot be abandoned, so a worker never leaves a chunk half way: once a wait has failed every later wait
+    // returns at once (abort flag), the warps run through the rest of the chunk together and stop at its end.
+    auto WSYNC = [&]() { asm volatile("bar.sync 1, 512;" ::: "memory"); };
     int w = blockIdx.x;
     for (; w < total && ok; w += gridDim.x, ++it) {
       const int c = w % d.NC, bh = w / d.NC, t0 = c * L;
       const int valid = min(L, d.T - t0);
       const int buf = it & 1;
       const bool more = w + (int)gridDim.x < total;
+      WS_STAMP(it == 2 && tid == 0, 0);
       if (more) prefetch_scalars(w + gridDim.x, buf ^ 1);
       if (more) asm volatile("cp.async.wait_group 1;" ::: "memory");
       else asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -223,7 +235,9 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
         umma::tma_store_wait_read();  // the previous chunk's Y store has read the staging tile
         slow_flag = 0;
       }
-      if (!(ok = WSYNC())) break;
+      WS_STAMP(it == 2 && tid == 0, 20);
+      WSYNC();
+      WS_STAMP(it == 2 && tid == 0, 21);
       // ---- per-token scalars ------------------------------------------------------------------
       const float2 *Mc = Mst + buf * L;
       const float4 *Kc = Kst + buf * L;
@@ -231,7 +245,9 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
         float2 mreg[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) mreg[i] = (4 * lane + i < valid) ? Mc[4 * lane + i] : make_float2(1.f, 0.f);
+        WS_STAMP(it == 2 && lane == 0, 60);
         chunk_prefix_fast128(mreg, lp, ph, mraw, &g_scan_bad);
+        WS_STAMP(it == 2 && lane == 0, 61);
       }
       if (t0 == 0 && tid >= 256 && tid < 256 + 40) {  // first chunk: the streaming inputs (fp32) stand in for token -1
         if (tid < 288) {
@@ -250,7 +266,9 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
           *reinterpret_cast<uint4 *>(upst + buf * 64 + 8 * q) = pack8<T>(tmp);
         }
       }
-      if (!(ok = WSYNC())) break;
+      WS_STAMP(it == 2 && tid == 0, 22);
+      WSYNC();
+      WS_STAMP(it == 2 && tid == 0, 23);
       if (tid < L) {
         const int t = tid;
         float2 gv;
@@ -266,21 +284,26 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
         gk2[t] = cscale(gv, decay_table_entry(lp, t, L));
         if (decay_step_out_of_range(lp, t)) slow_flag = 1;
       }
-      if (!(ok = WSYNC())) break;
+      WS_STAMP(it == 2 && tid == 0, 24);
+      WSYNC();
       const bool fast_decay = slow_flag == 0;
+      const bool stamp = (it == 2 && tid == 0);
+      WS_STAMP(stamp, 1);
 
       // ---- slabs: JC transform, boundary row ----------------------------------------------------
       float2 acc127 = make_float2(0.f, 0.f);
-      for (int sl = 0; sl < NB && ok; ++sl, ++g) {
-        const int st = g & 1;
-        ok = WAIT(FULL + st, (g >> 1) & 1);
-        if (!ok) break;
+      for (int sl = 0; sl < NB; ++sl, ++g) {
+        const int st = g % kWsStages, jb = g & 1;
+        ok = WAITW(FULL + st, (g / kWsStages) & 1) && ok;
+        // the JC buffer of this parity was last read by the products of the slab two back
+        if (g >= 2) ok = WAITW(EMPTY + (g - 2) % kWsStages, ((g - 2) / kWsStages) & 1) && ok;
+        WS_STAMP(stamp, 2 + 2 * sl);
         unsigned char *sb = base + st * kWsStageBytes;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           const uint32_t off = umma::swz_off(r0 + 64 * i, j);
           const uint4 cv = *reinterpret_cast<const uint4 *>(sb + off);
-          *reinterpret_cast<uint4 *>(sb + 40960 + off) = umma::jchunk(cv);
+          *reinterpret_cast<uint4 *>(tJ + 16384 * jb + off) = umma::jchunk(cv);
           if (i == 1 && r0 == 63) {  // row 127: keep <c_127, b_127> for the diagonal, hand the row to b_{-1}
             uint4 *brow = reinterpret_cast<uint4 *>(sb + 16384 + off);
             cdot_chunk<T>(cv, *brow, acc127);
@@ -289,9 +312,9 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
         }
         umma::fence_smem_to_async();
         __syncwarp();
-        if (lane == 0) umma::mbar_arrive(BAR(JREADY + st));
+        if (lane == 0) umma::mbar_arrive(BAR(JREADY + jb));
+        WS_STAMP(stamp, 3 + 2 * sl);
       }
-      if (!ok) break;
       if (warp == 15) {
         const float2 s = octet_sum(acc127);
         if (lane == 31) {
@@ -300,8 +323,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
         }
       }
       // ---- U tile: keep u_127, hand row 127 to u_{-1} --------------------------------------------
-      ok = WAIT(UFULL, it & 1);
-      if (!ok) break;
+      ok = WAITW(UFULL, it & 1) && ok;
       if (r0 == 63) {
         uint4 *urow = reinterpret_cast<uint4 *>(tU + umma::swz_off(L - 1, j));
         const uint4 uv = *urow;
@@ -315,9 +337,10 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
         *urow = *reinterpret_cast<const uint4 *>(upst + buf * 64 + 8 * j);
       }
       // ---- S -> S' ----------------------------------------------------------------------------------
-      ok = WAIT(ACCFULL, it & 1);
-      if (!ok) break;
+      WS_STAMP(stamp, 10);
+      ok = WAITW(ACCFULL, it & 1) && ok;
       umma::fence_after_sync();
+      WS_STAMP(stamp, 11);
       const float lpt = lp[row];
       const float2 pht = ph[row];
       {
@@ -365,10 +388,11 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
       umma::fence_before_sync();
       __syncwarp();
       if (lane == 0) umma::mbar_arrive(BAR(SREADY));
+      WS_STAMP(stamp, 12);
       // ---- Y = Yd + exp(lp_t) Re(phi_t H) (+ the diagonal of token 127) -> staging tile -> bulk store ---
-      ok = WAIT(YDONE, it & 1);
-      if (!ok) break;
+      ok = WAITW(YDONE, it & 1) && ok;
       umma::fence_after_sync();
+      WS_STAMP(stamp, 13);
       {
         uint32_t r_yd[16], r_re[16], r_im[16];
         umma::tmem_ld16_issue(umma::tmem_addr(tmem, 32 * q4, 384 + 16 * cb), r_yd);
@@ -394,11 +418,13 @@ __global__ void __launch_bounds__(kWsThreads, 1) chunk_scan_fwd_ws_kernel(ScanFw
       umma::fence_smem_to_async();
       __syncwarp();
       if (lane == 0) umma::mbar_arrive(BAR(TMEMFREE));
-      if (!(ok = WSYNC())) break;
-      if (tid == 0) {
+      WSYNC();
+      if (tid == 0 && ok) {
         umma::tma_store_3d(&maps.Y, 0, t0, bh, umma::smem_u32(tS));
         umma::tma_store_commit();
       }
+      WS_STAMP(stamp, 14);
+      if (!ok) break;  // (w stays at the failed chunk: it is poisoned below with the ones after it)
     }
     if (tid == 0) umma::tma_store_wait_all();
     if (!ok || abort_flag) {

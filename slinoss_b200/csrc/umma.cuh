@@ -130,32 +130,58 @@ __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-// Wait on an mbarrier phase inside a kernel whose warps play different roles.  Gives up after
-// `limit` clocks (about 0.2 s by default), and at once when another role has already given up:
-// *abort_flag (shared memory) is set by the first wait that runs out and read by all others, so
-// that a fault in one role ends the whole CTA within one timeout instead of one per wait.
+// Wait on an mbarrier phase inside a kernel whose warps play different roles.  What was measured on B200
+// (clock stamps per phase, same kernels, only the wait changed):
+//   * every thread of 16 warps parked in the blocking try_wait on one barrier: each synchronisation cost
+//     about 2.5 K cycles (the parked threads are released one after the other);
+//   * a spin on the non-blocking test_wait, or try_wait with a 100 ns suspend hint (which returns at once
+//     and so spins as well): the pollers take shared-memory atomics and issue slots from the warps that are
+//     still working; every phase ran two to five times slower;
+//   * ONE lane per warp parked in the blocking try_wait, the other lanes held at the warp's convergence
+//     barrier: what is used here.
+// Gives up after `limit` clocks (about 0.2 s by default), and at once when another role has already given
+// up: *abort_flag (shared memory) is set by the first wait that runs out and read by all others, so that a
+// fault in one role ends the whole CTA within one timeout instead of one per wait.
+__device__ __forceinline__ bool mbar_test(uint32_t mbar_saddr, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(mbar_saddr), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// one thread waits (producer / issuer lanes)
 __device__ __forceinline__ bool mbar_wait_abortable(uint32_t mbar_saddr, uint32_t parity, volatile int *abort_flag,
                                                     long long limit = 400000000LL) {
   long long t0 = 0;
+  if (*abort_flag) return false;
   for (int spin = 0;; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t"
-        "}\n"
-        : "=r"(done)
-        : "r"(mbar_saddr), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if (*abort_flag) return false;
-    if (spin == 0) t0 = clock64();
-    else if ((spin & 15) == 0 && clock64() - t0 > limit) {
-      *abort_flag = 1;
-      return false;
+    if (mbar_test(mbar_saddr, parity)) return true;
+    __nanosleep(40);  // keep the poll off the shared-memory pipe that the working warps need
+    if ((spin & 15) == 15) {
+      if (*abort_flag) return false;
+      if (t0 == 0) t0 = clock64();
+      else if (clock64() - t0 > limit) {
+        *abort_flag = 1;
+        return false;
+      }
     }
   }
+}
+// a whole (converged) warp waits: lane 0 polls, the result is broadcast, and every lane then observes the
+// completed phase itself with one test (which is what makes the data written by the asynchronous proxy
+// visible to it)
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t mbar_saddr, uint32_t parity, volatile int *abort_flag) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait_abortable(mbar_saddr, parity, abort_flag) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (ok) (void)mbar_test(mbar_saddr, parity);
+  return ok != 0;
 }
 
 // i * v on a packed pair (re, im) of halfs: (re, im) -> (-im, re).  One byte permute and one xor;

@@ -110,4 +110,51 @@ def cconv1d_b200(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
     return _CConv1dFn.apply(x, weight, bias, conv_state, activation in ("silu", "swish"))
 
 
-__all__ = ["cconv1d_b200"]
+@torch.no_grad()
+def cconv1d_update_b200(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                        conv_state: Optional[torch.Tensor] = None, *, activation: Optional[str] = None,
+                        inplace: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One decode token of the depthwise causal conv: the contract of the reference's
+    ``causal_conv1d_update`` as ``SLinOSSMixer._apply_causal_depthwise_conv_step`` uses it
+    (slinoss/layers/mixer.py:614-676).  ``x (b, C)`` -- possibly a column slice of the input
+    projection's one-token output -- and the rolling ``conv_state (b, C, W-1)`` give
+    ``(y (b, C), next_state (b, C, W-1))`` with ``y = act(bias + w . [state, x])`` and
+    ``next_state = [state[..., 1:], x]``.  ``inplace=True`` rolls ``conv_state`` in place and returns
+    it (it must then be contiguous and of ``x``'s dtype).  Inference only (no autograd)."""
+    if activation not in (None, "silu", "swish"):
+        raise NotImplementedError("activation must be None, silu, or swish")
+    if x.device.type != "cuda":
+        raise ValueError("slinoss_b200 cconv1d requires CUDA tensors.")
+    if x.ndim != 2:
+        raise ValueError(f"x must be (batch, channels). Got {tuple(x.shape)}.")
+    b, C = map(int, x.shape)
+    if weight.ndim != 2 or int(weight.shape[0]) != C:
+        raise ValueError(f"weight must be ({C}, width). Got {tuple(weight.shape)}.")
+    W = int(weight.shape[1])
+    if W not in (2, 3, 4):
+        raise ValueError(f"conv width must be 2, 3 or 4. Got {W}.")
+    if conv_state is not None and tuple(conv_state.shape) != (b, C, W - 1):
+        raise ValueError(f"conv_state must be {(b, C, W - 1)}. Got {tuple(conv_state.shape)}.")
+    dev = _lib.same_device(x, weight, bias, conv_state)
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    w = weight.to(x.dtype).contiguous()
+    bs = None if bias is None else bias.to(x.dtype).contiguous()
+    if inplace:
+        if conv_state is None or conv_state.dtype != x.dtype or not conv_state.is_contiguous():
+            raise ValueError("inplace=True needs a contiguous conv_state of x's dtype.")
+        st, nxt = conv_state, conv_state
+    else:
+        st = None if conv_state is None else conv_state.to(x.dtype).contiguous()
+        nxt = torch.empty((b, C, W - 1), device=dev, dtype=x.dtype)
+    y = torch.empty((b, C), device=dev, dtype=x.dtype)
+    s = _lib.ConvShape(b, 1, C, W, _lib.dtype_code(x.dtype), 1 if activation in ("silu", "swish") else 0,
+                       C, int(x.stride(0)))
+    with _lib.guard(dev):
+        _lib.check(_lib.lib().slx_cconv1d_update(byref(s), x.data_ptr(), w.data_ptr(), _lib.ptr(bs), _lib.ptr(st),
+                                                 y.data_ptr(), nxt.data_ptr(), _lib.stream_ptr(dev)),
+                   "cconv1d update")
+    return y, nxt
+
+
+__all__ = ["cconv1d_b200", "cconv1d_update_b200"]

@@ -178,7 +178,6 @@ def state_passing_b200(inc, m_chunk, *, initial_states=None, want_starts: bool =
     ``chunk_starts`` is stored as ``starts_dtype`` (fp32 like the reference by default; the fused
     op uses the activation dtype where the tensor-core kernels run).  ``want_starts=False``
     returns ``(None, final_state)`` and writes nothing but the final state (half the traffic)."""
-    _require_cuda(inc, m_chunk, initial_states)
     if inc.ndim != 5:
         raise ValueError(f"inc must be (batch,heads,chunks,P,2N). Got {tuple(inc.shape)}.")
     b, h, NC, P, D = map(int, inc.shape)
@@ -191,6 +190,7 @@ def state_passing_b200(inc, m_chunk, *, initial_states=None, want_starts: bool =
                          f"Got {tuple(initial_states.shape)}.")
     if starts_dtype not in _ACT_DTYPES:
         raise TypeError(f"starts_dtype must be float32, bfloat16 or float16. Got {starts_dtype}.")
+    _require_cuda(inc, m_chunk, initial_states)
     dev = _lib.same_device(inc, m_chunk, initial_states)
     inc, m_chunk = _f32(inc), _f32(m_chunk)
     init = _f32(initial_states)

@@ -110,3 +110,105 @@ def test_decode_step_host_checks():
                            device=torch.device("cuda", 0), dtype=torch.bfloat16)
     assert not be.supports(types.SimpleNamespace(d_state=4, output_norm=object()), batch_size=1,
                            device=torch.device("cuda", 0), dtype=torch.bfloat16)
+
+
+def test_device_guard_enters_the_tensors_device(monkeypatch):
+    """Every library call runs under ``_lib.guard(device)``: with another device current the guard
+    switches to the tensors' device for the duration of the call and back afterwards."""
+    from slinoss_b200 import _lib
+
+    events = []
+
+    class FakeCtx:
+        def __init__(self, idx):
+            self.idx = idx
+
+        def __enter__(self):
+            events.append(("enter", self.idx))
+
+        def __exit__(self, *exc):
+            events.append(("exit", self.idx))
+            return False
+
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    monkeypatch.setattr(torch.cuda, "device", FakeCtx)
+    with _lib.guard(torch.device("cuda", 1)):
+        events.append("call")
+    assert events == [("enter", 1), "call", ("exit", 1)]
+    events.clear()
+    with _lib.guard(torch.device("cuda", 0)):   # already current: nothing to switch
+        events.append("call")
+    assert events == ["call"]
+    with pytest.raises(ValueError, match="CUDA"):
+        with _lib.guard(torch.device("cpu")):
+            pass
+
+
+def test_ops_wrap_their_library_calls_in_the_guard():
+    """Source-level check that no op reaches the library outside a guard: every ``_lib.check(`` of
+    the op modules sits inside a ``with _lib.guard(`` block."""
+    import inspect
+
+    from slinoss_b200 import context_parallel
+    from slinoss_b200.ops import cconv1d, decode, scanprep, v2x2ssd
+
+    for mod in (cconv1d, decode, scanprep, v2x2ssd, context_parallel):
+        lines = inspect.getsource(mod).splitlines()
+        for i, line in enumerate(lines):
+            if "_lib.check(" in line and "def " not in line:
+                indent = len(line) - len(line.lstrip())
+                j = i - 1
+                while j >= 0 and (not lines[j].strip() or len(lines[j]) - len(lines[j].lstrip()) >= indent):
+                    j -= 1
+                assert "with _lib.guard(" in lines[j], f"{mod.__name__}:{i + 1} is outside a device guard"
+
+
+def test_same_device_rejects_mixed_devices():
+    from slinoss_b200 import _lib
+
+    class T:
+        def __init__(self, dev):
+            self.device = torch.device(dev)
+
+    assert _lib.same_device(T("cuda:1"), None, T("cuda:1")) == torch.device("cuda:1")
+    with pytest.raises(ValueError, match="same device"):
+        _lib.same_device(T("cuda:0"), T("cuda:1"))
+
+
+def test_stage_entry_points_validate_like_the_fused_op():
+    """The stage functions hand raw pointers to the kernels, so they run the fused op's checks first
+    (contiguity, shapes, dtypes); a time slice of a longer tensor must be made contiguous."""
+    U, M, K, B, C = _inputs(T=16)
+    sl = slice(4, 12)
+    with pytest.raises(ValueError, match="must be contiguous"):
+        slinoss_b200.chunk_increment_b200(U[:, :, sl], M[:, :, sl], K[:, :, sl], B[:, :, sl], chunk_size=16)
+    with pytest.raises(ValueError, match=r"M must be \(batch,heads,T,2\)"):
+        slinoss_b200.chunk_increment_b200(U, M[..., :1].contiguous(), K, B, chunk_size=16)
+    with pytest.raises(ValueError, match="requires CUDA"):
+        slinoss_b200.chunk_increment_b200(U, M, K, B, chunk_size=16)
+    with pytest.raises(ValueError, match="C must match B"):
+        slinoss_b200.chunk_scan_b200(U, M, K, B, C[..., :4].contiguous(), torch.zeros(1, 2, 1, 4, 6), chunk_size=16)
+    inc = torch.zeros(1, 2, 3, 4, 6)
+    with pytest.raises(ValueError, match="requires CUDA"):
+        slinoss_b200.state_passing_b200(inc, torch.zeros(1, 2, 3, 2))
+    with pytest.raises(ValueError, match=r"inc must be \(batch,heads,chunks,P,2N\)"):
+        slinoss_b200.state_passing_b200(inc[0], torch.zeros(2, 3, 2))
+
+
+def test_context_parallel_rejects_non_contiguous_slices():
+    import torch.distributed as dist
+
+    from slinoss_b200.context_parallel import v2x2ssd_context_parallel
+
+    U, M, K, B, C = _inputs(T=16)
+    import os
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29547")
+    dist.init_process_group("gloo", rank=0, world_size=1)
+    try:
+        with pytest.raises(ValueError, match="must be contiguous"):
+            v2x2ssd_context_parallel(U[:, :, 4:12], M[:, :, 4:12], K[:, :, 4:12], B[:, :, 4:12], C[:, :, 4:12],
+                                     chunk_size=8)
+    finally:
+        dist.destroy_process_group()

@@ -163,3 +163,120 @@ def test_nextchar_lm_step_matches_reference_backends():
     assert num_o / den <= max(2e-2, 1.5 * num_r / den)
     for n in g_o:
         assert torch.isfinite(g_o[n]).all(), n
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
+def test_mixer_step_matches_full_forward(dtype, tol):
+    """Token-by-token ``mixer.step`` (conv step through ``slx_cconv1d_update``, scan step through
+    ``B200MixerDecodeBackend``) against one ``forward`` over the same tokens with the same backends
+    (pattern of the reference's tests/test_mixer.py:543-576)."""
+    _, ours = _make_mixers(dtype, d_model=128, d_state=64, expand=2, chunk=32, seed=9)
+    ours.eval()
+    g = torch.Generator(device="cuda").manual_seed(10)
+    x = torch.randn((3, 11, 128), device="cuda", generator=g).to(dtype)
+    with torch.no_grad():
+        y_full, st_full = ours(x, return_state=True)
+        st = ours.init_state(x.shape[0], device=x.device, dtype=x.dtype)
+        pieces = []
+        for t in range(x.shape[1]):
+            y_t, st = ours.step(x[:, t, :], st)
+            pieces.append(y_t.unsqueeze(1))
+    y_step = torch.cat(pieces, dim=1)
+    errs = dict(y=_rel(y_step, y_full), conv=_rel(st.conv, st_full.conv),
+                state=_rel(st.scan.state, st_full.scan.state), b_prev=_rel(st.scan.b_prev, st_full.scan.b_prev),
+                u_prev=_rel(st.scan.u_prev, st_full.scan.u_prev))
+    print("[mixer step]", dtype, {k: f"{v:.2e}" for k, v in errs.items()})
+    assert max(errs.values()) <= tol, errs
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [2, 3, 4])
+def test_conv_update_matches_reference_conv_step(dtype, width):
+    """``cconv1d_update_b200`` against the reference's own conv step arithmetic
+    (``_apply_cconv_reference`` on a one-token sequence + SiLU, mixer.py:660-676), three tokens in
+    a row with the rolling state, out of place and in place."""
+    import_reference()
+    from slinoss.layers import SLinOSSMixer
+    from slinoss.layers.backend import ReferenceCConv1dBackend
+
+    import slinoss_b200 as sb
+
+    torch.manual_seed(width)
+    mixer = SLinOSSMixer(96, d_state=16, expand=2, d_head=64, d_conv=width, device="cuda", dtype=dtype,
+                         cconv_backend=ReferenceCConv1dBackend())
+    b, C = 5, mixer.d_inner
+    st_ref = torch.randn((b, C, width - 1), device="cuda").to(dtype)
+    st_out, st_in = st_ref.clone(), st_ref.clone().contiguous()
+    wide = torch.randn((3, b, 2 * C + 7), device="cuda").to(dtype)   # x is a column slice of a wider row
+    for t in range(3):
+        x = wide[t, :, 3:3 + C]
+        with torch.no_grad():
+            y_seq, st_ref = mixer._apply_cconv_reference(x.unsqueeze(1), st_ref)
+            y_ref = torch.nn.functional.silu(y_seq[:, 0, :])
+        y1, st_out = sb.cconv1d_update_b200(x, mixer.dw_weight, mixer.dw_bias, st_out, activation="silu")
+        y2, st_in2 = sb.cconv1d_update_b200(x, mixer.dw_weight, mixer.dw_bias, st_in, activation="silu", inplace=True)
+        assert st_in2 is st_in
+        tol = 1e-6 if dtype == torch.float32 else 1e-2
+        assert _rel(y1, y_ref) <= tol and _rel(y2, y_ref) <= tol
+        assert torch.equal(st_out, st_ref) and torch.equal(st_in, st_ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gate_skip_matches_reference_glue(dtype):
+    """``gate_skip_b200`` (skip, re-layout, SiLU gate in one pass; gate read as a column slice of a wider
+    projection row) against ``SLinOSSMixer._apply_gate_skip`` (mixer.py:585-599), forward and all four
+    gradients."""
+    import_reference()
+    from slinoss.layers import SLinOSSMixer
+
+    import slinoss_b200 as sb
+
+    torch.manual_seed(11)
+    mixer = SLinOSSMixer(192, d_state=16, expand=2, d_head=64, device="cuda", dtype=dtype)
+    with torch.no_grad():
+        mixer.skip.copy_(torch.randn_like(mixer.skip))
+    b, T, H, P = 2, 75, mixer.n_heads, mixer.d_head
+    g = torch.Generator(device="cuda").manual_seed(12)
+    wide = torch.randn((b, T, 2 * H * P + 8), device="cuda", generator=g).to(dtype)
+    leaves_r = [torch.randn((b, H, T, P), device="cuda", generator=g).to(dtype).requires_grad_(True) for _ in range(2)]
+    gate_r = wide[..., 8:8 + H * P].detach().clone().requires_grad_(True)
+    w = torch.randn((b, T, H * P), device="cuda", generator=g).to(dtype)
+    out_r = mixer._apply_gate_skip(leaves_r[0], leaves_r[1], gate_r, b, T)
+    gr = torch.autograd.grad(out_r, leaves_r + [gate_r, mixer.skip], w)
+    leaves_o = [t.detach().clone().requires_grad_(True) for t in leaves_r]
+    wide_o = wide.detach().clone().requires_grad_(True)
+    skip_o = mixer.skip.detach().clone().requires_grad_(True)
+    out_o = sb.gate_skip_b200(leaves_o[0], leaves_o[1], wide_o[..., 8:8 + H * P], skip_o)
+    go = torch.autograd.grad(out_o, leaves_o + [wide_o, skip_o], w)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    errs = dict(out=_rel(out_o, out_r), dy=_rel(go[0], gr[0]), du=_rel(go[1], gr[1]),
+                dgate=_rel(go[2][..., 8:8 + H * P], gr[2]), dskip=_rel(go[3], gr[3]))
+    print("[gate_skip]", dtype, {k: f"{v:.2e}" for k, v in errs.items()})
+    assert max(errs.values()) <= tol, errs
+    assert float(go[2][..., :8].abs().max()) == 0.0   # nothing leaks outside the gate's columns
+
+
+def test_mixer_fused_glue_matches_unfused():
+    """``use_b200_backends(..., fuse_glue=True)``: SiLU inside the conv kernel and the one-pass gate/skip
+    give the same layer output and gradients as the reference's own forward on the B200 backends."""
+    import slinoss_b200 as sb
+
+    _, plain = _make_mixers(torch.bfloat16, d_model=256, d_state=64, expand=1, chunk=64, seed=13)
+    fused = copy.deepcopy(plain)
+    assert sb.use_b200_backends(fused, fuse_glue=True) == 1
+    g = torch.Generator(device="cuda").manual_seed(14)
+    x = torch.randn((2, 300, 256), device="cuda", generator=g).to(torch.bfloat16)
+    w = torch.randn((2, 300, 256), device="cuda", generator=g)
+    y_p, g_p = _run_layer(plain, x, w)
+    y_f, g_f = _run_layer(fused, x, w)
+    errs = {"y": _rel(y_f, y_p)}
+    errs.update({n: _rel(g_f[n], g_p[n]) for n in g_p})
+    print("[fused glue]", {k: f"{v:.2e}" for k, v in errs.items()})
+    assert max(errs.values()) <= 1e-2, errs
+    # streaming state is carried the same way
+    with torch.no_grad():
+        y_a, st = fused(x[:, :100], return_state=True)
+        y_b, st = fused(x[:, 100:], state=st, return_state=True)
+        y_full, st_full = plain(x, return_state=True)
+    assert _rel(torch.cat([y_a, y_b], dim=1), y_full) <= 1e-2
+    assert _rel(st.scan.state, st_full.scan.state) <= 1e-2 and torch.equal(st.conv, st_full.conv)

@@ -50,8 +50,19 @@ def test_prep_golden_fp32():
     outs, grads = _run_prep(_cu(g["value"]), _cu(g["params"]), _cu(g["bc"]), pars, hp, H, N, P, gouts)
     assert torch.equal(outs[0].cpu(), torch.from_numpy(g["U"]))
     assert rel_err(_np(outs[1]), g["M"]) < 2e-6
-    # FOH taps: (rho-1)/z cancels in fp32 (in the reference too); see tests/test_oracle_pins.py
-    assert rel_err(_np(outs[2]), g["K"]) < 1e-4
+    # FOH taps: the reference evaluates (rho-1)/z and (rho(z-1)+1)/z^2 in fp32, where they cancel; the kernel uses
+    # series there.  Three-way comparison with the float64 oracle on the fixture's inputs says which side is off:
+    cfg_o = oprep.PrepConfig(n_heads=H, d_state=N, d_head=P, **hp)
+    bias_o = oprep.flat_bias(*(g[n] for n in BIAS_NAMES))
+    b_, T_ = g["value"].shape[:2]
+    _, K_oracle = oprep.coefficients_fwd(g["params"].astype(np.float64).reshape(b_, T_, H, 13), bias_o, cfg_o)
+    e_kernel_oracle = rel_err(_np(outs[2]), K_oracle)
+    e_fixture_oracle = rel_err(g["K"], K_oracle)
+    e_kernel_fixture = rel_err(_np(outs[2]), g["K"])
+    print(f"[prep K] kernel vs float64 oracle {e_kernel_oracle:.2e}; reference fp32 fixture vs oracle "
+          f"{e_fixture_oracle:.2e}; kernel vs fixture {e_kernel_fixture:.2e}")
+    assert e_kernel_oracle < 1e-5
+    assert e_kernel_fixture < 1e-5 + 1.5 * e_fixture_oracle   # the kernel is no further from the fixture than the fixture's own error
     assert rel_err(_np(outs[3]), g["B"]) < 2e-6 and rel_err(_np(outs[4]), g["C"]) < 2e-6
     assert rel_err(_np(grads[0]), g["d_value"]) < 1e-7
     assert rel_err(_np(grads[1]), g["d_params"]) < 2e-4
@@ -101,7 +112,7 @@ def test_prep_seeded_vs_oracle(dtype, N, P, H, b, T):
     tol_bc = 4e-3 if half else 2e-6
     assert torch.equal(outs[0], v0.view(b, T, H, P).permute(0, 2, 1, 3))
     assert rel_err(_np(outs[1]), Mo) < 2e-6
-    assert rel_err(_np(outs[2]), Ko) < 2e-4
+    assert rel_err(_np(outs[2]), Ko) < 1e-5     # series evaluation of the tap factors: no fp32 cancellation
     assert rel_err(_np(outs[3]), Bo) < tol_bc and rel_err(_np(outs[4]), Co) < tol_bc
     dp, dbias = oprep.coefficients_bwd(p4, bias, cfg, _np(gouts[1]), _np(gouts[2]))
     dbc, dscale = oprep.pack_bc_bwd(_np(c0), scale, cfg, _np(gouts[3]), _np(gouts[4]))
