@@ -334,8 +334,9 @@ def scan_stage_timings(inp, b, h, T, P, N, L, dtype, reps=10, warm=3, only=None)
     lib, st = _lib.lib(), _lib.stream_ptr(dev)
     s = _lib.scan_shape(BH, T, P, N, L, dtype)
     f32 = dict(device=dev, dtype=torch.float32)
-    inc = torch.empty((b, h, NC, P, D), **f32)
-    starts = torch.empty(inc.shape, device=dev, dtype=_lib.starts_dtype(s))
+    # increments / dZ0 are stored like the chunk starts, as the whole-op entry points store them
+    starts = torch.empty((b, h, NC, P, D), device=dev, dtype=_lib.starts_dtype(s))
+    inc = torch.empty_like(starts)
     sdt = _lib.dtype_code(starts.dtype)
     mch = torch.empty((b, h, NC, 2), **f32)
     final = torch.empty((b, h, P, D), **f32)
@@ -349,15 +350,15 @@ def scan_stage_timings(inp, b, h, T, P, N, L, dtype, reps=10, warm=3, only=None)
     cB, cU = torch.empty((b, h, NC, D), **f32), torch.empty((b, h, NC, P), **f32)
     ck = _lib.check
     ht = BH * T
-    state_bytes = BH * NC * P * D * 4
+    state_bytes = inc.numel() * inc.element_size()
     starts_bytes = starts.numel() * starts.element_size()
 
     def inc_fn():
         ck(lib.slx_chunk_increment_fwd(byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), None, None,
-                                       inc.data_ptr(), mch.data_ptr(), st), "inc")
+                                       inc.data_ptr(), sdt, mch.data_ptr(), st), "inc")
 
     def sp_fn():
-        ck(lib.slx_state_passing_fwd(BH, NC, P, N, inc.data_ptr(), mch.data_ptr(), None, starts.data_ptr(), sdt,
+        ck(lib.slx_state_passing_fwd(BH, NC, P, N, inc.data_ptr(), sdt, mch.data_ptr(), None, starts.data_ptr(), sdt,
                                      final.data_ptr(), st), "sp")
 
     def scan_fn():
@@ -365,10 +366,11 @@ def scan_stage_timings(inp, b, h, T, P, N, L, dtype, reps=10, warm=3, only=None)
                                   starts.data_ptr(), None, None, Y.data_ptr(), st), "scan")
 
     def dz0_fn():
-        ck(lib.slx_chunk_scan_bwd_dz0(byref(s), M.data_ptr(), C.data_ptr(), dY.data_ptr(), dz0.data_ptr(), st), "dz0")
+        ck(lib.slx_chunk_scan_bwd_dz0(byref(s), M.data_ptr(), C.data_ptr(), dY.data_ptr(), dz0.data_ptr(), sdt, st),
+           "dz0")
 
     def spb_fn():
-        ck(lib.slx_state_passing_bwd(BH, NC, P, N, dz0.data_ptr(), mch.data_ptr(), starts.data_ptr(), sdt,
+        ck(lib.slx_state_passing_bwd(BH, NC, P, N, dz0.data_ptr(), sdt, mch.data_ptr(), starts.data_ptr(), sdt,
                                      final.data_ptr(), None, d_inc.data_ptr(), None, zdot.data_ptr(),
                                      part.data_ptr(), st), "spb")
 

@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define SLX_ABI_VERSION 4
+#define SLX_ABI_VERSION 5
 
 typedef enum { SLX_F32 = 0, SLX_BF16 = 1, SLX_F16 = 2 } slx_dtype;
 
@@ -78,20 +78,27 @@ const char *slx_last_error_string(void);
 /* ---- forward stages --------------------------------------------------- */
 
 /* Replaces reference.py:937 chunk_increment (CuTe: kernels/fwd/__init__.py:740
- * chunk_increment_cute).  inc (BH,NC,P,2N) fp32, m_chunk (BH,NC,2) fp32. */
+ * chunk_increment_cute).  inc (BH,NC,P,2N) stored as inc_dtype: SLX_F32 (what the
+ * reference returns), or the activation dtype where the tensor-core kernels run
+ * (the whole-op entry points below use that: the increments only feed the fp32
+ * state pass, whose output is rounded to that dtype for the chunk kernels, and
+ * half storage halves the traffic of two HBM-bound kernels).
+ * m_chunk (BH,NC,2) fp32. */
 int slx_chunk_increment_fwd(const slx_scan_shape *s, const void *U,
                             const float *M, const float *K, const void *B,
                             const float *B_prev /*[opt] (BH,2N)*/,
-                            const float *U_prev /*[opt] (BH,P)*/, float *inc,
-                            float *m_chunk, void *stream);
+                            const float *U_prev /*[opt] (BH,P)*/, void *inc,
+                            int32_t inc_dtype, float *m_chunk, void *stream);
 
 /* Replaces reference.py:1015 state_passing (CuTe: kernels/fwd/__init__.py:897).
  * chunk_starts holds starts_dtype values (slx_dtype); with SLX_F32 it may alias
  * inc (the pass is then in place).  chunk_starts == NULL
  * asks for final_state only (nothing else is written): the affine offset of a
- * segment when segments are chained across devices. */
+ * segment when segments are chained across devices.
+ * inc is read as inc_dtype (SLX_F32 or starts_dtype); the recurrence is fp32. */
 int slx_state_passing_fwd(int32_t batch_heads, int32_t n_chunks, int32_t P,
-                          int32_t N, const float *inc, const float *m_chunk,
+                          int32_t N, const void *inc, int32_t inc_dtype,
+                          const float *m_chunk,
                           const float *initial_states /*[opt]*/,
                           void *chunk_starts /*[opt]*/, int32_t starts_dtype,
                           float *final_state, void *stream);
@@ -105,8 +112,8 @@ int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M,
 
 /* Replaces reference.py:1195 v2x2ssd / cute/kernels/fwd/__init__.py:1691
  * v2x2ssd_fwd_cute: the three stages back to back on one stream.
- * increments: fp32 scratch of (BH, NC, P, 2N) floats for the chunk increments.
- * NULL makes chunk_starts double as the increment buffer (only where
+ * increments: scratch of (BH, NC, P, 2N) values of starts_dtype for the chunk
+ * increments.  NULL makes chunk_starts double as the increment buffer (only where
  * slx_scan_starts_dtype(s) is fp32): no extra memory, but the state pass then
  * overwrites each line it has just read, which runs at well under half the
  * speed of the two-buffer pass on B200. */
@@ -116,7 +123,7 @@ int slx_v2x2ssd_fwd(const slx_scan_shape *s, const void *U, const float *M,
                     const float *B_prev /*[opt]*/, const float *U_prev /*[opt]*/,
                     void *Y, float *final_state,
                     void *chunk_starts /* slx_scan_starts_dtype(s) */,
-                    float *m_chunk, float *increments /*[opt]*/, void *stream);
+                    float *m_chunk, void *increments /*[opt]*/, void *stream);
 
 /* ---- backward ----------------------------------------------------------- */
 
@@ -125,20 +132,24 @@ size_t slx_v2x2ssd_bwd_workspace_bytes(const slx_scan_shape *s);
 
 /* dZ0[c] = sum_t conj(prefix_t) dY_t (x) c_t : gradient of the loss with respect
  * to each chunk's start state through that chunk's outputs only.  Replaces
- * cute/kernels/bwd/chunk_scan/dz0.py:521.  dZ0 (BH,NC,P,2N) fp32. */
+ * cute/kernels/bwd/chunk_scan/dz0.py:521.  dZ0 (BH,NC,P,2N) stored as dz0_dtype:
+ * SLX_F32, or the activation dtype on the tensor-core path (as for the increments). */
 int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *C,
-                           const void *dY, float *dZ0, void *stream);
+                           const void *dY, void *dZ0, int32_t dz0_dtype,
+                           void *stream);
 
 /* Reverse recurrence over chunks (cute/kernels/bwd/state_passing/state.py:119
  * and m.py:83 fused): on return d_inc[c] = dL/d(end state of chunk c), stored as
  * starts_dtype (with SLX_F32 it may alias dZ0), d_initial = dL/d(initial state),
  * and zdot (BH,NC,2) holds sum_{p,n} conj(end_state_c) * d_inc[c] (from the fp32
  * values), the chunk-level term of dM.  final_state is the forward's fp32 final
- * state; chunk_starts is read as starts_dtype.
+ * state; chunk_starts is read as starts_dtype, dZ0 as dz0_dtype (SLX_F32 or
+ * starts_dtype).
  * zdot and zdot_partials NULL: no dot products (chunk_starts and final_state are
  * then not read).  d_inc NULL as well: only d_initial is written. */
 int slx_state_passing_bwd(int32_t batch_heads, int32_t n_chunks, int32_t P,
-                          int32_t N, const float *dZ0, const float *m_chunk,
+                          int32_t N, const void *dZ0, int32_t dz0_dtype,
+                          const float *m_chunk,
                           const void *chunk_starts /*[opt]*/, int32_t starts_dtype,
                           const float *final_state /*[opt]*/,
                           const float *d_final /*[opt]*/, void *d_inc /*[opt]*/,

@@ -58,13 +58,13 @@ SIGNATURES = {
     "slx_abi_version": (c_int32, []),
     "slx_scan_starts_dtype": (c_int32, [POINTER(ScanShape)]),
     "slx_last_error_string": (c_char_p, []),
-    "slx_chunk_increment_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 9),
-    "slx_state_passing_fwd": (c_int32, [c_int32] * 4 + [_P] * 4 + [c_int32] + [_P] * 2),
+    "slx_chunk_increment_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 7 + [c_int32] + [_P] * 2),
+    "slx_state_passing_fwd": (c_int32, [c_int32] * 4 + [_P, c_int32] + [_P] * 3 + [c_int32] + [_P] * 2),
     "slx_chunk_scan_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 10),
     "slx_v2x2ssd_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 14),
     "slx_v2x2ssd_bwd_workspace_bytes": (c_size_t, [POINTER(ScanShape)]),
-    "slx_chunk_scan_bwd_dz0": (c_int32, [POINTER(ScanShape)] + [_P] * 5),
-    "slx_state_passing_bwd": (c_int32, [c_int32] * 4 + [_P] * 3 + [c_int32] + [_P] * 7),
+    "slx_chunk_scan_bwd_dz0": (c_int32, [POINTER(ScanShape)] + [_P] * 4 + [c_int32, _P]),
+    "slx_state_passing_bwd": (c_int32, [c_int32] * 4 + [_P, c_int32] + [_P] * 2 + [c_int32] + [_P] * 7),
     "slx_chunk_scan_bwd": (c_int32, [POINTER(ScanShape)] + [_P] * 19),
     "slx_v2x2ssd_bwd": (c_int32, [POINTER(ScanShape)] + [_P] * 21 + [c_size_t, _P]),
     "slx_v2x2ssd_bwd_begin": (c_int32, [POINTER(ScanShape)] + [_P] * 6 + [c_size_t, _P]),

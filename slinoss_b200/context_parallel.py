@@ -43,9 +43,13 @@ class B200Engine:
     """Local arithmetic on the sm_100a kernels (through the C ABI)."""
 
     def forward_parts(self, U, M, K, B, Bp, Up, L):
-        from .ops.v2x2ssd import chunk_increment_b200, state_passing_b200
+        from . import _lib
+        from .ops.v2x2ssd import _shape, chunk_increment_b200, state_passing_b200
 
-        inc, mch = chunk_increment_b200(U, M, K, B, B_prev=Bp, U_prev=Up, chunk_size=L)
+        b, h, T, P = map(int, U.shape)
+        # increments stored like the chunk starts (the activation dtype on the tensor-core path)
+        sdt = _lib.starts_dtype(_shape(b, h, T, P, int(B.shape[-1]) // 2, L, U.dtype))
+        inc, mch = chunk_increment_b200(U, M, K, B, B_prev=Bp, U_prev=Up, chunk_size=L, inc_dtype=sdt)
         _, f0 = state_passing_b200(inc, mch, initial_states=None, want_starts=False)
         return inc, mch, f0
 

@@ -212,16 +212,24 @@ static int launch_scan_fwd_ws(const ScanDims &d, const void *U, const float *M, 
   return check_launch("chunk_scan_fwd_ws");
 }
 
-template <typename T, int MODE>
-static int launch_outer_tc(const ScanDims &d, const void *A, const void *X, const float *M, const float *K,
-                           const float *Bprev, const float *Uprev, float *out, float *m_chunk, cudaStream_t st) {
-  OuterArgs<T> a{(const T *)A, (const T *)X, M, K, Bprev, Uprev, out, m_chunk, d};
-  auto kern = chunk_outer_tc_kernel<T, MODE>;
+template <typename T, int MODE, typename OT>
+static int launch_outer_tc_t(const ScanDims &d, const void *A, const void *X, const float *M, const float *K,
+                             const float *Bprev, const float *Uprev, void *out, float *m_chunk, cudaStream_t st) {
+  OuterArgs<T> a{(const T *)A, (const T *)X, M, K, Bprev, Uprev, (float *)out, m_chunk, d};
+  auto kern = chunk_outer_tc_kernel<T, MODE, OT>;
   size_t smem = outer_tc_smem_bytes();
   int rc = set_smem(kern, smem);
   if (rc) return rc;
   kern<<<dim3(d.NC, d.BH), kTcThreads, smem, st>>>(a);
   return check_launch(MODE == 0 ? "chunk_increment_fwd_tc" : "chunk_scan_bwd_dz0_tc");
+}
+// `out` holds fp32 values, or (half_out) values of the activation dtype T
+template <typename T, int MODE>
+static int launch_outer_tc(const ScanDims &d, const void *A, const void *X, const float *M, const float *K,
+                           const float *Bprev, const float *Uprev, void *out, bool half_out, float *m_chunk,
+                           cudaStream_t st) {
+  if (half_out) return launch_outer_tc_t<T, MODE, T>(d, A, X, M, K, Bprev, Uprev, out, m_chunk, st);
+  return launch_outer_tc_t<T, MODE, float>(d, A, X, M, K, Bprev, Uprev, out, m_chunk, st);
 }
 
 template <typename T>
@@ -258,28 +266,37 @@ static int launch_scan_bwd_ws(const ScanDims &d, const ScanBwdArgs<T> &a, cudaSt
   return check_launch("chunk_scan_bwd_ws");
 }
 
-template <typename ST>
-static int launch_state_fwd_t(int BH, int NC, int P, int N, const float *inc, const float *m_chunk, const float *init,
+template <typename ST, typename IT>
+static int launch_state_fwd_t(int BH, int NC, int P, int N, const IT *inc, const float *m_chunk, const float *init,
                               ST *starts, float *final_state, cudaStream_t st) {
   const int elems = P * 2 * N;
   if (elems % 4 == 0) {
     int nv = elems / 4;
-    state_passing_fwd_kernel<4, ST><<<dim3((nv + 255) / 256, BH), 256, 0, st>>>(inc, m_chunk, init, starts,
-                                                                              final_state, NC, nv);
+    state_passing_fwd_kernel<4, ST, IT><<<dim3((nv + 255) / 256, BH), 256, 0, st>>>(inc, m_chunk, init, starts,
+                                                                                  final_state, NC, nv);
   } else {
     int nv = elems / 2;
-    state_passing_fwd_kernel<2, ST><<<dim3((nv + 255) / 256, BH), 256, 0, st>>>(inc, m_chunk, init, starts,
-                                                                              final_state, NC, nv);
+    state_passing_fwd_kernel<2, ST, IT><<<dim3((nv + 255) / 256, BH), 256, 0, st>>>(inc, m_chunk, init, starts,
+                                                                                  final_state, NC, nv);
   }
   return check_launch("state_passing_fwd");
 }
-static int launch_state_fwd(int BH, int NC, int P, int N, const float *inc, const float *m_chunk, const float *init,
-                            void *starts, int starts_dtype, float *final_state, cudaStream_t st) {
-  if (starts_dtype == SLX_BF16)
-    return launch_state_fwd_t<__nv_bfloat16>(BH, NC, P, N, inc, m_chunk, init, (__nv_bfloat16 *)starts, final_state, st);
-  if (starts_dtype == SLX_F16)
-    return launch_state_fwd_t<__half>(BH, NC, P, N, inc, m_chunk, init, (__half *)starts, final_state, st);
-  return launch_state_fwd_t<float>(BH, NC, P, N, inc, m_chunk, init, (float *)starts, final_state, st);
+// inc_dtype is fp32 or starts_dtype (checked by the callers)
+static int launch_state_fwd(int BH, int NC, int P, int N, const void *inc, int inc_dtype, const float *m_chunk,
+                            const float *init, void *starts, int starts_dtype, float *final_state, cudaStream_t st) {
+  const bool half_inc = inc_dtype != SLX_F32;
+  if (starts_dtype == SLX_BF16) {
+    using H = __nv_bfloat16;
+    if (half_inc) return launch_state_fwd_t<H, H>(BH, NC, P, N, (const H *)inc, m_chunk, init, (H *)starts, final_state, st);
+    return launch_state_fwd_t<H, float>(BH, NC, P, N, (const float *)inc, m_chunk, init, (H *)starts, final_state, st);
+  }
+  if (starts_dtype == SLX_F16) {
+    using H = __half;
+    if (half_inc) return launch_state_fwd_t<H, H>(BH, NC, P, N, (const H *)inc, m_chunk, init, (H *)starts, final_state, st);
+    return launch_state_fwd_t<H, float>(BH, NC, P, N, (const float *)inc, m_chunk, init, (H *)starts, final_state, st);
+  }
+  return launch_state_fwd_t<float, float>(BH, NC, P, N, (const float *)inc, m_chunk, init, (float *)starts, final_state,
+                                          st);
 }
 
 static int state_bwd_blocks(int P, int N) {
@@ -288,18 +305,18 @@ static int state_bwd_blocks(int P, int N) {
   return (nv + 255) / 256;
 }
 
-template <typename ST>
-static int launch_state_bwd_t(int BH, int NC, int P, int N, const float *dZ0, const float *m_chunk, const ST *starts,
+template <typename ST, typename IT>
+static int launch_state_bwd_t(int BH, int NC, int P, int N, const IT *dZ0, const float *m_chunk, const ST *starts,
                               const float *final_state, const float *d_final, ST *d_inc, float *d_initial,
                               float *zdot, float *partials, cudaStream_t st) {
   const int elems = P * 2 * N;
   const int nblk = state_bwd_blocks(P, N);
   if (elems % 4 == 0) {
-    state_passing_bwd_kernel<4, ST><<<dim3(nblk, BH), 256, 0, st>>>(dZ0, m_chunk, starts, final_state, d_final, d_inc,
-                                                                   d_initial, partials, NC, elems / 4);
+    state_passing_bwd_kernel<4, ST, IT><<<dim3(nblk, BH), 256, 0, st>>>(dZ0, m_chunk, starts, final_state, d_final,
+                                                                       d_inc, d_initial, partials, NC, elems / 4);
   } else {
-    state_passing_bwd_kernel<2, ST><<<dim3(nblk, BH), 256, 0, st>>>(dZ0, m_chunk, starts, final_state, d_final, d_inc,
-                                                                   d_initial, partials, NC, elems / 2);
+    state_passing_bwd_kernel<2, ST, IT><<<dim3(nblk, BH), 256, 0, st>>>(dZ0, m_chunk, starts, final_state, d_final,
+                                                                       d_inc, d_initial, partials, NC, elems / 2);
   }
   int rc = check_launch("state_passing_bwd");
   if (rc || partials == nullptr) return rc;
@@ -307,20 +324,32 @@ static int launch_state_bwd_t(int BH, int NC, int P, int N, const float *dZ0, co
   zdot_reduce_kernel<<<(rows + 255) / 256, 256, 0, st>>>(partials, zdot, rows, nblk);
   return check_launch("zdot_reduce");
 }
-static int launch_state_bwd(int BH, int NC, int P, int N, const float *dZ0, const float *m_chunk, const void *starts,
-                            int starts_dtype, const float *final_state, const float *d_final, void *d_inc,
-                            float *d_initial, float *zdot, float *partials, cudaStream_t st) {
-  if (starts_dtype == SLX_BF16)
-    return launch_state_bwd_t<__nv_bfloat16>(BH, NC, P, N, dZ0, m_chunk, (const __nv_bfloat16 *)starts, final_state,
-                                             d_final, (__nv_bfloat16 *)d_inc, d_initial, zdot, partials, st);
-  if (starts_dtype == SLX_F16)
-    return launch_state_bwd_t<__half>(BH, NC, P, N, dZ0, m_chunk, (const __half *)starts, final_state, d_final,
-                                      (__half *)d_inc, d_initial, zdot, partials, st);
-  return launch_state_bwd_t<float>(BH, NC, P, N, dZ0, m_chunk, (const float *)starts, final_state, d_final,
-                                   (float *)d_inc, d_initial, zdot, partials, st);
+// dz0_dtype is fp32 or starts_dtype (checked by the callers)
+static int launch_state_bwd(int BH, int NC, int P, int N, const void *dZ0, int dz0_dtype, const float *m_chunk,
+                            const void *starts, int starts_dtype, const float *final_state, const float *d_final,
+                            void *d_inc, float *d_initial, float *zdot, float *partials, cudaStream_t st) {
+  const bool half_dz = dz0_dtype != SLX_F32;
+  if (starts_dtype == SLX_BF16) {
+    using H = __nv_bfloat16;
+    if (half_dz)
+      return launch_state_bwd_t<H, H>(BH, NC, P, N, (const H *)dZ0, m_chunk, (const H *)starts, final_state, d_final,
+                                      (H *)d_inc, d_initial, zdot, partials, st);
+    return launch_state_bwd_t<H, float>(BH, NC, P, N, (const float *)dZ0, m_chunk, (const H *)starts, final_state,
+                                        d_final, (H *)d_inc, d_initial, zdot, partials, st);
+  }
+  if (starts_dtype == SLX_F16) {
+    using H = __half;
+    if (half_dz)
+      return launch_state_bwd_t<H, H>(BH, NC, P, N, (const H *)dZ0, m_chunk, (const H *)starts, final_state, d_final,
+                                      (H *)d_inc, d_initial, zdot, partials, st);
+    return launch_state_bwd_t<H, float>(BH, NC, P, N, (const float *)dZ0, m_chunk, (const H *)starts, final_state,
+                                        d_final, (H *)d_inc, d_initial, zdot, partials, st);
+  }
+  return launch_state_bwd_t<float, float>(BH, NC, P, N, (const float *)dZ0, m_chunk, (const float *)starts, final_state,
+                                          d_final, (float *)d_inc, d_initial, zdot, partials, st);
 }
 
-// workspace layout of the backward (all fp32, 256-byte aligned sections)
+// workspace layout of the backward (256-byte aligned sections; dZ0 and d_inc as starts_dtype, the rest fp32)
 struct BwdWs {
   size_t d_inc, dz0, zdot, partials, carryB, carryU, total;  // dz0 == d_inc where the reverse pass runs in place
 };
@@ -330,11 +359,12 @@ static BwdWs bwd_ws(const ScanDims &d, int starts_dtype) {
   size_t off = 0;
   const size_t n_state = (size_t)d.BH * d.NC * d.P * d.D;
   w.dz0 = off;
-  off += align256(sizeof(float) * n_state);
   if (starts_dtype == SLX_F32) {
+    off += align256(sizeof(float) * n_state);
     w.d_inc = w.dz0;  // fp32 d_inc overwrites dZ0 chunk by chunk
-  } else {
-    w.d_inc = off;  // d_inc in the activation dtype next to the fp32 dZ0
+  } else {  // dZ0 and d_inc both in the activation dtype, side by side
+    off += align256(2 * n_state);
+    w.d_inc = off;
     off += align256(2 * n_state);
   }
   w.zdot = off;
@@ -411,26 +441,32 @@ int slx_read_scan_status(int *host_out) {
 const char *slx_last_error_string(void) { return g_err; }
 
 int slx_chunk_increment_fwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
-                            const float *B_prev, const float *U_prev, float *inc, float *m_chunk, void *stream) {
+                            const float *B_prev, const float *U_prev, void *inc, int32_t inc_dtype, float *m_chunk,
+                            void *stream) {
   ScanDims d;
   int rc = check_shape(s, &d);
   if (rc) return rc;
   SLX_REQUIRE(U && M && K && B && inc && m_chunk, SLX_E_NULL, "chunk_increment_fwd: NULL tensor");
+  SLX_REQUIRE(inc_dtype == SLX_F32 || (use_tc(s) && inc_dtype == s->dtype), SLX_E_DTYPE,
+              "chunk_increment_fwd: inc_dtype %d must be fp32, or the activation dtype on the tensor-core path",
+              inc_dtype);
   SLX_REQUIRE_ALIGNED("chunk_increment_fwd", U, M, K, B, B_prev, U_prev, inc, m_chunk);
   SLX_REQUIRE((B_prev == nullptr) == (U_prev == nullptr), SLX_E_NULL, "B_prev and U_prev must be passed together");
   if (use_tc(s)) {
     if (s->dtype == SLX_BF16)
-      return launch_outer_tc<__nv_bfloat16, 0>(d, U, B, M, K, B_prev, U_prev, inc, m_chunk, as_stream(stream));
-    return launch_outer_tc<__half, 0>(d, U, B, M, K, B_prev, U_prev, inc, m_chunk, as_stream(stream));
+      return launch_outer_tc<__nv_bfloat16, 0>(d, U, B, M, K, B_prev, U_prev, inc, inc_dtype != SLX_F32, m_chunk,
+                                               as_stream(stream));
+    return launch_outer_tc<__half, 0>(d, U, B, M, K, B_prev, U_prev, inc, inc_dtype != SLX_F32, m_chunk,
+                                      as_stream(stream));
   }
-  SLX_DISPATCH_T(s->dtype, SLX_DISPATCH_L(d.L, rc = (launch_outer<T_, L_, 0>(d, U, B, M, K, B_prev, U_prev, inc,
+  SLX_DISPATCH_T(s->dtype, SLX_DISPATCH_L(d.L, rc = (launch_outer<T_, L_, 0>(d, U, B, M, K, B_prev, U_prev, (float *)inc,
                                                                               m_chunk, as_stream(stream)))));
   return rc;
 }
 
-int slx_state_passing_fwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const float *inc, const float *m_chunk,
-                          const float *initial_states, void *chunk_starts, int32_t starts_dtype, float *final_state,
-                          void *stream) {
+int slx_state_passing_fwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const void *inc, int32_t inc_dtype,
+                          const float *m_chunk, const float *initial_states, void *chunk_starts, int32_t starts_dtype,
+                          float *final_state, void *stream) {
   SLX_REQUIRE(BH > 0 && NC > 0 && P > 0 && N > 0, SLX_E_SHAPE, "state_passing_fwd: sizes must be positive");
   SLX_REQUIRE(BH <= 65535, SLX_E_UNSUPPORTED, "batch_heads=%d exceeds 65535", BH);
   SLX_REQUIRE(inc && m_chunk && final_state, SLX_E_NULL, "state_passing_fwd: NULL tensor");
@@ -439,8 +475,13 @@ int slx_state_passing_fwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const fl
               "state_passing_fwd: bad starts_dtype %d", starts_dtype);
   SLX_REQUIRE(starts_dtype == SLX_F32 || chunk_starts != (void *)inc, SLX_E_UNSUPPORTED,
               "state_passing_fwd: the in-place pass needs fp32 chunk_starts");
-  return launch_state_fwd(BH, NC, P, N, inc, m_chunk, initial_states, chunk_starts, starts_dtype, final_state,
-                          as_stream(stream));
+  SLX_REQUIRE(inc_dtype == SLX_F32 || inc_dtype == SLX_BF16 || inc_dtype == SLX_F16, SLX_E_DTYPE,
+              "state_passing_fwd: bad inc_dtype %d", inc_dtype);
+  if (chunk_starts == nullptr && inc_dtype != SLX_F32) starts_dtype = inc_dtype;  // nothing is stored as starts_dtype
+  SLX_REQUIRE(inc_dtype == SLX_F32 || inc_dtype == starts_dtype, SLX_E_DTYPE,
+              "state_passing_fwd: inc_dtype %d must be fp32 or starts_dtype %d", inc_dtype, starts_dtype);
+  return launch_state_fwd(BH, NC, P, N, inc, inc_dtype, m_chunk, initial_states, chunk_starts, starts_dtype,
+                          final_state, as_stream(stream));
 }
 
 int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
@@ -471,7 +512,7 @@ int slx_chunk_scan_fwd(const slx_scan_shape *s, const void *U, const float *M, c
 
 int slx_v2x2ssd_fwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
                     const void *C, const float *initial_states, const float *B_prev, const float *U_prev, void *Y,
-                    float *final_state, void *chunk_starts, float *m_chunk, float *increments, void *stream) {
+                    float *final_state, void *chunk_starts, float *m_chunk, void *increments, void *stream) {
   ScanDims d0;
   {
     int rc0 = check_shape(s, &d0);
@@ -480,12 +521,12 @@ int slx_v2x2ssd_fwd(const slx_scan_shape *s, const void *U, const float *M, cons
   const int sdt = s->starts_dtype;
   SLX_REQUIRE(increments != nullptr || sdt == SLX_F32, SLX_E_NULL,
               "v2x2ssd_fwd: this shape keeps chunk_starts in the activation dtype and needs the increments buffer");
-  float *inc = increments ? increments : (float *)chunk_starts;
-  int rc = slx_chunk_increment_fwd(s, U, M, K, B, B_prev, U_prev, inc, m_chunk, stream);
+  void *inc = increments ? increments : chunk_starts;  // increments are stored as starts_dtype, like the states
+  int rc = slx_chunk_increment_fwd(s, U, M, K, B, B_prev, U_prev, inc, sdt, m_chunk, stream);
   if (rc) return rc;
   SLX_REQUIRE(final_state != nullptr, SLX_E_NULL, "v2x2ssd_fwd: final_state is NULL");
   const int NC = (s->T + s->chunk - 1) / s->chunk;
-  rc = slx_state_passing_fwd(s->batch_heads, NC, s->P, s->N, inc, m_chunk, initial_states, chunk_starts, sdt,
+  rc = slx_state_passing_fwd(s->batch_heads, NC, s->P, s->N, inc, sdt, m_chunk, initial_states, chunk_starts, sdt,
                              final_state, stream);
   if (rc) return rc;
   return slx_chunk_scan_fwd(s, U, M, K, B, C, chunk_starts, B_prev, U_prev, Y, stream);
@@ -497,25 +538,30 @@ size_t slx_v2x2ssd_bwd_workspace_bytes(const slx_scan_shape *s) {
   return bwd_ws(d, s->starts_dtype).total;
 }
 
-int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *C, const void *dY, float *dZ0,
-                           void *stream) {
+int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *C, const void *dY, void *dZ0,
+                           int32_t dz0_dtype, void *stream) {
   ScanDims d;
   int rc = check_shape(s, &d);
   if (rc) return rc;
   SLX_REQUIRE(M && C && dY && dZ0, SLX_E_NULL, "chunk_scan_bwd_dz0: NULL tensor");
+  SLX_REQUIRE(dz0_dtype == SLX_F32 || (use_tc(s) && dz0_dtype == s->dtype), SLX_E_DTYPE,
+              "chunk_scan_bwd_dz0: dz0_dtype %d must be fp32, or the activation dtype on the tensor-core path",
+              dz0_dtype);
   SLX_REQUIRE_ALIGNED("chunk_scan_bwd_dz0", M, C, dY, dZ0);
   if (use_tc(s)) {
     if (s->dtype == SLX_BF16)
-      return launch_outer_tc<__nv_bfloat16, 1>(d, dY, C, M, nullptr, nullptr, nullptr, dZ0, nullptr,
-                                               as_stream(stream));
-    return launch_outer_tc<__half, 1>(d, dY, C, M, nullptr, nullptr, nullptr, dZ0, nullptr, as_stream(stream));
+      return launch_outer_tc<__nv_bfloat16, 1>(d, dY, C, M, nullptr, nullptr, nullptr, dZ0, dz0_dtype != SLX_F32,
+                                               nullptr, as_stream(stream));
+    return launch_outer_tc<__half, 1>(d, dY, C, M, nullptr, nullptr, nullptr, dZ0, dz0_dtype != SLX_F32, nullptr,
+                                      as_stream(stream));
   }
   SLX_DISPATCH_T(s->dtype, SLX_DISPATCH_L(d.L, rc = (launch_outer<T_, L_, 1>(d, dY, C, M, nullptr, nullptr, nullptr,
-                                                                              dZ0, nullptr, as_stream(stream)))));
+                                                                              (float *)dZ0, nullptr, as_stream(stream)))));
   return rc;
 }
 
-int slx_state_passing_bwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const float *dZ0, const float *m_chunk,
+int slx_state_passing_bwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const void *dZ0, int32_t dz0_dtype,
+                          const float *m_chunk,
                           const void *chunk_starts, int32_t starts_dtype, const float *final_state,
                           const float *d_final, void *d_inc,
                           float *d_initial, float *zdot, float *zdot_partials, void *stream) {
@@ -532,9 +578,14 @@ int slx_state_passing_bwd(int32_t BH, int32_t NC, int32_t P, int32_t N, const fl
               "state_passing_bwd: the in-place pass needs fp32 d_inc");
   SLX_REQUIRE(starts_dtype == SLX_F32 || starts_dtype == SLX_BF16 || starts_dtype == SLX_F16, SLX_E_DTYPE,
               "state_passing_bwd: bad starts_dtype %d", starts_dtype);
-  return launch_state_bwd(BH, NC, P, N, dZ0, m_chunk, chunk_starts, starts_dtype, final_state, d_final, d_inc,
-                          d_initial, zdot,
-                          zdot_partials, as_stream(stream));
+  SLX_REQUIRE(dz0_dtype == SLX_F32 || dz0_dtype == SLX_BF16 || dz0_dtype == SLX_F16, SLX_E_DTYPE,
+              "state_passing_bwd: bad dz0_dtype %d", dz0_dtype);
+  // with neither d_inc nor the dot products asked for, nothing is read or stored as starts_dtype
+  if (d_inc == nullptr && zdot == nullptr && dz0_dtype != SLX_F32) starts_dtype = dz0_dtype;
+  SLX_REQUIRE(dz0_dtype == SLX_F32 || dz0_dtype == starts_dtype, SLX_E_DTYPE,
+              "state_passing_bwd: dz0_dtype %d must be fp32 or starts_dtype %d", dz0_dtype, starts_dtype);
+  return launch_state_bwd(BH, NC, P, N, dZ0, dz0_dtype, m_chunk, chunk_starts, starts_dtype, final_state, d_final,
+                          d_inc, d_initial, zdot, zdot_partials, as_stream(stream));
 }
 
 int slx_chunk_scan_bwd(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,
@@ -583,7 +634,7 @@ static int v2x2ssd_bwd_impl(const slx_scan_shape *s, const void *U, const float 
               "v2x2ssd_bwd: workspace must be 256-byte aligned");
   char *base = static_cast<char *>(workspace);
   void *d_inc = base + w.d_inc;
-  float *dz0 = reinterpret_cast<float *>(base + w.dz0);
+  void *dz0 = base + w.dz0;  // stored as starts_dtype
   float *zdot = reinterpret_cast<float *>(base + w.zdot);
   float *partials = reinterpret_cast<float *>(base + w.partials);
   float *carryB = reinterpret_cast<float *>(base + w.carryB);
@@ -591,12 +642,11 @@ static int v2x2ssd_bwd_impl(const slx_scan_shape *s, const void *U, const float 
   cudaStream_t st = as_stream(stream);
 
   if (!dz0_ready) {
-    rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, dz0, stream);
+    rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, dz0, s->starts_dtype, stream);
     if (rc) return rc;
   }
-  rc = launch_state_bwd(d.BH, d.NC, d.P, d.N, dz0, m_chunk, chunk_starts, s->starts_dtype, final_state,
-                        d_final, d_inc, d_initial,
-                        zdot, partials, st);
+  rc = launch_state_bwd(d.BH, d.NC, d.P, d.N, dz0, s->starts_dtype, m_chunk, chunk_starts, s->starts_dtype,
+                        final_state, d_final, d_inc, d_initial, zdot, partials, st);
   if (rc) return rc;
   rc = slx_chunk_scan_bwd(s, U, M, K, B, C, B_prev, U_prev, chunk_starts, d_inc, zdot, dY, dU, dM, dK, dB, dC, carryB,
                           carryU, stream);
@@ -630,11 +680,11 @@ int slx_v2x2ssd_bwd_begin(const slx_scan_shape *s, const float *M, const void *C
               "v2x2ssd_bwd_begin: workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
   SLX_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, SLX_E_WORKSPACE,
               "v2x2ssd_bwd_begin: workspace must be 256-byte aligned");
-  float *dz0 = reinterpret_cast<float *>(static_cast<char *>(workspace) + w.dz0);
-  rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, dz0, stream);
+  void *dz0 = static_cast<char *>(workspace) + w.dz0;
+  rc = slx_chunk_scan_bwd_dz0(s, M, C, dY, dz0, s->starts_dtype, stream);
   if (rc) return rc;
-  return launch_state_bwd(d.BH, d.NC, d.P, d.N, dz0, m_chunk, nullptr, SLX_F32, nullptr, nullptr, nullptr,
-                          d_initial_zero_final, nullptr, nullptr, as_stream(stream));
+  return launch_state_bwd(d.BH, d.NC, d.P, d.N, dz0, s->starts_dtype, m_chunk, nullptr, s->starts_dtype, nullptr,
+                          nullptr, nullptr, d_initial_zero_final, nullptr, nullptr, as_stream(stream));
 }
 
 int slx_v2x2ssd_bwd_finish(const slx_scan_shape *s, const void *U, const float *M, const float *K, const void *B,

@@ -400,9 +400,11 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
 // on tensor cores: out^T (d x p) = Xop^T (d x t) * A (t x p), M = 128 state
 // columns per product, N = 64, K = 128 tokens.  MODE as chunk_outer_kernel:
 // 0 = chunk increment (A = U, x = B, writes m_chunk), 1 = dZ0 (A = dY, x = C).
+// OT is the storage type of `out` (float, or T: the consumer is the fp32 state pass,
+// whose own output is rounded to T for the chunk kernels' operands anyway).
 constexpr size_t outer_tc_smem_bytes() { return 1024 + 80 * 1024 + 8 * 1024; }
 
-template <typename T, int MODE>
+template <typename T, int MODE, typename OT>
 __global__ void __launch_bounds__(kTcThreads, 2) chunk_outer_tc_kernel(OuterArgs<T> a) {
   constexpr int L = kTcL, P = kTcP;
   extern __shared__ unsigned char smem_raw[];
@@ -534,7 +536,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_outer_tc_kernel(OuterArgs
   const bool ok = umma::mbar_wait(mbar_s, 0);
   umma::fence_after_sync();
   const int q4 = warp & 3;
-  float *outc = a.out + ((size_t)bh * d.NC + c) * P * d.D;
+  OT *outc = reinterpret_cast<OT *>(a.out) + ((size_t)bh * d.NC + c) * P * d.D;
   for (int g = warp >> 2; g < NG; g += 2) {
     const int dd = 128 * g + 32 * q4 + lane;
     float v0[32], v1[32];
@@ -545,15 +547,15 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_outer_tc_kernel(OuterArgs
       if (MODE == 0) bw = (dd & 1) ? bh1[dd >> 1].y : bh1[dd >> 1].x;
 #pragma unroll
       for (int p = 0; p < 32; ++p) {
-        outc[(size_t)p * d.D + dd] = (MODE == 0) ? fmaf(um1[p], bw, v0[p]) : v0[p];
-        outc[(size_t)(p + 32) * d.D + dd] = (MODE == 0) ? fmaf(um1[p + 32], bw, v1[p]) : v1[p];
+        outc[(size_t)p * d.D + dd] = from_f<OT>((MODE == 0) ? fmaf(um1[p], bw, v0[p]) : v0[p]);
+        outc[(size_t)(p + 32) * d.D + dd] = from_f<OT>((MODE == 0) ? fmaf(um1[p + 32], bw, v1[p]) : v1[p]);
       }
     }
   }
   umma::fence_before_sync();
   if (__syncthreads_or(!ok)) {  // a bounded wait ran out: NaN instead of values from an unfinished product
     const float nanf_ = __int_as_float(0x7fc00000);
-    for (int e = tid; e < P * d.D; e += kTcThreads) outc[e] = nanf_;
+    for (int e = tid; e < P * d.D; e += kTcThreads) outc[e] = from_f<OT>(nanf_);
     if (tid == 0) atomicExch(&g_tc_status, 1);
   }
   if (warp == 0) umma::tmem_dealloc(tmem, 128);

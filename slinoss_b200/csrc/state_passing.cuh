@@ -71,8 +71,10 @@ __device__ __forceinline__ float2 cdot(float4 a, float4 b) {
 // coalesced 8/16-byte vector.  `starts` may alias `inc`: each chunk's increment
 // is read before its slot is overwritten.  `starts` may be NULL: only the final state is wanted
 // (the affine offset of a segment in the context-parallel chain), and the pass writes nothing else.
-template <int VEC, typename ST>
-__global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc, const float *__restrict__ m_chunk,
+// The increments are stored as IT (float, or the activation dtype where the tensor-core chunk
+// kernel wrote them so); the recurrence is fp32 either way.
+template <int VEC, typename ST, typename IT>
+__global__ void __launch_bounds__(256) state_passing_fwd_kernel(const IT *inc, const float *__restrict__ m_chunk,
                                                                 const float *__restrict__ init, ST *starts,
                                                                 float *__restrict__ final_state, int NC,
                                                                 int n_vec /* P*D/VEC */) {
@@ -81,15 +83,18 @@ __global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc
   const int bh = blockIdx.y;
   if (i >= n_vec) return;
   const size_t per = (size_t)n_vec;
-  const V *incv = reinterpret_cast<const V *>(inc) + (size_t)bh * NC * per + i;
+  const IT *incv = inc + ((size_t)bh * NC * per + i) * VEC;  // + c * per * VEC per chunk
   ST *stv = starts ? starts + ((size_t)bh * NC * per + i) * VEC : nullptr;  // + c * per * VEC per chunk
   const size_t cs = per * VEC;
   const float2 *mc = reinterpret_cast<const float2 *>(m_chunk) + (size_t)bh * NC;
   V z = init ? reinterpret_cast<const V *>(init)[(size_t)bh * per + i] : vzero(V());
   int c = 0;
   for (; c + 4 <= NC; c += 4) {
-    V v0 = incv[(size_t)(c + 0) * per], v1 = incv[(size_t)(c + 1) * per];
-    V v2 = incv[(size_t)(c + 2) * per], v3 = incv[(size_t)(c + 3) * per];
+    V v0, v1, v2, v3;
+    st_load<IT>(incv + (size_t)(c + 0) * cs, v0);
+    st_load<IT>(incv + (size_t)(c + 1) * cs, v1);
+    st_load<IT>(incv + (size_t)(c + 2) * cs, v2);
+    st_load<IT>(incv + (size_t)(c + 3) * cs, v3);
     float2 m0 = mc[c], m1 = mc[c + 1], m2 = mc[c + 2], m3 = mc[c + 3];
     if (stv) st_store<ST>(stv + (size_t)(c + 0) * cs, z);
     z = axpy_c(m0, z, v0);
@@ -101,7 +106,8 @@ __global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc
     z = axpy_c(m3, z, v3);
   }
   for (; c < NC; ++c) {
-    V v = incv[(size_t)c * per];
+    V v;
+    st_load<IT>(incv + (size_t)c * cs, v);
     float2 m = mc[c];
     if (stv) st_store<ST>(stv + (size_t)c * cs, z);
     z = axpy_c(m, z, v);
@@ -116,8 +122,8 @@ __global__ void __launch_bounds__(256) state_passing_fwd_kernel(const float *inc
 // it to the activation dtype for its products anyway); with ST = float it may alias dZ0.  With zdot_partials == NULL the dot products (and the reads
 // of starts / final_state) are skipped, with d_inc == NULL nothing but d_initial is written: that
 // is the reduce-only pass that gives a segment's d_initial for a zero d_final.
-template <int VEC, typename ST>
-__global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0, const float *__restrict__ m_chunk,
+template <int VEC, typename ST, typename IT>
+__global__ void __launch_bounds__(256) state_passing_bwd_kernel(const IT *dZ0, const float *__restrict__ m_chunk,
                                                                 const ST *__restrict__ starts,
                                                                 const float *__restrict__ final_state,
                                                                 const float *__restrict__ d_final, ST *d_inc,
@@ -130,7 +136,7 @@ __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0
   const bool live = i < n_vec;
   const int iv = live ? i : 0;
   const size_t per = (size_t)n_vec;
-  const V *dzv = reinterpret_cast<const V *>(dZ0) + (size_t)bh * NC * per + iv;
+  const IT *dzv = dZ0 + ((size_t)bh * NC * per + iv) * VEC;  // + c * per * VEC per chunk, stored as IT
   ST *div = d_inc ? d_inc + ((size_t)bh * NC * per + iv) * VEC : nullptr;  // + c * per * VEC per chunk
   const size_t ds = per * VEC;
   if (zdot_partials == nullptr) {  // reduce-only / no dot products: a plain reverse recurrence
@@ -138,8 +144,11 @@ __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0
     V g0 = (d_final && live) ? reinterpret_cast<const V *>(d_final)[(size_t)bh * per + iv] : vzero(V());
     int c = NC - 1;
     for (; c >= 3; c -= 4) {  // four loads in flight
-      V d0 = dzv[(size_t)(c - 0) * per], d1 = dzv[(size_t)(c - 1) * per];
-      V d2 = dzv[(size_t)(c - 2) * per], d3 = dzv[(size_t)(c - 3) * per];
+      V d0, d1, d2, d3;
+      st_load<IT>(dzv + (size_t)(c - 0) * ds, d0);
+      st_load<IT>(dzv + (size_t)(c - 1) * ds, d1);
+      st_load<IT>(dzv + (size_t)(c - 2) * ds, d2);
+      st_load<IT>(dzv + (size_t)(c - 3) * ds, d3);
       const float2 m0 = mc0[c], m1 = mc0[c - 1], m2 = mc0[c - 2], m3 = mc0[c - 3];
       if (div && live) st_store<ST>(div + (size_t)(c - 0) * ds, g0);
       g0 = axpy_c(cconj(m0), g0, d0);
@@ -151,7 +160,8 @@ __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0
       g0 = axpy_c(cconj(m3), g0, d3);
     }
     for (; c >= 0; --c) {
-      V dz = dzv[(size_t)c * per];
+      V dz;
+      st_load<IT>(dzv + (size_t)c * ds, dz);
       if (div && live) st_store<ST>(div + (size_t)c * ds, g0);
       g0 = axpy_c(cconj(mc0[c]), g0, dz);
     }
@@ -165,7 +175,8 @@ __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const float *dZ0
   V endst = reinterpret_cast<const V *>(final_state)[(size_t)bh * per + iv];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int c = NC - 1; c >= 0; --c) {
-    V dz = dzv[(size_t)c * per];
+    V dz;
+    st_load<IT>(dzv + (size_t)c * ds, dz);
     V st;  // start of chunk c = end state of chunk c-1 (next iteration)
     st_load<ST>(stv + (size_t)c * cs, st);
     float2 m = mc[c];

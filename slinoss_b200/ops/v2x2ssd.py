@@ -151,9 +151,12 @@ def _stage_inputs(U, M, K, B, C, B_prev, U_prev):
     return cast(U), f32(M), f32(K), cast(B), cast(C)
 
 
-def chunk_increment_b200(U, M, K, B, *, B_prev=None, U_prev=None, chunk_size: int):
-    """Stage 1 -> ``(inc (b,h,C,P,2N) fp32, m_chunk (b,h,C,2) fp32)``.  Inputs are checked as
-    the reference checks them (contiguous, matching shapes, one device)."""
+def chunk_increment_b200(U, M, K, B, *, B_prev=None, U_prev=None, chunk_size: int,
+                         inc_dtype: torch.dtype = torch.float32):
+    """Stage 1 -> ``(inc (b,h,C,P,2N), m_chunk (b,h,C,2) fp32)``.  Inputs are checked as
+    the reference checks them (contiguous, matching shapes, one device).  ``inc`` is fp32 like the
+    reference's by default; ``inc_dtype`` = the activation dtype (tensor-core shapes only) stores
+    it as the fused op does, halving the traffic of this stage's output and the next stage's input."""
     U, M, K, B, _ = _stage_inputs(U, M, K, B, None, B_prev, U_prev)
     b, h, T, P = map(int, U.shape)
     D = int(B.shape[-1])
@@ -162,13 +165,16 @@ def chunk_increment_b200(U, M, K, B, *, B_prev=None, U_prev=None, chunk_size: in
         raise ValueError(f"chunk_size must be positive. Got {chunk_size}.")
     NC = (T + L - 1) // L
     s = _shape(b, h, T, P, D // 2, L, U.dtype)
-    inc = torch.empty((b, h, NC, P, D), device=U.device, dtype=torch.float32)
+    if inc_dtype not in _ACT_DTYPES:
+        raise TypeError(f"inc_dtype must be float32, bfloat16 or float16. Got {inc_dtype}.")
+    inc = torch.empty((b, h, NC, P, D), device=U.device, dtype=inc_dtype)
     mch = torch.empty((b, h, NC, 2), device=U.device, dtype=torch.float32)
     bp, up = _f32(B_prev), _f32(U_prev)
     with _lib.guard(U.device):
         _lib.check(_lib.lib().slx_chunk_increment_fwd(
             byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), _lib.ptr(bp), _lib.ptr(up),
-            inc.data_ptr(), mch.data_ptr(), _lib.stream_ptr(U.device)), "chunk_increment")
+            inc.data_ptr(), _lib.dtype_code(inc_dtype), mch.data_ptr(), _lib.stream_ptr(U.device)),
+            "chunk_increment")
     return inc, mch
 
 
@@ -177,7 +183,9 @@ def state_passing_b200(inc, m_chunk, *, initial_states=None, want_starts: bool =
     """Stage 2 -> ``(chunk_starts, final_state)``.  The recurrence and ``final_state`` are fp32;
     ``chunk_starts`` is stored as ``starts_dtype`` (fp32 like the reference by default; the fused
     op uses the activation dtype where the tensor-core kernels run).  ``want_starts=False``
-    returns ``(None, final_state)`` and writes nothing but the final state (half the traffic)."""
+    returns ``(None, final_state)`` and writes nothing but the final state (half the traffic).
+    ``inc`` is read in its own dtype: fp32, or ``starts_dtype`` (what ``chunk_increment_b200`` wrote
+    with ``inc_dtype`` set)."""
     if inc.ndim != 5:
         raise ValueError(f"inc must be (batch,heads,chunks,P,2N). Got {tuple(inc.shape)}.")
     b, h, NC, P, D = map(int, inc.shape)
@@ -192,14 +200,19 @@ def state_passing_b200(inc, m_chunk, *, initial_states=None, want_starts: bool =
         raise TypeError(f"starts_dtype must be float32, bfloat16 or float16. Got {starts_dtype}.")
     _require_cuda(inc, m_chunk, initial_states)
     dev = _lib.same_device(inc, m_chunk, initial_states)
-    inc, m_chunk = _f32(inc), _f32(m_chunk)
+    if inc.dtype != torch.float32 and want_starts and inc.dtype != starts_dtype:
+        raise TypeError(f"inc must be float32 or starts_dtype={starts_dtype}. Got {inc.dtype}.")
+    if inc.dtype not in _ACT_DTYPES:
+        inc = inc.to(torch.float32)
+    inc, m_chunk = _aligned(inc.detach().contiguous()), _f32(m_chunk)
     init = _f32(initial_states)
     starts = torch.empty(inc.shape, device=dev, dtype=starts_dtype) if want_starts else None
     final = torch.empty((b, h, P, D), device=dev, dtype=torch.float32)
     with _lib.guard(dev):
         _lib.check(_lib.lib().slx_state_passing_fwd(
-            b * h, NC, P, D // 2, inc.data_ptr(), m_chunk.data_ptr(), _lib.ptr(init), _lib.ptr(starts),
-            _lib.dtype_code(starts_dtype), final.data_ptr(), _lib.stream_ptr(dev)), "state_passing")
+            b * h, NC, P, D // 2, inc.data_ptr(), _lib.dtype_code(inc.dtype), m_chunk.data_ptr(), _lib.ptr(init),
+            _lib.ptr(starts), _lib.dtype_code(starts_dtype), final.data_ptr(), _lib.stream_ptr(dev)),
+            "state_passing")
     return starts, final
 
 
@@ -247,8 +260,9 @@ def _fwd_impl(U, M, K, B, C, init32, bp32, up32, L):
     final = torch.empty((b, h, P, D), device=dev, dtype=torch.float32)
     starts = torch.empty((b, h, NC, P, D), device=dev, dtype=_lib.starts_dtype(s))
     mch = torch.empty((b, h, NC, 2), device=dev, dtype=torch.float32)
-    # separate fp32 increment buffer: the two-buffer state pass is ~2.5x faster than the in-place one
-    inc = torch.empty((b, h, NC, P, D), device=dev, dtype=torch.float32)
+    # separate increment buffer (stored like the chunk starts): the two-buffer state pass is ~2.5x
+    # faster than the in-place one
+    inc = torch.empty((b, h, NC, P, D), device=dev, dtype=starts.dtype)
     with _lib.guard(dev):
         _lib.check(_lib.lib().slx_v2x2ssd_fwd(
             byref(s), U.data_ptr(), M.data_ptr(), K.data_ptr(), B.data_ptr(), C.data_ptr(),
@@ -353,7 +367,7 @@ class _V2x2SSDFn(torch.autograd.Function):
                 init32 = starts if starts.numel() else None
                 b_, h_, T_, P_ = map(int, U.shape)
                 sdt = _lib.starts_dtype(_shape(b_, h_, T_, P_, int(B.shape[-1]) // 2, ctx.L, U.dtype))
-                inc, _ = chunk_increment_b200(U, M, K, B, B_prev=bp32, U_prev=up32, chunk_size=ctx.L)
+                inc, _ = chunk_increment_b200(U, M, K, B, B_prev=bp32, U_prev=up32, chunk_size=ctx.L, inc_dtype=sdt)
                 starts, _ = state_passing_b200(inc, mch, initial_states=init32, starts_dtype=sdt)
                 del inc
             dU, dM, dK, dB, dC, d_init, dBp, dUp = _bwd_impl(

@@ -132,7 +132,7 @@ PREP_PARAM_NAMES = ("dt_bias", "gamma_bias", "omega_bias", "mix_r_bias", "mix_th
 
 
 def _cfg0():
-    """BASELINE config 0: scan inputs from a seeded default-init prep."""
+    """Smallest reference shape (b2 H4 T256 P32 N16): scan inputs from a seeded default-init prep."""
     torch.manual_seed(0)
     b, T, H, P, N, L = 2, 256, 4, 32, 16, 64
     prep = _prep_module(H, N, P, seed=0, randomize=False)

@@ -53,14 +53,14 @@ def test_selftest_library_exports_its_header():
 
 
 def test_abi_version(lib):
-    assert lib.slx_abi_version() == 4
+    assert lib.slx_abi_version() == 5
 
 
 def test_argument_errors_are_reported_without_touching_the_gpu(lib):
     from slinoss_b200 import _lib
 
     # NULL shape -> SLX_E_NULL before any CUDA call
-    assert lib.slx_chunk_increment_fwd(None, *([None] * 9)) == -1
+    assert lib.slx_chunk_increment_fwd(None, *([None] * 7), 0, None, None) == -1
     assert b"NULL" in lib.slx_last_error_string()
     s = _lib.ScanShape(4, 64, 32, 16, 48, 0)  # chunk 48 is not a kernel size
     assert lib.slx_chunk_scan_fwd(ctypes.byref(s), *([None] * 10)) == -3

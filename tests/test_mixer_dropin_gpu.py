@@ -18,6 +18,7 @@ same maps, which is the tighter statement.
 
 from __future__ import annotations
 
+import contextlib
 import copy
 
 import pytest
@@ -81,23 +82,63 @@ def test_mixer_layer_bf16_matches_reference_backends():
     assert not bad, bad
 
 
+@contextlib.contextmanager
+def _reference_taps_in_double():
+    """Inside this context the installed reference evaluates its first-order-hold taps in
+    float64 (same closed form, ``kappa1 = (e^z - 1)/z``, ``kappa2 = (e^z (z-1) + 1)/z^2``, results
+    cast back to fp32).  The reference's own fp32 evaluation of ``kappa2`` cancels to a relative
+    error of about eps/|z|^2 (and its autograd derivative to eps/|z|^3) for the small ``|z|`` a
+    default-initialised layer produces, so an fp32 reference run is not a usable truth for the
+    gradients of the scan-prep parameters; this gives one."""
+    import slinoss.layers.scanprep as layer_mod
+    import slinoss.ops.scanprep.reference as ref_mod
+
+    def taps64(dt_f, log_r_f, theta_f, rho, *, eps):
+        z = torch.complex(log_r_f.double(), theta_f.double())
+        e = torch.exp(z)
+        tiny = (z.real.square() + z.imag.square()) < 1e-8
+        zs = torch.where(tiny, torch.ones_like(z), z)
+        k1 = torch.where(tiny, 1 + z / 2 + z * z / 6, (e - 1) / zs)
+        k2 = torch.where(tiny, 0.5 + z / 3 + z * z / 8, (e * (zs - 1) + 1) / (zs * zs))
+        k_prev = dt_f.double() * k2
+        k_curr = dt_f.double() * k1 - k_prev
+        return ref_mod._pack_complex(k_prev), ref_mod._pack_complex(k_curr)
+
+    saved = (layer_mod._foh_taps_from_normalized, ref_mod._foh_taps_from_normalized)
+    layer_mod._foh_taps_from_normalized = ref_mod._foh_taps_from_normalized = taps64
+    try:
+        yield
+    finally:
+        layer_mod._foh_taps_from_normalized, ref_mod._foh_taps_from_normalized = saved
+
+
 def test_mixer_layer_fp32_matches_reference_backends():
-    """fp32 module, ragged length (not a multiple of the chunk), expand 2."""
+    """fp32 module, ragged length (not a multiple of the chunk), expand 2.  Three-way: the B200
+    backends and the reference's fp32 backends against the reference with its taps in double.
+    The layer output must agree to 1e-4; every gradient must be within 3e-4 of the truth or at
+    least as close to it as 1.5x the reference's own fp32 run."""
     prev = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = False
     try:
         ref, ours = _make_mixers(torch.float32, d_model=128, d_state=16, expand=2, chunk=32, seed=3)
+        truth = copy.deepcopy(ref)
+        use_reference_backends(truth)
         g = torch.Generator(device="cuda").manual_seed(4)
         x = torch.randn((2, 77, 128), device="cuda", generator=g)
         w = torch.randn((2, 77, 128), device="cuda", generator=g)
+        with _reference_taps_in_double():
+            y_t, g_t = _run_layer(truth, x, w)
         y_r, g_r = _run_layer(ref, x, w)
         y_o, g_o = _run_layer(ours, x, w)
-        errs = {"y": _rel(y_o, y_r)}
-        errs.update({n: _rel(g_o[n], g_r[n]) for n in g_r})
-        for n, e in errs.items():
-            print(f"[mixer fp32] {n:32s} {e:.3e}")
-        assert errs["y"] <= 1e-4, errs
-        assert max(errs.values()) <= 2e-3, errs
+        report = {"y": (_rel(y_o, y_t), _rel(y_r, y_t), _rel(y_o, y_r))}
+        for n in g_t:
+            report[n] = (_rel(g_o[n], g_t[n]), _rel(g_r[n], g_t[n]), _rel(g_o[n], g_r[n]))
+        for n, (eo, er, eor) in report.items():
+            print(f"[mixer fp32] {n:32s} b200 vs truth {eo:.3e}   reference fp32 vs truth {er:.3e}   "
+                  f"b200 vs reference fp32 {eor:.3e}")
+        assert report["y"][0] <= 1e-4 and report["y"][2] <= 1e-4, report["y"]
+        bad = {n: v for n, v in report.items() if not (v[0] <= 3e-4 or v[0] <= 1.5 * v[1])}
+        assert not bad, bad
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
 
@@ -257,22 +298,31 @@ def test_gate_skip_matches_reference_glue(dtype):
 
 
 def test_mixer_fused_glue_matches_unfused():
-    """``use_b200_backends(..., fuse_glue=True)``: SiLU inside the conv kernel and the one-pass gate/skip
-    give the same layer output and gradients as the reference's own forward on the B200 backends."""
+    """``use_b200_backends(..., fuse_glue=True)``: SiLU inside the conv kernel and the one-pass gate/skip.
+    The fused layer skips two roundings to bf16 that the reference's forward makes, so the two bf16
+    layers are compared three-way against the fp32 reference layer: every tensor of the fused layer
+    must be within 2e-2 of the truth or no further from it than 1.5x the unfused layer."""
     import slinoss_b200 as sb
 
-    _, plain = _make_mixers(torch.bfloat16, d_model=256, d_state=64, expand=1, chunk=64, seed=13)
+    ref, plain = _make_mixers(torch.bfloat16, d_model=256, d_state=64, expand=1, chunk=64, seed=13)
     fused = copy.deepcopy(plain)
     assert sb.use_b200_backends(fused, fuse_glue=True) == 1
+    truth = copy.deepcopy(ref).float()
+    use_reference_backends(truth)
     g = torch.Generator(device="cuda").manual_seed(14)
     x = torch.randn((2, 300, 256), device="cuda", generator=g).to(torch.bfloat16)
     w = torch.randn((2, 300, 256), device="cuda", generator=g)
+    y_t, g_t = _run_layer(truth, x.float(), w)
     y_p, g_p = _run_layer(plain, x, w)
     y_f, g_f = _run_layer(fused, x, w)
-    errs = {"y": _rel(y_f, y_p)}
-    errs.update({n: _rel(g_f[n], g_p[n]) for n in g_p})
-    print("[fused glue]", {k: f"{v:.2e}" for k, v in errs.items()})
-    assert max(errs.values()) <= 1e-2, errs
+    assert set(g_f) == set(g_p) == set(g_t)
+    report = {"y": (_rel(y_f, y_t), _rel(y_p, y_t))}
+    for n in g_t:
+        report[n] = (_rel(g_f[n], g_t[n]), _rel(g_p[n], g_t[n]))
+    for n, (ef, ep) in report.items():
+        print(f"[fused glue] {n:32s} fused vs fp32 truth {ef:.3e}   unfused vs truth {ep:.3e}")
+    bad = {n: v for n, v in report.items() if not (v[0] <= 2e-2 or v[0] <= 1.5 * v[1])}
+    assert not bad, bad
     # streaming state is carried the same way
     with torch.no_grad():
         y_a, st = fused(x[:, :100], return_state=True)

@@ -78,7 +78,7 @@ def test_prep_golden_fp32():
 @pytest.mark.parametrize("dtype,N,P,H,b,T", [
     (torch.bfloat16, 128, 64, 4, 2, 300),   # headline head shape, 16-byte vector path
     (torch.float16, 64, 64, 3, 1, 130),
-    (torch.float32, 16, 32, 4, 2, 256),     # BASELINE config 0 shape
+    (torch.float32, 16, 32, 4, 2, 256),     # the smallest reference shape
     (torch.float32, 5, 6, 2, 1, 33),        # scalar path (nothing 16-byte aligned)
     (torch.bfloat16, 64, 64, 12, 1, 70),    # config-1 head shape; inputs are slices of one projection
     (torch.bfloat16, 32, 64, 8, 2, 300),    # heads % 8 == 0: parameter rows read as aligned 16-byte vectors

@@ -82,6 +82,30 @@ def test_increment_stage_tc_vs_exact(N, T, dtype):
     assert rel_err(to_np(inc_tc), to_np(inc_ex)) < 5e-3
 
 
+@pytest.mark.parametrize("N,T,dtype", [(128, 640, torch.bfloat16), (32, 300, torch.float16)])
+def test_half_increments_are_the_rounded_fp32_ones(N, T, dtype):
+    """The whole-op entry points keep the chunk increments in the activation dtype.  At stage level:
+    ``inc_dtype`` = that dtype gives exactly the fp32 increments rounded once, and the state pass
+    reads them as those values (its recurrence stays fp32)."""
+    import slinoss_b200 as sb
+
+    inp = make_scan_inputs(2, 2, T, N, 64, dtype, seed=N + 1, streaming=True, with_init=True, dist="cfg2")
+    kw = dict(B_prev=inp["B_prev"], U_prev=inp["U_prev"], chunk_size=128)
+    inc32, mch = sb.chunk_increment_b200(inp["U"], inp["M"], inp["K"], inp["B"], **kw)
+    inc16, mch16 = sb.chunk_increment_b200(inp["U"], inp["M"], inp["K"], inp["B"], inc_dtype=dtype, **kw)
+    assert inc16.dtype == dtype and torch.equal(inc16, inc32.to(dtype)) and torch.equal(mch, mch16)
+    st_a, fin_a = sb.state_passing_b200(inc16, mch, initial_states=inp["initial_states"], starts_dtype=dtype)
+    st_b, fin_b = sb.state_passing_b200(inc16.float(), mch, initial_states=inp["initial_states"], starts_dtype=dtype)
+    assert torch.equal(st_a, st_b) and torch.equal(fin_a, fin_b)
+    _, fin_c = sb.state_passing_b200(inc16, mch, initial_states=inp["initial_states"], want_starts=False)
+    assert torch.equal(fin_c, fin_a)
+    # against the fp32 increments the final state moves by the storage rounding only
+    _, fin32 = sb.state_passing_b200(inc32, mch, initial_states=inp["initial_states"])
+    assert rel_err(to_np(fin_a), to_np(fin32)) < (4e-3 if dtype == torch.bfloat16 else 6e-4)
+    with pytest.raises(TypeError):
+        sb.state_passing_b200(inc16, mch, starts_dtype=torch.float32)
+
+
 @pytest.mark.parametrize("N,T,dtype,streaming", [
     (128, 384, torch.bfloat16, True),
     (128, 200, torch.bfloat16, False),   # ragged last chunk

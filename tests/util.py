@@ -15,7 +15,7 @@ def golden(name: str) -> dict:
 
 
 def rel_err(got, ref) -> float:
-    """||got - ref||_2 / ||ref||_2 (the parity metric of the north star)."""
+    """||got - ref||_2 / ||ref||_2 (the parity metric of every scan test)."""
     got = np.asarray(got, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
     den = np.linalg.norm(ref.ravel())
