@@ -344,7 +344,7 @@ def scan_stage_timings(inp, b, h, T, P, N, L, dtype, reps=10, warm=3, only=None)
     dz0 = torch.empty_like(inc)
     d_inc = torch.empty_like(starts)
     zdot = torch.empty((b, h, NC, 2), **f32)
-    part = torch.empty((BH * NC * 2 * 64,), **f32)
+    part = torch.empty((int(lib.slx_state_passing_bwd_partials_bytes(BH, NC, P, N)) // 4,), **f32)
     dU, dB, dC = torch.empty_like(U), torch.empty_like(B), torch.empty_like(C)
     dM, dK = torch.empty_like(M), torch.empty_like(K)
     cB, cU = torch.empty((b, h, NC, D), **f32), torch.empty((b, h, NC, P), **f32)

@@ -145,8 +145,11 @@ int slx_chunk_scan_bwd_dz0(const slx_scan_shape *s, const float *M, const void *
  * values), the chunk-level term of dM.  final_state is the forward's fp32 final
  * state; chunk_starts is read as starts_dtype, dZ0 as dz0_dtype (SLX_F32 or
  * starts_dtype).
+ * zdot_partials is scratch of slx_state_passing_bwd_partials_bytes() bytes.
  * zdot and zdot_partials NULL: no dot products (chunk_starts and final_state are
  * then not read).  d_inc NULL as well: only d_initial is written. */
+size_t slx_state_passing_bwd_partials_bytes(int32_t batch_heads, int32_t n_chunks,
+                                            int32_t P, int32_t N);
 int slx_state_passing_bwd(int32_t batch_heads, int32_t n_chunks, int32_t P,
                           int32_t N, const void *dZ0, int32_t dz0_dtype,
                           const float *m_chunk,

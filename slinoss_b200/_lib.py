@@ -64,6 +64,7 @@ SIGNATURES = {
     "slx_v2x2ssd_fwd": (c_int32, [POINTER(ScanShape)] + [_P] * 14),
     "slx_v2x2ssd_bwd_workspace_bytes": (c_size_t, [POINTER(ScanShape)]),
     "slx_chunk_scan_bwd_dz0": (c_int32, [POINTER(ScanShape)] + [_P] * 4 + [c_int32, _P]),
+    "slx_state_passing_bwd_partials_bytes": (c_size_t, [c_int32] * 4),
     "slx_state_passing_bwd": (c_int32, [c_int32] * 4 + [_P, c_int32] + [_P] * 2 + [c_int32] + [_P] * 7),
     "slx_chunk_scan_bwd": (c_int32, [POINTER(ScanShape)] + [_P] * 19),
     "slx_v2x2ssd_bwd": (c_int32, [POINTER(ScanShape)] + [_P] * 21 + [c_size_t, _P]),

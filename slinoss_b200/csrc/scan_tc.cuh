@@ -545,6 +545,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_outer_tc_kernel(OuterArgs
     if (dd < d.D) {
       float bw = 0.f;
       if (MODE == 0) bw = (dd & 1) ? bh1[dd >> 1].y : bh1[dd >> 1].x;
+      // (for half output, trading values between neighbouring lanes to store 4-byte pairs was
+      // measured slower than these 2-byte stores: 0.227 against 0.203 ms at 8192 chunks)
 #pragma unroll
       for (int p = 0; p < 32; ++p) {
         outc[(size_t)p * d.D + dd] = from_f<OT>((MODE == 0) ? fmaf(um1[p], bw, v0[p]) : v0[p]);

@@ -16,6 +16,15 @@ template <>
 struct VecT<4> {
   using type = float4;
 };
+// eight floats (four complex lanes): the unit of the passes whose stored tensors are all half
+// precision, so that every access is still 16 bytes wide
+struct alignas(16) Float8 {
+  float4 a, b;
+};
+template <>
+struct VecT<8> {
+  using type = Float8;
+};
 
 __device__ __forceinline__ float2 axpy_c(float2 m, float2 z, float2 v) {  // m*z + v
   return make_float2(fmaf(m.x, z.x, fmaf(-m.y, z.y, v.x)), fmaf(m.x, z.y, fmaf(m.y, z.x, v.y)));
@@ -24,6 +33,12 @@ __device__ __forceinline__ float4 axpy_c(float2 m, float4 z, float4 v) {
   float2 a = axpy_c(m, make_float2(z.x, z.y), make_float2(v.x, v.y));
   float2 b = axpy_c(m, make_float2(z.z, z.w), make_float2(v.z, v.w));
   return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ Float8 axpy_c(float2 m, Float8 z, Float8 v) {
+  Float8 r;
+  r.a = axpy_c(m, z.a, v.a);
+  r.b = axpy_c(m, z.b, v.b);
+  return r;
 }
 // chunk-start states are stored as ST (float, or the activation dtype on the tensor-core path:
 // those kernels round Z0 to it anyway); the recurrence itself stays in fp32 registers
@@ -57,6 +72,30 @@ __device__ __forceinline__ void st_load(const ST *p, float4 &v) {
   const PackedVec<ST, 4> q = *reinterpret_cast<const PackedVec<ST, 4> *>(p);
   v = make_float4(to_f(q.v[0]), to_f(q.v[1]), to_f(q.v[2]), to_f(q.v[3]));
 }
+template <typename ST>
+__device__ __forceinline__ void st_store(ST *p, Float8 v) {
+  PackedVec<ST, 8> q;
+  q.v[0] = from_f<ST>(v.a.x);
+  q.v[1] = from_f<ST>(v.a.y);
+  q.v[2] = from_f<ST>(v.a.z);
+  q.v[3] = from_f<ST>(v.a.w);
+  q.v[4] = from_f<ST>(v.b.x);
+  q.v[5] = from_f<ST>(v.b.y);
+  q.v[6] = from_f<ST>(v.b.z);
+  q.v[7] = from_f<ST>(v.b.w);
+  *reinterpret_cast<PackedVec<ST, 8> *>(p) = q;
+}
+template <typename ST>
+__device__ __forceinline__ void st_load(const ST *p, Float8 &v) {
+  const PackedVec<ST, 8> q = *reinterpret_cast<const PackedVec<ST, 8> *>(p);
+  v.a = make_float4(to_f(q.v[0]), to_f(q.v[1]), to_f(q.v[2]), to_f(q.v[3]));
+  v.b = make_float4(to_f(q.v[4]), to_f(q.v[5]), to_f(q.v[6]), to_f(q.v[7]));
+}
+__device__ __forceinline__ Float8 vzero(Float8) {
+  Float8 r;
+  r.a = r.b = make_float4(0.f, 0.f, 0.f, 0.f);
+  return r;
+}
 __device__ __forceinline__ float2 vzero(float2) { return make_float2(0.f, 0.f); }
 __device__ __forceinline__ float4 vzero(float4) { return make_float4(0.f, 0.f, 0.f, 0.f); }
 // sum over the complex lanes of conj(a) * b
@@ -64,6 +103,7 @@ __device__ __forceinline__ float2 cdot(float2 a, float2 b) { return cmul(cconj(a
 __device__ __forceinline__ float2 cdot(float4 a, float4 b) {
   return cadd(cmul(make_float2(a.x, -a.y), make_float2(b.x, b.y)), cmul(make_float2(a.z, -a.w), make_float2(b.z, b.w)));
 }
+__device__ __forceinline__ float2 cdot(Float8 a, Float8 b) { return cadd(cdot(a.a, b.a), cdot(a.b, b.b)); }
 
 // starts[c] = z; z = m_chunk[c] * z + inc[c]     (reference.py:439-457)
 // One thread owns VEC/2 complex state lanes for the whole sequence of chunks;
@@ -116,7 +156,7 @@ __global__ void __launch_bounds__(256) state_passing_fwd_kernel(const IT *inc, c
 }
 
 // Reverse pass: g = d_final; for c = NC-1..0:
-//   zdot_partial[c] = sum conj(end_state_c) * g      (end_state_c = starts[c+1] or final)
+//   zdot_partial[c][warp] = sum over the warp's lanes of conj(end_state_c) * g   (end_state_c = starts[c+1] or final)
 //   d_inc[c] = g;  g = dZ0[c] + conj(m_chunk[c]) * g
 // d_initial = g.  d_inc is stored as ST like the chunk-start states (the per-chunk backward rounds
 // it to the activation dtype for its products anyway); with ST = float it may alias dZ0.  With zdot_partials == NULL the dot products (and the reads
@@ -130,7 +170,6 @@ __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const IT *dZ0, c
                                                                 float *__restrict__ d_initial,
                                                                 float *__restrict__ zdot_partials, int NC, int n_vec) {
   using V = typename VecT<VEC>::type;
-  __shared__ float2 red[8];
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   const int bh = blockIdx.y;
   const bool live = i < n_vec;
@@ -168,35 +207,51 @@ __global__ void __launch_bounds__(256) state_passing_bwd_kernel(const IT *dZ0, c
     if (d_initial && live) reinterpret_cast<V *>(d_initial)[(size_t)bh * per + iv] = g0;
     return;
   }
+  // With the dot products: every warp writes its own partial of every chunk (no barrier in the
+  // loop, so the loads of four chunks are in flight together); zdot_reduce_kernel adds the
+  // gridDim.x * warps partials of a chunk in a fixed order.
   const ST *stv = starts + ((size_t)bh * NC * per + iv) * VEC;
   const size_t cs = per * VEC;
   const float2 *mc = reinterpret_cast<const float2 *>(m_chunk) + (size_t)bh * NC;
   V g = (d_final && live) ? reinterpret_cast<const V *>(d_final)[(size_t)bh * per + iv] : vzero(V());
   V endst = reinterpret_cast<const V *>(final_state)[(size_t)bh * per + iv];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int c = NC - 1; c >= 0; --c) {
-    V dz;
-    st_load<IT>(dzv + (size_t)c * ds, dz);
-    V st;  // start of chunk c = end state of chunk c-1 (next iteration)
-    st_load<ST>(stv + (size_t)c * cs, st);
-    float2 m = mc[c];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const size_t nparts = (size_t)gridDim.x * nwarp;
+  float2 *pout = reinterpret_cast<float2 *>(zdot_partials) + (size_t)bh * NC * nparts + blockIdx.x * nwarp + warp;
+  auto step = [&](int c, const V &dz, const V &st, float2 m) {
     float2 part = live ? cdot(endst, g) : make_float2(0.f, 0.f);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
       part.x += __shfl_xor_sync(0xffffffffu, part.x, off);
       part.y += __shfl_xor_sync(0xffffffffu, part.y, off);
     }
-    if (lane == 0) red[warp] = part;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float2 acc = red[0];
-      for (int w = 1; w < (int)(blockDim.x >> 5); ++w) acc = cadd(acc, red[w]);
-      reinterpret_cast<float2 *>(zdot_partials)[((size_t)bh * NC + c) * gridDim.x + blockIdx.x] = acc;
-    }
-    __syncthreads();
+    if (lane == 0) pout[(size_t)c * nparts] = part;
     if (live && div) st_store<ST>(div + (size_t)c * ds, g);
     g = axpy_c(cconj(m), g, dz);
-    endst = st;
+    endst = st;  // start of chunk c = end state of chunk c-1
+  };
+  int c = NC - 1;
+  for (; c >= 3; c -= 4) {
+    V d0, d1, d2, d3, s0, s1, s2, s3;
+    st_load<IT>(dzv + (size_t)(c - 0) * ds, d0);
+    st_load<ST>(stv + (size_t)(c - 0) * cs, s0);
+    st_load<IT>(dzv + (size_t)(c - 1) * ds, d1);
+    st_load<ST>(stv + (size_t)(c - 1) * cs, s1);
+    st_load<IT>(dzv + (size_t)(c - 2) * ds, d2);
+    st_load<ST>(stv + (size_t)(c - 2) * cs, s2);
+    st_load<IT>(dzv + (size_t)(c - 3) * ds, d3);
+    st_load<ST>(stv + (size_t)(c - 3) * cs, s3);
+    const float2 m0 = mc[c], m1 = mc[c - 1], m2 = mc[c - 2], m3 = mc[c - 3];
+    step(c, d0, s0, m0);
+    step(c - 1, d1, s1, m1);
+    step(c - 2, d2, s2, m2);
+    step(c - 3, d3, s3, m3);
+  }
+  for (; c >= 0; --c) {
+    V dz, st;
+    st_load<IT>(dzv + (size_t)c * ds, dz);
+    st_load<ST>(stv + (size_t)c * cs, st);
+    step(c, dz, st, mc[c]);
   }
   if (d_initial && live) reinterpret_cast<V *>(d_initial)[(size_t)bh * per + iv] = g;
 }

@@ -115,8 +115,8 @@ def _reference_taps_in_double():
 def test_mixer_layer_fp32_matches_reference_backends():
     """fp32 module, ragged length (not a multiple of the chunk), expand 2.  Three-way: the B200
     backends and the reference's fp32 backends against the reference with its taps in double.
-    The layer output must agree to 1e-4; every gradient must be within 3e-4 of the truth or at
-    least as close to it as 1.5x the reference's own fp32 run."""
+    The layer output must agree with both to 1e-4 and every gradient must be within 2e-5 of the
+    truth (measured ~1e-6, where the reference's own fp32 run is up to 2.4e-3 away from it)."""
     prev = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = False
     try:
@@ -137,7 +137,7 @@ def test_mixer_layer_fp32_matches_reference_backends():
             print(f"[mixer fp32] {n:32s} b200 vs truth {eo:.3e}   reference fp32 vs truth {er:.3e}   "
                   f"b200 vs reference fp32 {eor:.3e}")
         assert report["y"][0] <= 1e-4 and report["y"][2] <= 1e-4, report["y"]
-        bad = {n: v for n, v in report.items() if not (v[0] <= 3e-4 or v[0] <= 1.5 * v[1])}
+        bad = {n: v for n, v in report.items() if not v[0] <= 2e-5}
         assert not bad, bad
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
@@ -301,7 +301,9 @@ def test_mixer_fused_glue_matches_unfused():
     """``use_b200_backends(..., fuse_glue=True)``: SiLU inside the conv kernel and the one-pass gate/skip.
     The fused layer skips two roundings to bf16 that the reference's forward makes, so the two bf16
     layers are compared three-way against the fp32 reference layer: every tensor of the fused layer
-    must be within 2e-2 of the truth or no further from it than 1.5x the unfused layer."""
+    must be within 2e-2 of the truth or no further from it than 1.5x the unfused layer.  The per-head
+    bias gradients of the scan prep (4 numbers each here, every one a sum of ~1e5 signed terms that
+    nearly cancel) move by a few percent between any two bf16 evaluations of the layer; they get 5e-2."""
     import slinoss_b200 as sb
 
     ref, plain = _make_mixers(torch.bfloat16, d_model=256, d_state=64, expand=1, chunk=64, seed=13)
@@ -321,7 +323,9 @@ def test_mixer_fused_glue_matches_unfused():
         report[n] = (_rel(g_f[n], g_t[n]), _rel(g_p[n], g_t[n]))
     for n, (ef, ep) in report.items():
         print(f"[fused glue] {n:32s} fused vs fp32 truth {ef:.3e}   unfused vs truth {ep:.3e}")
-    bad = {n: v for n, v in report.items() if not (v[0] <= 2e-2 or v[0] <= 1.5 * v[1])}
+    small = {n for n in g_t if g_t[n].numel() <= 16}
+    bad = {n: v for n, v in report.items()
+           if not (v[0] <= 2e-2 or v[0] <= 1.5 * v[1] or (n in small and v[0] <= 5e-2))}
     assert not bad, bad
     # streaming state is carried the same way
     with torch.no_grad():

@@ -196,10 +196,12 @@ def test_two_call_backward_and_final_only_state_pass(dtype, T, N, P, L):
         assert torch.equal(a, b_)
     zero = _bwd_impl(U, M, K, B, C, bp, up, starts, mch, fin, dY, None, L, want_initial=True, want_prev=True)
     assert torch.equal(g0, zero[5])
-    inc, mch2 = sb.chunk_increment_b200(U, M, K, B, B_prev=bp, U_prev=up, chunk_size=L)
-    st_full, fin_full = sb.state_passing_b200(inc, mch2, initial_states=init)
+    # the fused forward stores its increments like its chunk starts
+    inc, mch2 = sb.chunk_increment_b200(U, M, K, B, B_prev=bp, U_prev=up, chunk_size=L, inc_dtype=starts.dtype)
+    st_full, fin_full = sb.state_passing_b200(inc, mch2, initial_states=init, starts_dtype=starts.dtype)
     none, fin_only = sb.state_passing_b200(inc, mch2, initial_states=init, want_starts=False)
     assert none is None and torch.equal(fin_only, fin_full) and torch.equal(fin_full, fin)
+    assert torch.equal(st_full, starts)
 
 
 def test_views_at_odd_storage_offsets_are_handled():

@@ -202,8 +202,9 @@ def test_chunk_starts_dtype_follows_the_kernel_path():
     assert _lib.starts_dtype(_shape(1, 2, 256, 64, 64, 128, torch.float32)) == torch.float32
     Y, fin, starts, mch = _fwd_impl(U, M, K, B, C, None, None, None, 128)
     assert starts.dtype == torch.bfloat16
-    inc, mch2 = sb.chunk_increment_b200(U, M, K, B, chunk_size=128)
-    st32, fin2 = sb.state_passing_b200(inc, mch2)
+    # the fused op keeps its increments in the activation dtype too; fp32 starts from those increments
+    inc, mch2 = sb.chunk_increment_b200(U, M, K, B, chunk_size=128, inc_dtype=torch.bfloat16)
+    st32, fin2 = sb.state_passing_b200(inc.float(), mch2)
     assert st32.dtype == torch.float32 and torch.equal(fin2, fin)
     assert torch.equal(st32.to(torch.bfloat16), starts)          # same recurrence, one rounding
     y_stage = sb.chunk_scan_b200(U, M, K, B, C, st32, chunk_size=128)   # fp32 starts are converted
