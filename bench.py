@@ -260,8 +260,10 @@ def run_reference_arm(args, cfg):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    n_slices = 2
-    cpu_sample(cfg, args.chunk, 1, warm=True)
+    # one slice timed first; then as many slices per step as keep the whole run within ~2 minutes
+    t_one, _, _ = cpu_sample(cfg, args.chunk, 1, warm=True)
+    BH = cfg["batch"] * cfg["heads"]
+    n_slices = max(1, min(BH, int(120.0 / (max(args.steps, 1) * max(t_one, 1e-3)))))
     for i in range(max(args.warmup - 1, 0)):
         cpu_sample(dict(cfg, T=min(cfg["T"], 1024)), args.chunk, 1, seed=900 + i, warm=False)
     secs, units, info = [], n_slices, None
@@ -897,7 +899,10 @@ def main() -> int:
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        sec, units, info = cpu_sample(cfg, L, 4)
+        t_one, _, _ = cpu_sample(cfg, L, 1)
+        # ~15 s of host work: the whole workload when it fits, else as many slices as do
+        sec, units, info = cpu_sample(cfg, L, max(1, min(cfg["batch"] * cfg["heads"], int(15.0 / max(t_one, 1e-3)))),
+                                      warm=False)
         cpu = dict(info, value=cpu_tokens_per_s(cfg, sec, units, T), seconds=round(sec, 2))
 
     if rank == 0:

@@ -21,13 +21,16 @@ struct alignas(64) ScanTileMaps {
 };
 
 __device__ int g_tc_status = 0;  // becomes non-zero when a bounded wait ran out
-// Phase-clock stamps (clock64() of CTA (0,0) at the phase boundaries) exist only in builds with
+// Phase-clock stamps (clock64() of the CTA in the middle of the grid, i.e. of a steady-state wave, at the
+// phase boundaries) exist only in builds with
 // -DSLX_DIAG; the shipped library carries none.
 #ifdef SLX_DIAG
 __device__ long long g_phase_clock[128];
-#define SLX_DIAG_STAMP(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_phase_clock[i] = clock64(); } while (0)
+#define SLX_DIAG_STAMP(i) SLX_DIAG_STAMP_T(i, 0)
+#define SLX_DIAG_STAMP_T(i, t) do { if (blockIdx.x == gridDim.x / 2 && blockIdx.y == gridDim.y / 2 && threadIdx.x == (t)) g_phase_clock[i] = clock64(); } while (0)
 #else
 #define SLX_DIAG_STAMP(i) do { } while (0)
+#define SLX_DIAG_STAMP_T(i, t) do { } while (0)
 #endif
 
 constexpr int kTcL = 128;
