@@ -50,7 +50,7 @@ def _worker(rank, world, port, out_dir):
         gf = torch.autograd.grad([Yf, finf], full + [init_f], [inp["dY"], inp["d_final"].to(finf.dtype)])
 
         def rel(a, b):
-            return float((a.float() - b.float()).norm() / b.float().norm())
+            return float((a.detach().float() - b.detach().float()).norm() / b.detach().float().norm())
 
         errs = {"Y": rel(Y, Yf[:, :, lo:hi])}
         for n, g, r in zip(names, grads, gf):
