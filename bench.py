@@ -491,6 +491,55 @@ def prep_conv_decode_timings(b, T, H, P, N, dtype, reps=10, warm=3, only=None, d
 
             out.append(_stage("cconv1d_bwd", _time_kernel(cbwd, reps, warm), b * T * Cn * 3 * es, 0, peaks, "hbm"))
         del x, y
+    if want("gate_skip_fwd") or want("gate_skip_bwd"):
+        # the mixer's skip + re-layout + SiLU gate (one pass each way); gate read as a contiguous (b,T,H*P) tensor
+        yh = torch.randn((b, H, T, P), generator=g).to(dtype).to(dev)
+        uh = torch.randn((b, H, T, P), generator=g).to(dtype).to(dev)
+        gt = torch.randn((b, T, H * P), generator=g).to(dtype).to(dev)
+        sk = torch.randn((H * P,), generator=g).to(dev)
+        og = torch.empty((b, T, H * P), device=dev, dtype=dtype)
+        gs = _lib.GlueShape(b, T, H, P, _lib.dtype_code(dtype), H * P, T * H * P)
+        n_el = b * T * H * P
+
+        def gfwd():
+            ck(lib.slx_gate_skip_fwd(byref(gs), yh.data_ptr(), uh.data_ptr(), gt.data_ptr(), sk.data_ptr(), og.data_ptr(),
+                                     st), "gate_skip fwd")
+
+        if want("gate_skip_fwd"):
+            out.append(_stage("gate_skip_fwd", _time_kernel(gfwd, reps, warm), n_el * 4 * es, 0, peaks, "hbm",
+                              "reads y, u, gate; writes the gated token-major rows"))
+        if want("gate_skip_bwd"):
+            go = torch.randn_like(og)
+            dyh, duh, dgt = torch.empty_like(yh), torch.empty_like(uh), torch.empty_like(gt)
+            dsk = torch.empty((H * P,), device=dev, dtype=torch.float32)
+            nbytes = int(lib.slx_gate_skip_bwd_workspace_bytes(byref(gs)))
+            wsg = torch.empty((max(nbytes, 16),), device=dev, dtype=torch.uint8)
+
+            def gbwd():
+                ck(lib.slx_gate_skip_bwd(byref(gs), yh.data_ptr(), uh.data_ptr(), gt.data_ptr(), sk.data_ptr(),
+                                         go.data_ptr(), dyh.data_ptr(), duh.data_ptr(), dgt.data_ptr(), dsk.data_ptr(),
+                                         wsg.data_ptr(), nbytes, st), "gate_skip bwd")
+
+            out.append(_stage("gate_skip_bwd", _time_kernel(gbwd, reps, warm), n_el * 7 * es, 0, peaks, "hbm",
+                              "reads y, u, gate, d_out; writes dy, du, d_gate (+ d_skip partials)"))
+        del yh, uh, gt, og
+    if want("cconv1d_update"):
+        # one decode token through the conv (state shifted in place), serving batch
+        bd, Cn, W = decode_batch, H * P, 4
+        xu = torch.randn((bd, Cn), generator=g).to(dtype).to(dev)
+        wu = torch.randn((Cn, W), generator=g).to(dtype).to(dev)
+        bu = torch.randn((Cn,), generator=g).to(dtype).to(dev)
+        su = torch.randn((bd, Cn, W - 1), generator=g).to(dtype).to(dev)
+        yu = torch.empty_like(xu)
+        cs = _lib.ConvShape(bd, 1, Cn, W, _lib.dtype_code(dtype), 1, Cn, Cn)
+
+        def cupd():
+            ck(lib.slx_cconv1d_update(byref(cs), xu.data_ptr(), wu.data_ptr(), bu.data_ptr(), su.data_ptr(), yu.data_ptr(),
+                                      su.data_ptr(), st), "conv update")
+
+        out.append(_stage("cconv1d_update", _time_kernel(cupd, reps, warm), bd * Cn * (2 + 2 * (W - 1)) * es, 0, peaks,
+                          "hbm", f"one token, batch {bd}, {Cn} channels, SiLU fused, state updated in place "
+                                 "(3.7 MB: latency-bound, not bandwidth-bound)"))
     if want("decode_step"):
         bd = decode_batch
         r = lambda *sh: torch.randn(*sh, generator=g)
