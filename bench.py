@@ -908,7 +908,38 @@ def main() -> int:
         e2e = dict(value=tokens_step / (float(te.item()) / Ke * 1e-3), unit="tokens/s",
                    h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, steps=Ke,
                    overlap="upload, kernels and download of consecutive steps on three streams, two buffer slots")
-        del host_in, host_out, dev_in
+        # what the host link gives for the same buffers with no kernels in between (this rank's copies while the
+        # other ranks do the same): upload alone, download alone, both at once.  The end-to-end step cannot be
+        # faster than its larger copy at the both-at-once rate.
+        outs0 = [torch.empty(o.shape, dtype=o.dtype, device=dev) for o in host_out[0]]
+
+        def up():
+            with torch.cuda.stream(s_in):
+                for k in host_in:
+                    dev_in[0][k].copy_(host_in[k], non_blocking=True)
+
+        def down():
+            with torch.cuda.stream(s_out):
+                for ho, o in zip(host_out[0], outs0):
+                    ho.copy_(o, non_blocking=True)
+
+        def timed(fns, reps=3):
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                for f in fns:
+                    f()
+            s_in.synchronize()
+            s_out.synchronize()
+            return (time.perf_counter() - t0) / reps
+
+        up(), down()
+        t_up, t_down, t_both = timed([up]), timed([down]), timed([up, down])
+        step_s = float(te.item()) / Ke * 1e-3
+        e2e["host_link"] = dict(h2d_gbs=round(h2d / t_up / 1e9, 1), d2h_gbs=round(d2h / t_down / 1e9, 1),
+                                both_at_once_gbs_each_way=round(max(h2d, d2h) / t_both / 1e9, 1),
+                                step_over_copy_floor=round(step_s / t_both, 3))
+        del host_in, host_out, dev_in, outs0
 
     # ---- every kernel by itself; the dominant one gives the roofline object ----------------------
     stages = None
