@@ -683,32 +683,56 @@ def model_configs(args, world, rank, local_rank, dev, barrier):
 
     c1 = None
     if world == 1:
-        torch.manual_seed(0)
-        mixer = SLinOSSMixer(768, d_state=64, expand=1, d_head=64, d_conv=4, chunk_size=64, device=dev,
-                             dtype=torch.bfloat16).train()
-        sb.use_b200_backends(mixer)
         x = torch.randn((8, 2048, 768), device=dev, dtype=torch.bfloat16, requires_grad=True)
 
-        def layer_step():
-            y = mixer(x)
-            y.float().square().mean().backward()
+        def time_layer(kind):
+            torch.manual_seed(0)
+            mixer = SLinOSSMixer(768, d_state=64, expand=1, d_head=64, d_conv=4, chunk_size=64, device=dev,
+                                 dtype=torch.bfloat16).train()
+            if kind == "reference":
+                from slinoss.layers.backend import (ReferenceCConv1dBackend, ReferenceMixerDecodeBackend,
+                                                    ReferenceScanBackend, ReferenceScanPrepBackend)
+                mixer.backend = ReferenceScanBackend(compute_dtype=None)
+                mixer.scanprep.backend = ReferenceScanPrepBackend()
+                mixer.cconv_backend = ReferenceCConv1dBackend()
+                mixer.decode_backend = ReferenceMixerDecodeBackend()
+            else:
+                sb.use_b200_backends(mixer, fuse_glue=(kind == "fused"))
 
-        ms, n, _ = _timed_steps(layer_step, 3, 300.0, barrier, dev)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(5):
-            layer_step()
-        torch.cuda.synchronize()
-        wall = (time.perf_counter() - t0) / 5 * 1e3
+            def layer_step():
+                y = mixer(x)
+                y.float().square().mean().backward()
+
+            ms, n, _ = _timed_steps(layer_step, 3, 300.0 if kind != "reference" else 150.0, barrier, dev)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(3):
+                layer_step()
+            torch.cuda.synchronize()
+            wall = (time.perf_counter() - t0) / 3 * 1e3
+            del mixer
+            torch.cuda.empty_cache()
+            return ms, n, wall
+
+        ms_f, n_f, wall_f = time_layer("fused")
+        ms_p, _, _ = time_layer("plain")
+        try:  # the reference's own torch backends on the same GPU: the "before" of this drop-in
+            ms_r, _, _ = time_layer("reference")
+        except Exception as exc:  # e.g. out of memory in the reference's autograd graph
+            ms_r = None
+            print(f"[bench] reference backends on the GPU failed: {exc!r}"[:300], file=sys.stderr)
         c1 = dict(workload="reference SLinOSSMixer layer fwd+bwd, d_model 768, 12 heads x 64, d_state 64, conv 4, "
-                           "chunk 64, batch 8, 2048 tokens, bf16 / fp32 scan state, B200 backends",
-                  ms_per_step=ms, steps_timed=n, wall_ms_per_step=wall, tokens_per_s=8 * 2048 / (ms * 1e-3))
-        del mixer, x
+                           "chunk 64, batch 8, 2048 tokens, bf16 / fp32 scan state, "
+                           "use_b200_backends(mixer, fuse_glue=True)",
+                  ms_per_step=ms_f, steps_timed=n_f, wall_ms_per_step=wall_f, tokens_per_s=8 * 2048 / (ms_f * 1e-3),
+                  unfused_glue_ms_per_step=ms_p, reference_backends_same_gpu_ms_per_step=ms_r,
+                  speedup_vs_reference_backends=(None if ms_r is None else ms_r / ms_f))
+        del x
         torch.cuda.empty_cache()
     torch.manual_seed(1)
     model = NextCharLM(vocab_size=256, block_size=4096, d_model=1024, n_layers=24, d_state=128, expand=1,
                        d_head=64, d_conv=4, chunk_size=64).to(device=dev, dtype=torch.bfloat16)
-    sb.use_b200_backends(model)
+    sb.use_b200_backends(model, fuse_glue=True)
     ddp = model
     if world > 1:
         ddp = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
@@ -728,7 +752,8 @@ def model_configs(args, world, rank, local_rank, dev, barrier):
 
     ms, n, _ = _timed_steps(train_step, 3, 1500.0, barrier, dev)
     c3 = dict(workload="reference NextCharLM training step, 24 layers, d_model 1024, 16 heads x 64, d_state 128, "
-                       "vocab 256 (uniform random tokens), batch 16 per GPU, 4096 tokens, bf16, B200 backends, "
+                       "vocab 256 (uniform random tokens), batch 16 per GPU, 4096 tokens, bf16, "
+                       "use_b200_backends(model, fuse_glue=True), "
                        + (f"DDP over {world} GPUs" if world > 1 else "1 GPU"),
               ms_per_step=ms, steps_timed=n, tokens_per_s=16 * 4096 * world / (ms * 1e-3), n_gpus=world)
     del model, ddp, opt

@@ -182,14 +182,33 @@ def _mixer_state(conv_state, scan_state):
     return SLinOSSMixerState(conv=conv_state, scan=scan_state)
 
 
-def use_b200_backends(model, *, decode_conv: bool = True, fuse_glue: bool = False) -> int:
+def _padded_linear_forward(self, x: torch.Tensor) -> torch.Tensor:
+    """``nn.Linear.forward`` for a projection whose output width is not a multiple of 8 half values
+    (e.g. the mixer's input projection at d_model 768, 12 heads, d_state 64: 2*768 + 12*13 + 4*12*64 =
+    4764).  With such a width every row of the output starts on an odd 8-byte boundary, the library GEMM
+    falls back to its 4-byte-aligned kernels (measured 0.46 ms against 0.13 ms per product at 16384 x 768 x
+    4764, bf16) and every consumer of the row slices loses its 16-byte accesses.  The weight is padded with
+    zero rows to the next multiple of 8 for the product (a 7 MB copy per call) and the extra columns are
+    sliced off again: same values, rows 16-byte aligned.  The parameters themselves are untouched."""
+    pad = (-int(self.out_features)) % 8
+    if pad == 0 or x.device.type != "cuda" or x.dtype == torch.float32:
+        return torch.nn.functional.linear(x, self.weight, self.bias)
+    w = torch.nn.functional.pad(self.weight, (0, 0, 0, pad))
+    b = None if self.bias is None else torch.nn.functional.pad(self.bias, (0, pad))
+    return torch.nn.functional.linear(x, w, b)[..., : self.out_features]
+
+
+def use_b200_backends(model, *, decode_conv: bool = True, fuse_glue: bool = False,
+                      align_projection: bool = True) -> int:
     """Point every ``SLinOSSMixer`` inside ``model`` (a mixer, a block, a whole ``NextCharLM``) at
     the four B200 backends, the way the reference's own workload builder swaps backends
     (scripts/perf/_nextchar.py:101-127: ``module.backend``, ``module.scanprep.backend``,
     ``module.cconv_backend``, ``module.decode_backend``).  With ``decode_conv`` the one-token conv
     step of each mixer (not behind a backend object in the reference) is replaced as well; with
     ``fuse_glue`` each mixer's ``forward`` is replaced by ``_mixer_forward_fused`` (same results; the
-    SiLU after the conv and the skip / re-layout / gate pass run inside kernels).  The
+    SiLU after the conv and the skip / re-layout / gate pass run inside kernels); with
+    ``align_projection`` an input projection whose width is not a multiple of 8 runs its product on a
+    zero-padded weight (``_padded_linear_forward``).  The
     reference package must be importable; its own ``ScanInputs`` / ``ScanState`` classes are used
     for the values handed back to the mixer.  Returns the number of mixers switched."""
     from slinoss.layers import SLinOSSMixer
@@ -211,6 +230,8 @@ def use_b200_backends(model, *, decode_conv: bool = True, fuse_glue: bool = Fals
                 module._apply_causal_depthwise_conv_step = types.MethodType(_conv_step_b200, module)
             if fuse_glue:
                 module.forward = types.MethodType(_mixer_forward_fused, module)
+            if align_projection and int(module.in_proj.out_features) % 8 != 0:
+                module.in_proj.forward = types.MethodType(_padded_linear_forward, module.in_proj)
             n += 1
     return n
 

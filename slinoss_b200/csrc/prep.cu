@@ -70,6 +70,11 @@ __device__ __forceinline__ void load_vec(const T *p, float (&v)[VEC]) {
     const T *e = reinterpret_cast<const T *>(&raw);
 #pragma unroll
     for (int i = 0; i < VEC; ++i) v[i] = to_f(e[i]);
+  } else if constexpr (VEC * sizeof(T) == 8) {
+    uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] = to_f(e[i]);
   } else {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) v[i] = to_f(p[i]);
@@ -83,6 +88,12 @@ __device__ __forceinline__ void store_vec(T *p, const float (&v)[VEC]) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) e[i] = from_f<T>(v[i]);
     *reinterpret_cast<uint4 *>(p) = raw;
+  } else if constexpr (VEC * sizeof(T) == 8) {
+    uint2 raw;
+    T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) e[i] = from_f<T>(v[i]);
+    *reinterpret_cast<uint2 *>(p) = raw;
   } else {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) p[i] = from_f<T>(v[i]);
@@ -786,14 +797,18 @@ static int params_rows_wide(const slx_prep_shape *s, const void *params) {
          ((long long)s->heads * 13 * 2) % 16 == 0;
 }
 
-// vector width (elements) usable for this problem: 16-byte vectors when every
-// row start and row width is 16-byte aligned, else scalar
+// vector width (elements) usable for this problem: 16-byte vectors when every row start and row
+// width is 16-byte aligned, 8-byte vectors when they are 8-byte aligned (a projection whose row
+// is a multiple of 4 but not of 8 half values, e.g. 4764 = 2*768 + 12*13 + 4*12*64), else scalar
 template <typename T>
 static int pick_vec(const slx_prep_shape *s, std::initializer_list<const void *> ptrs) {
-  const int v = 16 / (int)sizeof(T);
-  bool ok = (s->N % v == 0) && (s->P % v == 0) && (s->value_stride % v == 0) && (s->bc_stride % v == 0);
-  for (const void *p : ptrs) ok = ok && (p == nullptr || aligned16(p));
-  return ok ? v : 1;
+  for (int bytes = 16; bytes >= 8; bytes /= 2) {
+    const int v = bytes / (int)sizeof(T);
+    bool ok = (s->N % v == 0) && (s->P % v == 0) && (s->value_stride % v == 0) && (s->bc_stride % v == 0);
+    for (const void *p : ptrs) ok = ok && (p == nullptr || (reinterpret_cast<uintptr_t>(p) % bytes) == 0);
+    if (ok) return v;
+  }
+  return 1;
 }
 
 // lane-group width: 16 lanes x 16-byte vectors cover N = 128 half values in one
@@ -890,6 +905,8 @@ int slx_scanprep_fwd(const slx_prep_shape *s, const void *value, const void *par
     int vec = pick_vec<T_>(s, {value, bc, U, B, C});
     constexpr int VFULL = 16 / (int)sizeof(T_);
     if (vec == VFULL) rc = launch_prep_fwd<T_, VFULL>(s, d, value, params, bc, bias, scale, U, M, K, B, C, st);
+    else if (vec == VFULL / 2)
+      rc = launch_prep_fwd<T_, VFULL / 2>(s, d, value, params, bc, bias, scale, U, M, K, B, C, st);
     else rc = launch_prep_fwd<T_, 1>(s, d, value, params, bc, bias, scale, U, M, K, B, C, st);
   });
   return rc;
@@ -924,6 +941,9 @@ int slx_scanprep_bwd(const slx_prep_shape *s, const void *params, const void *bc
     if (vec == VFULL)
       rc = launch_prep_bwd<T_, VFULL>(s, d, params, bc, bias, scale, dU, dM, dK, dB, dC, d_value, d_params, d_bc,
                                       d_bias, d_scale, part, st);
+    else if (vec == VFULL / 2)
+      rc = launch_prep_bwd<T_, VFULL / 2>(s, d, params, bc, bias, scale, dU, dM, dK, dB, dC, d_value, d_params, d_bc,
+                                          d_bias, d_scale, part, st);
     else
       rc = launch_prep_bwd<T_, 1>(s, d, params, bc, bias, scale, dU, dM, dK, dB, dC, d_value, d_params, d_bc, d_bias,
                                   d_scale, part, st);
