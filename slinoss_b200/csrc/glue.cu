@@ -127,13 +127,24 @@ __global__ void __launch_bounds__(256) gate_skip_bwd_kernel(const T *__restrict_
   reinterpret_cast<float4 *>(pp)[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
 
-__global__ void __launch_bounds__(256) gate_skip_reduce_kernel(const float *__restrict__ part, float *__restrict__ d_skip,
+// d_skip[c] = sum over the partial rows, in a fixed order: 32 channels x 16 row groups per CTA, every
+// thread adds the rows of its group (i = g, g + 16, ...), then the 16 group sums are added in order.
+__global__ void __launch_bounds__(512) gate_skip_reduce_kernel(const float *__restrict__ part, float *__restrict__ d_skip,
                                                                int n_part, int C) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+  __shared__ float red[16][33];
+  const int cx = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float acc = 0.f;
-  for (int i = 0; i < n_part; ++i) acc += part[(size_t)i * C + c];
-  d_skip[c] = acc;
+  if (c < C)
+    for (int i = g; i < n_part; i += 16) acc += part[(size_t)i * C + c];
+  red[g][cx] = acc;
+  __syncthreads();
+  if (g == 0 && c < C) {
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) tot += red[k][cx];
+    d_skip[c] = tot;
+  }
 }
 
 static int check_glue(const slx_glue_shape *s, GlueDims *d) {
@@ -216,7 +227,7 @@ int slx_gate_skip_bwd(const slx_glue_shape *s, const void *y, const void *u, con
   rc = check_launch("gate_skip_bwd");
   if (rc) return rc;
   const int C = d.H * d.P;
-  gate_skip_reduce_kernel<<<(C + 255) / 256, 256, 0, as_stream(stream)>>>(part, d_skip, d.batch * n_tiles, C);
+  gate_skip_reduce_kernel<<<(C + 31) / 32, 512, 0, as_stream(stream)>>>(part, d_skip, d.batch * n_tiles, C);
   return check_launch("gate_skip_reduce");
 }
 
