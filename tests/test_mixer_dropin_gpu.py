@@ -334,3 +334,26 @@ def test_mixer_fused_glue_matches_unfused():
         y_full, st_full = plain(x, return_state=True)
     assert _rel(torch.cat([y_a, y_b], dim=1), y_full) <= 1e-2
     assert _rel(st.scan.state, st_full.scan.state) <= 1e-2 and torch.equal(st.conv, st_full.conv)
+
+
+def test_aligned_projection_gives_the_same_rows_on_16_byte_boundaries():
+    """``use_b200_backends`` runs an input projection whose width is not a multiple of 8 (4764 at
+    d_model 768, 12 heads, d_state 64) on a zero-padded weight: same values as the plain ``nn.Linear``
+    (up to the rounding of a different GEMM kernel), rows 4768 apart, parameters untouched, gradients
+    of weight and input as before."""
+    ref, ours = _make_mixers(torch.bfloat16, d_model=768, d_state=64, expand=1, chunk=64, seed=21)
+    assert int(ours.in_proj.out_features) == 4764 and "forward" in vars(ours.in_proj) and "forward" not in vars(ref.in_proj)
+    g = torch.Generator(device="cuda").manual_seed(22)
+    x = torch.randn((2, 96, 768), device="cuda", generator=g).to(torch.bfloat16).requires_grad_(True)
+    w = torch.randn((2, 96, 4764), device="cuda", generator=g).to(torch.bfloat16)
+    y_r = ref.in_proj(x)
+    y_o = ours.in_proj(x)
+    assert tuple(y_o.shape) == (2, 96, 4764) and y_o.stride(1) == 4768 and y_r.stride(1) == 4764
+    assert _rel(y_o, y_r) <= 4e-3
+    gx_r, gw_r = torch.autograd.grad(y_r, [x, ref.in_proj.weight], w)
+    gx_o, gw_o = torch.autograd.grad(y_o, [x, ours.in_proj.weight], w)
+    assert gw_o.shape == gw_r.shape == (4764, 768)
+    assert _rel(gx_o, gx_r) <= 4e-3 and _rel(gw_o, gw_r) <= 4e-3
+    # a projection that is already aligned keeps the stock forward
+    _, other = _make_mixers(torch.bfloat16, d_model=512, d_state=64, expand=1, chunk=64, seed=23)   # width 3176
+    assert int(other.in_proj.out_features) % 8 == 0 and "forward" not in vars(other.in_proj)
