@@ -14,18 +14,21 @@ tanh(N(0,1)) pi/4, taps 0.1 N(0,1), B, C ~ N(0,1/N)).  Rank 0 prints ONE JSON li
              K steps repeated `inner_repeats` times so that it lasts >= 1 s.
   e2e        the same metric through the public op with HOST buffers: pinned
              host -> device copies of every input and device -> host copies of
-             every result inside the timed region
+             every result inside the timed region; `host_link` beside it gives the
+             copy rates of the same buffers with no kernels (upload, download, both)
   roofline   the dominant kernel (per-chunk backward), timed alone with CUDA
              events: dense-tile flops per launch / duration against the measured
              bf16 burst peak; `traffic` from the ncu capture recorded in
              profiles/dominant_kernel_traffic.json
   stages     every kernel of the path timed by itself through the C ABI
-             (scan stages, scan prep, conv, decode step): ms, bound, achieved, frac
+             (scan stages, scan prep, conv, gate/skip, conv update, decode step): ms,
+             bound, achieved, frac
   cp         the context-parallel mode: one b1 H32 T262144 sequence split over the
              ranks along time (at N = 1 the same sequence on one GPU)
   config1 / config3   the reference's own SLinOSSMixer layer (fwd+bwd) and NextCharLM
              training step with every mixer on the B200 backends (needs the reference
-             package under baseline/_ref)
+             package under baseline/_ref); config1 also times the layer with unfused
+             glue and on the reference's own torch backends on the same GPU
   cpu_baseline  the reference's CPU path timed on the host cores on a bounded
              sample of the same workload (rank 0, N=1)
 
