@@ -243,6 +243,8 @@ static int launch_scan_bwd_tc(const ScanDims &d, const ScanBwdArgs<T> &a, cudaSt
   if (rc) return rc;
   rc = make_tile_map<T>(&maps.B, a.B, d.BH, d.T, d.D, 128, "chunk_scan_bwd");
   if (rc) return rc;
+  if ((rc = make_tile_map<T>(&maps.dC, a.dC, d.BH, d.T, d.D, 128, "chunk_scan_bwd"))) return rc;
+  if ((rc = make_tile_map<T>(&maps.dB, a.dB, d.BH, d.T, d.D, 128, "chunk_scan_bwd"))) return rc;
   kern<<<dim3(d.NC, d.BH), kTcBwdThreads, smem, st>>>(a, maps);
   return check_launch("chunk_scan_bwd_tc");
 }

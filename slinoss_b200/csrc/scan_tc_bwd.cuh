@@ -28,7 +28,10 @@
 
 namespace slx {
 
-using ScanBwdMaps = ScanTileMaps;
+// tensor maps of the raw C and B operands (loads) and of dC, dB (stores): (D, T, BH), boxes of 64 columns x 128 tokens
+struct alignas(64) ScanBwdMaps {
+  CUtensorMap C, B, dC, dB;
+};
 
 constexpr int kTcBwdThreads = 512;
 constexpr size_t scan_bwd_tc_smem_bytes() { return 1024 + 144 * 1024 + 28 * 1024 + 32 * 1024; }
@@ -121,6 +124,8 @@ __global__ void __launch_bounds__(kTcBwdThreads, 1) chunk_scan_bwd_tc_kernel(Sca
     umma::fence_mbar_init();
     umma::tma_prefetch_map(&maps.C);
     umma::tma_prefetch_map(&maps.B);
+    umma::tma_prefetch_map(&maps.dC);
+    umma::tma_prefetch_map(&maps.dB);
   }
   prefetch_cb(0);
   uint32_t tphase = 0;
