@@ -157,6 +157,8 @@ def chunk_increment_b200(U, M, K, B, *, B_prev=None, U_prev=None, chunk_size: in
     the reference checks them (contiguous, matching shapes, one device).  ``inc`` is fp32 like the
     reference's by default; ``inc_dtype`` = the activation dtype (tensor-core shapes only) stores
     it as the fused op does, halving the traffic of this stage's output and the next stage's input."""
+    if inc_dtype not in _ACT_DTYPES:
+        raise TypeError(f"inc_dtype must be float32, bfloat16 or float16. Got {inc_dtype}.")
     U, M, K, B, _ = _stage_inputs(U, M, K, B, None, B_prev, U_prev)
     b, h, T, P = map(int, U.shape)
     D = int(B.shape[-1])
@@ -165,8 +167,6 @@ def chunk_increment_b200(U, M, K, B, *, B_prev=None, U_prev=None, chunk_size: in
         raise ValueError(f"chunk_size must be positive. Got {chunk_size}.")
     NC = (T + L - 1) // L
     s = _shape(b, h, T, P, D // 2, L, U.dtype)
-    if inc_dtype not in _ACT_DTYPES:
-        raise TypeError(f"inc_dtype must be float32, bfloat16 or float16. Got {inc_dtype}.")
     inc = torch.empty((b, h, NC, P, D), device=U.device, dtype=inc_dtype)
     mch = torch.empty((b, h, NC, 2), device=U.device, dtype=torch.float32)
     bp, up = _f32(B_prev), _f32(U_prev)
@@ -198,10 +198,10 @@ def state_passing_b200(inc, m_chunk, *, initial_states=None, want_starts: bool =
                          f"Got {tuple(initial_states.shape)}.")
     if starts_dtype not in _ACT_DTYPES:
         raise TypeError(f"starts_dtype must be float32, bfloat16 or float16. Got {starts_dtype}.")
+    if inc.dtype in _ACT_DTYPES and inc.dtype != torch.float32 and want_starts and inc.dtype != starts_dtype:
+        raise TypeError(f"inc must be float32 or starts_dtype={starts_dtype}. Got {inc.dtype}.")
     _require_cuda(inc, m_chunk, initial_states)
     dev = _lib.same_device(inc, m_chunk, initial_states)
-    if inc.dtype != torch.float32 and want_starts and inc.dtype != starts_dtype:
-        raise TypeError(f"inc must be float32 or starts_dtype={starts_dtype}. Got {inc.dtype}.")
     if inc.dtype not in _ACT_DTYPES:
         inc = inc.to(torch.float32)
     inc, m_chunk = _aligned(inc.detach().contiguous()), _f32(m_chunk)

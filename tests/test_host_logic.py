@@ -193,6 +193,11 @@ def test_stage_entry_points_validate_like_the_fused_op():
         slinoss_b200.state_passing_b200(inc, torch.zeros(1, 2, 3, 2))
     with pytest.raises(ValueError, match=r"inc must be \(batch,heads,chunks,P,2N\)"):
         slinoss_b200.state_passing_b200(inc[0], torch.zeros(2, 3, 2))
+    # half-precision increments go with chunk starts of the same dtype only
+    with pytest.raises(TypeError, match="inc must be float32 or starts_dtype"):
+        slinoss_b200.state_passing_b200(inc.to(torch.bfloat16), torch.zeros(1, 2, 3, 2))
+    with pytest.raises(TypeError, match="inc_dtype must be"):
+        slinoss_b200.chunk_increment_b200(U, M, K, B, chunk_size=16, inc_dtype=torch.float64)
 
 
 def test_context_parallel_rejects_non_contiguous_slices():
@@ -212,3 +217,33 @@ def test_context_parallel_rejects_non_contiguous_slices():
                                      chunk_size=8)
     finally:
         dist.destroy_process_group()
+
+
+def test_use_b200_backends_switches_every_mixer_and_leaves_cpu_math_alone():
+    """``use_b200_backends`` on the reference's own mixer: the four backend slots are replaced, an input
+    projection whose width is not a multiple of 8 gets the padded forward, and that forward is the plain
+    ``nn.Linear`` for tensors it does not apply to (CPU, fp32)."""
+    from ref_util import import_reference
+
+    import_reference()
+    from slinoss.layers import SLinOSSMixer
+
+    import slinoss_b200 as sb
+
+    torch.manual_seed(0)
+    mixer = SLinOSSMixer(96, d_state=16, expand=1, d_head=32, d_conv=4, chunk_size=32)
+    width = int(mixer.in_proj.out_features)
+    assert width == 2 * 96 + 3 * 13 + 4 * 3 * 16 and width % 8 != 0
+    x = torch.randn(2, 5, 96)
+    before = mixer.in_proj(x)
+    assert sb.use_b200_backends(mixer) == 1
+    assert isinstance(mixer.backend, sb.B200ScanBackend) and isinstance(mixer.scanprep.backend, sb.B200ScanPrepBackend)
+    assert isinstance(mixer.cconv_backend, sb.B200CConv1dBackend)
+    assert isinstance(mixer.decode_backend, sb.B200MixerDecodeBackend)
+    assert "forward" in vars(mixer.in_proj) and "_apply_causal_depthwise_conv_step" in vars(mixer)
+    assert "forward" not in vars(mixer)                       # the fused forward is opt-in
+    assert torch.equal(mixer.in_proj(x), before)              # CPU tensors: the stock product
+    other = SLinOSSMixer(96, d_state=16, expand=1, d_head=32, d_conv=4, chunk_size=32)
+    assert sb.use_b200_backends(other, fuse_glue=True, align_projection=False, decode_conv=False) == 1
+    assert "forward" in vars(other) and "forward" not in vars(other.in_proj)
+    assert "_apply_causal_depthwise_conv_step" not in vars(other)
