@@ -245,7 +245,8 @@ def cpu_sample(cfg, chunk, n_slices, seed=0, warm=True):
         sec = cpu_reference_time(cfg, chunk, n_slices, T, seed=seed)
         info = dict(unit="tokens/s", cores=torch.get_num_threads(), kind="reference",
                     sample=f"{n_slices} (batch 1, head 1) slices x {T} tokens, fwd + autograd.grad of the reference's "
-                           f"v2x2ssd (bf16 inputs, fp32 compute, torch CPU ops); extrapolated to {BH} slices")
+                           f"v2x2ssd (bf16 inputs, fp32 compute, torch CPU ops); "
+                           + (f"extrapolated to {BH} slices" if n_slices < BH else "that is the whole workload"))
         return sec, n_slices, info
     threads = os.cpu_count() or 1
     bh_s = min(threads, BH)
