@@ -113,7 +113,7 @@ constexpr size_t scan_fwd_tc_smem_bytes() { return 1024 + 88 * 1024 + 12 * 1024;
 
 // Forward chunk scan (replaces reference.py:1059 chunk_scan) on tensor cores.
 //   S  = Qbar kappa^T          (128 x 128, K = D)       tcgen05, fp32 in TMEM
-//   Yo = Qbar Z0^T             (128 x 64,  K = D)
+//   Yo = Qbar Z0^T             (128 x 64,  K = D)       (one product with S: N = 192)
 //   Yd = S' U                  (128 x 64,  K = 128),  S' = masked/decayed S (+ diagonal)
 //   Y  = Yd + exp(lp_t) Yo + sigma_t u_{-1}
 template <typename T>
@@ -125,8 +125,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   unsigned char *tQ = base;               // [128][64]  Qbar slab   (also the Y staging tile)
   unsigned char *tK = base + 16384;       // [128][64]  kappa slab
   unsigned char *tS = base;               // 2 x [128][64]  S' (over the Qbar and kappa tiles, idle by then)
-  unsigned char *tU = base + 32768;       // [128][64]  U
-  unsigned char *tZ = base + 49152;       // [64][64]   Z0 slab
+  unsigned char *tZ = base + 32768;       // [64][64]   Z0 slab, right behind kappa: [kappa ; Z0] is ONE 192-row B operand
+  unsigned char *tU = base + 40960;       // [128][64]  U
   unsigned char *sC = base + 57344;       // raw C slab, filled by cp.async one slab ahead
   unsigned char *sB = base + 73728;       // raw B slab
   float *lp = reinterpret_cast<float *>(base + 90112);  // 128
@@ -233,8 +233,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   }
   const bool fast_decay = !__syncthreads_or(tid < L && decay_step_out_of_range(lp, tid));
 
-  const uint32_t sQ = umma::smem_u32(tQ), sK = umma::smem_u32(tK), sU = umma::smem_u32(tU), sS = umma::smem_u32(tS),
-                 sZ = umma::smem_u32(tZ);
+  const uint32_t sQ = umma::smem_u32(tQ), sK = umma::smem_u32(tK), sU = umma::smem_u32(tU), sS = umma::smem_u32(tS);
   constexpr int fmt = umma::HalfFmt<T>::value;
   float2 acc_cb[4], acc_cbm[4];
 #pragma unroll
@@ -297,14 +296,12 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
     SLX_FSTAMP(11 + 4 * sl);
     if (tid == 0) {
       umma::fence_after_sync();
-      const uint32_t id_s = umma::make_idesc(128, 128, false, false, fmt);
-      const uint32_t id_o = umma::make_idesc(128, 64, false, false, fmt);
+      // [S | Yo] = Qbar [kappa ; Z0]^T as one product of N = 192 per K-step: Qbar is fetched once for both, and at
+      // this width the fetches fit under the product's own time (two products of N = 128 and N = 64 do not)
+      const uint32_t id_so = umma::make_idesc(128, 192, false, false, fmt);
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        uint64_t da = umma::desc_kmajor(sQ, kk);
-        umma::mma_ss(tmem + 0, da, umma::desc_kmajor(sK, kk), id_s, (sl | kk) != 0);
-        umma::mma_ss(tmem + 128, da, umma::desc_kmajor(sZ, kk), id_o, (sl | kk) != 0);
-      }
+      for (int kk = 0; kk < 4; ++kk)
+        umma::mma_ss(tmem + 0, umma::desc_kmajor(sQ, kk), umma::desc_kmajor(sK, kk), id_so, (sl | kk) != 0);
       umma::commit(mbar_s);
     }
   }
