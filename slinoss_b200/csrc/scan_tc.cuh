@@ -115,7 +115,8 @@ constexpr size_t scan_fwd_tc_smem_bytes() { return 1024 + 88 * 1024 + 12 * 1024;
 //   S  = Qbar kappa^T          (128 x 128, K = D)       tcgen05, fp32 in TMEM
 //   Yo = Qbar Z0^T             (128 x 64,  K = D)       (one product with S: N = 192)
 //   Yd = S' U                  (128 x 64,  K = 128),  S' = masked/decayed S (+ diagonal)
-//   Y  = Yd + exp(lp_t) Yo + sigma_t u_{-1}
+//   Y  = Yd + exp(lp_t) Yo;  the token in front of the chunk takes source slot 127 of S' / U, token 127's own
+//        diagonal term is added by hand
 template <typename T>
 __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFwdArgs<T> a) {
   constexpr int L = kTcL, P = kTcP;
@@ -131,10 +132,11 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   unsigned char *sB = base + 73728;       // raw B slab
   float *lp = reinterpret_cast<float *>(base + 90112);  // 128
   float2 *ph = reinterpret_cast<float2 *>(lp + L);      // 128 each from here
-  float2 *mraw = ph + L, *kc = mraw + L, *kp = kc + L, *gk = kp + L, *cbv = gk + L, *cbm = cbv + L;
-  float2 *bm1 = cbm + L;                                 // 128 (b_{-1}, all of D)
+  float2 *mraw = ph + L, *kc = mraw + L, *kp = kc + L, *gk = kp + L, *cbv = gk + L;
+  float2 *bm1 = cbv + L;                                 // 128 (b_{-1}, all of D)
   float *um1 = reinterpret_cast<float *>(bm1 + 128);     // 64
   float *e2 = um1 + 64;                                  // 128: decay table (decay_mask32)
+  unsigned char *u127 = reinterpret_cast<unsigned char *>(e2 + L);  // 128 bytes: token 127's own u row
   __shared__ uint64_t mbar;
   __shared__ uint32_t tmem_slot;
 
@@ -226,8 +228,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   const uint32_t tmem = tmem_slot;
   if (tid < L) {
     int t = tid;
-    float2 g = make_float2(0.f, 0.f);
-    if (t + 1 < L) g = cmulc(cadd(cmul(mraw[t + 1], kc[t]), kp[t + 1]), ph[t + 1]);  // gamma_t conj(phi_{t+1})
+    // gamma_t conj(phi_{t+1}); slot 127 (no query follows the last token, so its column is free) carries the
+    // token in front of the chunk: kappa[127] = k^p_0 conj(phi_0) b_{-1}
+    float2 g = cmulc(kp[0], ph[0]);
+    if (t + 1 < L) g = cmulc(cadd(cmul(mraw[t + 1], kc[t]), kp[t + 1]), ph[t + 1]);
     gk[t] = g;
     e2[t] = decay_table_entry(lp, t, L);
   }
@@ -235,9 +239,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
 
   const uint32_t sQ = umma::smem_u32(tQ), sK = umma::smem_u32(tK), sU = umma::smem_u32(tU), sS = umma::smem_u32(tS);
   constexpr int fmt = umma::HalfFmt<T>::value;
-  float2 acc_cb[4], acc_cbm[4];
+  float2 acc_cb[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) acc_cb[i] = acc_cbm[i] = make_float2(0.f, 0.f);
+  for (int i = 0; i < 4; ++i) acc_cb[i] = make_float2(0.f, 0.f);
   uint32_t phase = 0;
   bool ok = true;
 
@@ -249,6 +253,15 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
     if (sl > 0) {
       ok = umma::mbar_wait(mbar_s, phase) && ok;  // previous slab's products are done: tiles are free
       phase ^= 1;
+    } else if (r0 == 31) {
+      // source slot 127 of S' is the token in front of the chunk: its row of the U tile (which this thread
+      // copied in) becomes u_{-1}; token 127's own diagonal term is added by hand in the epilogue
+      float tmp[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) tmp[e] = um1[8 * j + e];
+      uint4 *cell = reinterpret_cast<uint4 *>(tU + umma::swz_off(L - 1, j));
+      *reinterpret_cast<uint4 *>(u127 + 16 * j) = *cell;  // kept for the epilogue
+      *cell = pack8<T>(tmp);
     }
     uint4 cr[4], br[4];
 #pragma unroll
@@ -258,9 +271,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
       br[i] = *reinterpret_cast<const uint4 *>(sB + off);
     }
     SLX_FSTAMP(9 + 4 * sl);
-    // b_{-1} chunk of this slab (for the boundary score)
-    uint4 bm;
-    {
+    // b_{-1} chunk of this slab: only the threads that stage row 127 (the boundary slot) need it
+    uint4 bm = make_uint4(0, 0, 0, 0);
+    if (r0 == 31) {
       float tmp[8];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -274,9 +287,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
     for (int i = 0; i < 4; ++i) {
       int r = r0 + 32 * i;
       *reinterpret_cast<uint4 *>(tQ + umma::swz_off(r, j)) = rotate_chunk<T>(cr[i], cconj(ph[r]));
-      *reinterpret_cast<uint4 *>(tK + umma::swz_off(r, j)) = rotate_chunk<T>(br[i], gk[r]);
+      *reinterpret_cast<uint4 *>(tK + umma::swz_off(r, j)) = rotate_chunk<T>(r == L - 1 ? bm : br[i], gk[r]);
       cdot_chunk<T>(cr[i], br[i], acc_cb[i]);
-      cdot_chunk<T>(cr[i], bm, acc_cbm[i]);
     }
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
@@ -306,14 +318,11 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
     }
   }
   SLX_FSTAMP(2);
-  // per-row dots: cb_t = <c_t, b_t>, cbm_t = <c_t, b_{-1}>
+  // per-row dots: cb_t = <c_t, b_t>
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float2 s1 = octet_sum(acc_cb[i]), s2 = octet_sum(acc_cbm[i]);
-    if (j == 0) {
-      cbv[r0 + 32 * i] = s1;
-      cbm[r0 + 32 * i] = s2;
-    }
+    float2 s1 = octet_sum(acc_cb[i]);
+    if (j == 0) cbv[r0 + 32 * i] = s1;
   }
   ok = umma::mbar_wait(mbar_s, phase) && ok;
   phase ^= 1;
@@ -331,10 +340,20 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
     for (int half = 0; half < 2; ++half) {
       const int c0 = 64 * h + 32 * half;
       float v[32];
-      if (c0 <= 32 * q4 + 31) {
+      const bool last = c0 == 96;  // the block that holds column 127, the boundary slot
+      if (c0 <= 32 * q4 + 31 || last) {
         umma::tmem_ld32(umma::tmem_addr(tmem, 32 * q4, c0), v);
-        if (fast_decay) decay_mask32<true>(v, c0, t, lpt, lp, e2, dg);
-        else decay_mask32<false>(v, c0, t, lpt, lp, e2, dg);
+        const float s127 = v[31];
+        if (c0 <= 32 * q4 + 31) {
+          if (fast_decay) decay_mask32<true>(v, c0, t, lpt, lp, e2, dg);
+          else decay_mask32<false>(v, c0, t, lpt, lp, e2, dg);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0.f;
+        }
+        // column 127: <Qbar_t, k^p_0 conj(phi_0) b_{-1}> exp(lp_t - lp_0), the term of the token in front of the
+        // chunk, for every row (row 127 loses its diagonal entry here: added in the epilogue)
+        if (last) v[31] = s127 * __expf(lpt - lp[0]);
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0.f;
@@ -362,16 +381,28 @@ __global__ void __launch_bounds__(kTcThreads, 2) chunk_scan_fwd_tc_kernel(ScanFw
   umma::fence_after_sync();
 
   SLX_FSTAMP(5);
-  // ---- Y = Yd + exp(lp_t) Yo + sigma_t u_{-1} -> staging tile -> global ---------------
+  // ---- Y = Yd + exp(lp_t) Yo (+ the diagonal term of token 127) -> staging tile -> global -------------
   {
     float yo[32], yd[32];
     umma::tmem_ld32(umma::tmem_addr(tmem, 32 * q4, 128 + 32 * h), yo);
     umma::tmem_ld32(umma::tmem_addr(tmem, 32 * q4, 192 + 32 * h), yd);
     const float el = __expf(lpt);
-    float2 w = cmul(cmul(cmulc(ph[t], ph[0]), kp[0]), cbm[t]);
-    const float sig = __expf(lpt - lp[0]) * w.x;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) yd[i] = fmaf(sig, um1[32 * h + i], fmaf(el, yo[i], yd[i]));
+    for (int i = 0; i < 32; ++i) yd[i] = fmaf(el, yo[i], yd[i]);
+    if (t == L - 1) {  // token 127's diagonal term (zero for a row past the end of the sequence: c, b, u are zero)
+      const float dg = kc[t].x * cbv[t].x - kc[t].y * cbv[t].y;  // Re(k^c_t <c_t,b_t>)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint4 ul = *reinterpret_cast<const uint4 *>(u127 + 64 * h + 16 * k);
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(&ul);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 uv = umma::unpack2(w[e], T());
+          yd[8 * k + 2 * e] = fmaf(dg, uv.x, yd[8 * k + 2 * e]);
+          yd[8 * k + 2 * e + 1] = fmaf(dg, uv.y, yd[8 * k + 2 * e + 1]);
+        }
+      }
+    }
 #pragma unroll
     for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4 *>(tQ + umma::swz_off(t, 4 * h + k)) = pack8<T>(yd + 8 * k);
   }
