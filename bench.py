@@ -725,12 +725,35 @@ def model_configs(args, world, rank, local_rank, dev, barrier):
         except Exception as exc:  # e.g. out of memory in the reference's autograd graph
             ms_r = None
             print(f"[bench] reference backends on the GPU failed: {exc!r}"[:300], file=sys.stderr)
+        # host cost of the scan op at this layer's shape (b8 H12 T2048 P64 N64): Python-level forward + backward
+        # wall time against the sum of its kernels timed one by one through the C ABI
+        ocfg = dict(batch=8, heads=12, T=2048, P=64, N=64)
+        oin = make_inputs(ocfg, dev, 7, torch.bfloat16)
+        olv = [oin[k].requires_grad_(True) for k in ("U", "M", "K", "B", "C")]
+
+        def op_step():
+            Yo = sb.v2x2ssd_b200(*olv, chunk_size=128)
+            torch.autograd.grad(Yo, olv, oin["dY"])
+
+        for _ in range(5):
+            op_step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(50):
+            op_step()
+        torch.cuda.synchronize()
+        op_wall = (time.perf_counter() - t0) / 50 * 1e3
+        op_kernels = sum(st["ms"] for st in scan_stage_timings(
+            {k: v.detach() for k, v in oin.items()}, 8, 12, 2048, 64, 64, 128, torch.bfloat16, reps=10, warm=3))
+        del oin, olv
         c1 = dict(workload="reference SLinOSSMixer layer fwd+bwd, d_model 768, 12 heads x 64, d_state 64, conv 4, "
                            "chunk 64, batch 8, 2048 tokens, bf16 / fp32 scan state, "
                            "use_b200_backends(mixer, fuse_glue=True)",
                   ms_per_step=ms_f, steps_timed=n_f, wall_ms_per_step=wall_f, tokens_per_s=8 * 2048 / (ms_f * 1e-3),
                   unfused_glue_ms_per_step=ms_p, reference_backends_same_gpu_ms_per_step=ms_r,
-                  speedup_vs_reference_backends=(None if ms_r is None else ms_r / ms_f))
+                  speedup_vs_reference_backends=(None if ms_r is None else ms_r / ms_f),
+                  scan_op_wall_ms=op_wall, scan_op_kernel_ms_sum=op_kernels,
+                  scan_op_wall_over_kernels=op_wall / op_kernels)
         del x
         torch.cuda.empty_cache()
     torch.manual_seed(1)
