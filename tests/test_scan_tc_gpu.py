@@ -68,6 +68,18 @@ def test_full_op_tc_vs_oracle(N, T, dtype):
     assert all(v < 2e-2 for v in errs.values()), errs
 
 
+@pytest.mark.parametrize("N,T,streaming", [(64, 1, True), (32, 5, True), (128, 127, False), (128, 129, True)])
+def test_short_and_one_past_a_chunk_tc_vs_oracle(N, T, streaming):
+    """Sequences shorter than one 128-token chunk (row 127 of every tile is padding and doubles as the slot of
+    the token in front of the chunk) and one token past a chunk, with and without streaming inputs."""
+    inp = make_scan_inputs(2, 2, T, N, 64, torch.bfloat16, seed=T, streaming=streaming, with_init=True, dist="cfg2")
+    Y, fin, grads = run_b200_fwd_bwd(inp, 128)
+    Yo, fino, go = oracle_fwd_bwd(inp)
+    errs = {"Y": rel_err(to_np(Y), Yo), "final": rel_err(to_np(fin), fino)}
+    errs.update({k: rel_err(to_np(grads[k]), go[k]) for k in SCAN_GRADS if grads[k] is not None})
+    assert all(v < 2e-2 for v in errs.values()), errs
+
+
 @pytest.mark.parametrize("N,T,dtype", [(128, 300, torch.bfloat16), (32, 256, torch.float16), (96, 128, torch.bfloat16)])
 def test_increment_stage_tc_vs_exact(N, T, dtype):
     import slinoss_b200 as sb
